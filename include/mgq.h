@@ -1,0 +1,157 @@
+/*
+ * mgq -- B200 (sm_100a) CUDA implementation of meganeura's Q4/Q8 dequantize-fused matmul.
+ *
+ * C ABI of libmgq.  Plain pointers and sizes only; no C++ or framework types.
+ * Every function returns an mgq_status (0 = ok) unless stated; the message of the
+ * last failure on the calling thread is available from mgq_last_error().
+ * Nothing in this library falls back to the CPU: a call that needs a GPU and finds
+ * none returns MGQ_ERR_CUDA.
+ *
+ * Each group cites the meganeura interface it stands in for (paths inside the
+ * meganeura source tree).  Packed weight layouts are byte-for-byte the reference's:
+ *
+ *   Q8: 36 B per 32-element block: f16 scale, 2 zero bytes, 32 int8 codes;
+ *       block index = n * (K/32) + k/32                       (src/codegen.rs:785-805)
+ *   Q4: all block headers first (u32 = f16 d | f16 m << 16), then 16 nibble bytes per
+ *       block (element 2j low nibble, 2j+1 high nibble); value = nibble * d + m
+ *                                                            (src/codegen.rs:748-769)
+ */
+#ifndef MGQ_H
+#define MGQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* WeightFormat, same order as meganeura's enum (src/compile.rs:6-13). */
+#define MGQ_FMT_F32 0
+#define MGQ_FMT_F16 1
+#define MGQ_FMT_Q4  2
+#define MGQ_FMT_Q8  3
+
+/* Activation dtype of the A operand. */
+#define MGQ_A_F32  0
+#define MGQ_A_BF16 1
+
+typedef enum mgq_status {
+    MGQ_OK = 0,
+    MGQ_ERR_NULL = 1,        /* a required pointer was null */
+    MGQ_ERR_SHAPE = 2,       /* K % 32 != 0, zero-sized or out-of-range dimension (replaces the
+                                reference's assert!, src/runtime.rs:2037-2040, 2145-2148) */
+    MGQ_ERR_FORMAT = 3,      /* weight format or dtype not handled by this library */
+    MGQ_ERR_CUDA = 4,        /* a CUDA runtime call failed (no device, launch error, ...) */
+    MGQ_ERR_NAME = 5,        /* unknown parameter / input name (reference panics, src/runtime.rs:2492) */
+    MGQ_ERR_SIZE = 6,        /* host slice length does not match the tensor */
+    MGQ_ERR_ALIGN = 7,       /* device pointer not aligned as the kernel requires (16 B for weights) */
+    MGQ_ERR_STATE = 8,       /* call not valid in the object's current state */
+    MGQ_ERR_TIMEOUT = 9      /* a bounded device-side wait ran out */
+} mgq_status;
+
+const char *mgq_last_error(void);
+const char *mgq_version(void);
+
+/* ---- format: TensorType::size_bytes for quantized dtypes (src/graph.rs:52-68) ---------- */
+size_t mgq_packed_bytes(int fmt, size_t k, size_t n);
+
+/* ---- host quantizers: quantize_q4_0 / dequantize_q4_0 / quantize_q8_0 / dequantize_q8_0
+ *      (src/runtime.rs:2035-2215).  w and out are row-major [k, n] f32 on the host. ------- */
+int mgq_quantize_q4(const float *w, size_t k, size_t n, uint8_t *out);
+int mgq_quantize_q8(const float *w, size_t k, size_t n, uint8_t *out);
+int mgq_dequantize_q4(const uint8_t *packed, size_t k, size_t n, float *out);
+int mgq_dequantize_q8(const uint8_t *packed, size_t k, size_t n, float *out);
+
+/* Columns [n0, n1) of a packed [k, n] weight as a self-contained packed [k, n1-n0] weight
+ * (host memory).  No reference counterpart: the reference is single-device; a block never
+ * spans columns (block = n*(K/32)+b, src/codegen.rs:753, 788), so a column range is itself a
+ * valid weight.  out must hold mgq_packed_bytes(fmt, k, n1-n0). */
+int mgq_shard_columns(int fmt, const uint8_t *packed, size_t k, size_t n, size_t n0, size_t n1, uint8_t *out);
+
+/* ---- device buffers: Session buffer allocation (zero-filled, src/runtime.rs:1737-1755),
+ *      upload_buffer (2552-2558) and read-back (2612-2629). ------------------------------- */
+int mgq_buffer_create(size_t bytes, void **out_dev);
+int mgq_buffer_destroy(void *dev);
+int mgq_buffer_upload(void *dev, const void *host, size_t bytes, void *stream);
+int mgq_buffer_download(const void *dev, void *host, size_t bytes, void *stream);
+
+/* ---- kernels.  All pointers are device pointers; stream is a cudaStream_t (NULL = default).
+ *
+ * y[m,n] = x[m,k] . dequant(w)[k,n] (+ addend[m,n]),  f32 in, f32 accumulate, f32 out.
+ * Stands in for the MatMulGemv / MatMulGemvAdd dispatches (src/compile.rs:1390-1406,
+ * 1498-1509; bindings matrix_a, matrix_b, matrix_c[, src], params=[m,k,n,0]) with the
+ * quantized weight semantics of dequant_q4 / dequant_q8.  The reference has no working
+ * quantized GEMV (src/codegen.rs:1065-1073 falls back to the f32 shader), so the result is
+ * defined by the tiled kernel's math.  1 <= m <= MGQ_GEMV_MAX_M; w must be 16-byte aligned. */
+#define MGQ_GEMV_MAX_M 16
+int mgq_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
+             uint32_t m, uint32_t k, uint32_t n, void *stream);
+
+/* c[m,n] = a[m,k] . dequant(w)[k,n] (+ addend[m,n]); a is f32 or bf16 row-major, c is f32.
+ * Stands in for the MatMul / FusedMatMulAdd dispatches with a quantized weight_format
+ * (src/compile.rs:1408-1419, 1511-1522; src/shaders/matmul.wgsl:28-109). */
+int mgq_gemm(int fmt, const void *a, int a_dtype, const void *w, const float *addend, float *c,
+             uint32_t m, uint32_t k, uint32_t n, void *stream);
+
+/* Routing wrapper: mgq_gemv when m <= MGQ_GEMV_MAX_M (f32 activations), else mgq_gemm. */
+int mgq_matmul(int fmt, const void *a, int a_dtype, const void *w, const float *addend, float *c,
+               uint32_t m, uint32_t k, uint32_t n, void *stream);
+
+/* Same contraction with HOST activations/outputs and a resident device weight: copies
+ * a (and addend) to the device, runs mgq_matmul, copies c back and synchronises.  This is
+ * the set_input -> step -> wait -> read_output round trip of a one-node session. */
+int mgq_matmul_host(int fmt, const void *a_host, int a_dtype, const void *w_dev, const float *addend_host,
+                    float *c_host, uint32_t m, uint32_t k, uint32_t n);
+
+/* ---- Graph / Session surface (src/graph.rs:714-795, src/train.rs:380-389,
+ *      src/runtime.rs:2327-2345, 2496-2550, 2612-2643, 2786-2791, 2835-2959).
+ *
+ * Only the nodes on the quantized-matmul path exist: inputs, parameters (f32 vectors are
+ * accepted only as addends; matmul weights must be Q4/Q8), matmul and add.  MatMul+Add is
+ * fused to FusedMatMulAdd like apply_matmul_add_fusions (src/optimize.rs:724-767) and the
+ * plan's dispatches carry the reference's shader names, workgroups, params and labels. */
+typedef struct mgq_graph mgq_graph;
+typedef struct mgq_session mgq_session;
+
+/* ShaderEntry values used by plan dispatches (names as in src/compile.rs). */
+#define MGQ_SHADER_MATMUL            0
+#define MGQ_SHADER_FUSED_MATMUL_ADD  1
+#define MGQ_SHADER_MATMUL_GEMV       2
+#define MGQ_SHADER_MATMUL_GEMV_ADD   3
+#define MGQ_SHADER_ADD               4
+
+mgq_graph *mgq_graph_new(void);
+void mgq_graph_free(mgq_graph *g);
+/* Each builder returns the new node id (>= 0) or -status. */
+int mgq_graph_input(mgq_graph *g, const char *name, const size_t *shape, size_t rank);
+int mgq_graph_parameter(mgq_graph *g, const char *name, const size_t *shape, size_t rank);
+int mgq_graph_parameter_q4(mgq_graph *g, const char *name, const size_t *shape, size_t rank);
+int mgq_graph_parameter_q8(mgq_graph *g, const char *name, const size_t *shape, size_t rank);
+int mgq_graph_matmul(mgq_graph *g, int a, int b);
+int mgq_graph_add(mgq_graph *g, int a, int b);
+int mgq_graph_set_outputs(mgq_graph *g, const int *ids, size_t count);
+
+/* build_inference_session (src/train.rs:380-389): fuse, lower, allocate zero-filled buffers. */
+int mgq_build_inference_session(const mgq_graph *g, mgq_session **out);
+void mgq_session_free(mgq_session *s);
+/* set_parameter quantizes f32 data on the host for Q4/Q8 parameters (src/runtime.rs:2327-2345). */
+int mgq_session_set_parameter(mgq_session *s, const char *name, const float *data, size_t len);
+/* upload_param: raw bytes into the parameter buffer, no conversion (src/runtime.rs:2786-2791). */
+int mgq_session_upload_param(mgq_session *s, const char *name, const void *bytes, size_t nbytes);
+int mgq_session_set_input(mgq_session *s, const char *name, const float *data, size_t len);
+int mgq_session_step(mgq_session *s);
+int mgq_session_wait(mgq_session *s);
+int mgq_session_read_output(mgq_session *s, float *out, size_t len);
+int mgq_session_read_output_by_index(mgq_session *s, size_t index, float *out, size_t len);
+/* plan() inspection (tests/gemv_parity.rs:32-52 reads dispatches[i].shader). */
+int mgq_session_num_dispatches(const mgq_session *s);
+int mgq_session_dispatch_info(const mgq_session *s, size_t index, int *shader, uint32_t workgroups[3],
+                              uint32_t params[4], int *weight_format, char *label, size_t label_cap);
+/* Number of kernels launched by this session so far. */
+uint64_t mgq_session_launch_count(const mgq_session *s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MGQ_H */

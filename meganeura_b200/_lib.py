@@ -1,0 +1,100 @@
+"""ctypes binding of libmgq (the C ABI declared in include/mgq.h).
+
+The shared library is built in-tree by ``meganeura_b200/csrc/Makefile``.  There is no
+fallback: if the library is missing the import fails, and every call that needs a GPU
+returns ``MGQ_ERR_CUDA`` (raised here as :class:`MgqError`) when none is usable.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "csrc", "libmgq.so")
+
+FMT_F32, FMT_F16, FMT_Q4, FMT_Q8 = 0, 1, 2, 3
+A_F32, A_BF16 = 0, 1
+GEMV_MAX_M = 16
+
+STATUS_NAMES = {
+    0: "MGQ_OK", 1: "MGQ_ERR_NULL", 2: "MGQ_ERR_SHAPE", 3: "MGQ_ERR_FORMAT", 4: "MGQ_ERR_CUDA",
+    5: "MGQ_ERR_NAME", 6: "MGQ_ERR_SIZE", 7: "MGQ_ERR_ALIGN", 8: "MGQ_ERR_STATE", 9: "MGQ_ERR_TIMEOUT",
+}
+
+
+class MgqError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"{STATUS_NAMES.get(status, status)}: {message}")
+        self.status = status
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `make -C {os.path.join(_HERE, 'csrc')}` "
+            "(nvcc, sm_100a).  There is no CPU fallback.")
+    return ctypes.CDLL(LIB_PATH)
+
+
+lib = _load()
+
+_sz, _u32, _int, _vp = ctypes.c_size_t, ctypes.c_uint32, ctypes.c_int, ctypes.c_void_p
+_f32p = ctypes.POINTER(ctypes.c_float)
+_u8p = ctypes.POINTER(ctypes.c_uint8)
+_szp = ctypes.POINTER(ctypes.c_size_t)
+
+# name -> (restype, argtypes).  Every symbol include/mgq.h declares is listed here.
+SIGNATURES = {
+    "mgq_last_error": (ctypes.c_char_p, []),
+    "mgq_version": (ctypes.c_char_p, []),
+    "mgq_packed_bytes": (_sz, [_int, _sz, _sz]),
+    "mgq_quantize_q4": (_int, [_vp, _sz, _sz, _vp]),
+    "mgq_quantize_q8": (_int, [_vp, _sz, _sz, _vp]),
+    "mgq_dequantize_q4": (_int, [_vp, _sz, _sz, _vp]),
+    "mgq_dequantize_q8": (_int, [_vp, _sz, _sz, _vp]),
+    "mgq_shard_columns": (_int, [_int, _vp, _sz, _sz, _sz, _sz, _vp]),
+    "mgq_buffer_create": (_int, [_sz, ctypes.POINTER(_vp)]),
+    "mgq_buffer_destroy": (_int, [_vp]),
+    "mgq_buffer_upload": (_int, [_vp, _vp, _sz, _vp]),
+    "mgq_buffer_download": (_int, [_vp, _vp, _sz, _vp]),
+    "mgq_gemv": (_int, [_int, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
+    "mgq_gemm": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
+    "mgq_matmul": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
+    "mgq_matmul_host": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32]),
+    "mgq_graph_new": (_vp, []),
+    "mgq_graph_free": (None, [_vp]),
+    "mgq_graph_input": (_int, [_vp, ctypes.c_char_p, _szp, _sz]),
+    "mgq_graph_parameter": (_int, [_vp, ctypes.c_char_p, _szp, _sz]),
+    "mgq_graph_parameter_q4": (_int, [_vp, ctypes.c_char_p, _szp, _sz]),
+    "mgq_graph_parameter_q8": (_int, [_vp, ctypes.c_char_p, _szp, _sz]),
+    "mgq_graph_matmul": (_int, [_vp, _int, _int]),
+    "mgq_graph_add": (_int, [_vp, _int, _int]),
+    "mgq_graph_set_outputs": (_int, [_vp, ctypes.POINTER(_int), _sz]),
+    "mgq_build_inference_session": (_int, [_vp, ctypes.POINTER(_vp)]),
+    "mgq_session_free": (None, [_vp]),
+    "mgq_session_set_parameter": (_int, [_vp, ctypes.c_char_p, _vp, _sz]),
+    "mgq_session_upload_param": (_int, [_vp, ctypes.c_char_p, _vp, _sz]),
+    "mgq_session_set_input": (_int, [_vp, ctypes.c_char_p, _vp, _sz]),
+    "mgq_session_step": (_int, [_vp]),
+    "mgq_session_wait": (_int, [_vp]),
+    "mgq_session_read_output": (_int, [_vp, _vp, _sz]),
+    "mgq_session_read_output_by_index": (_int, [_vp, _sz, _vp, _sz]),
+    "mgq_session_num_dispatches": (_int, [_vp]),
+    "mgq_session_dispatch_info": (_int, [_vp, _sz, ctypes.POINTER(_int), ctypes.POINTER(_u32), ctypes.POINTER(_u32),
+                                         ctypes.POINTER(_int), ctypes.c_char_p, _sz]),
+    "mgq_session_launch_count": (ctypes.c_uint64, [_vp]),
+}
+
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def last_error() -> str:
+    return lib.mgq_last_error().decode()
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise MgqError(status, last_error())

@@ -1,0 +1,115 @@
+// C ABI entry points that touch the device: buffers, argument checking and kernel routing.
+#include <cuda_runtime.h>
+
+#include "mgq_internal.h"
+
+namespace mgq {
+
+int cuda_check(int cuda_err, const char *what, const char *file, int line)
+{
+    if (cuda_err == (int)cudaSuccess) return MGQ_OK;
+    return fail(MGQ_ERR_CUDA, "%s failed at %s:%d: %s", what, file, line,
+                cudaGetErrorString(static_cast<cudaError_t>(cuda_err)));
+}
+
+static int check_matmul_args(int fmt, const void *a, const void *w, const float *c, uint32_t m, uint32_t k, uint32_t n)
+{
+    if (!a || !w || !c) return fail(MGQ_ERR_NULL, "null operand pointer");
+    if (!is_quant(fmt)) return fail(MGQ_ERR_FORMAT, "weight format %d is not handled (only Q4=%d, Q8=%d)", fmt, MGQ_FMT_Q4, MGQ_FMT_Q8);
+    if (m == 0 || k == 0 || n == 0) return fail(MGQ_ERR_SHAPE, "empty matmul %ux%ux%u", m, k, n);
+    if (k % 32 != 0) return fail(MGQ_ERR_SHAPE, "K must be a multiple of 32 (quantization block), got %u", k);
+    if (reinterpret_cast<uintptr_t>(w) % 16 != 0) return fail(MGQ_ERR_ALIGN, "packed weight pointer must be 16-byte aligned");
+    return MGQ_OK;
+}
+
+}  // namespace mgq
+
+using namespace mgq;
+
+extern "C" {
+
+int mgq_buffer_create(size_t bytes, void **out_dev)
+{
+    if (!out_dev) return fail(MGQ_ERR_NULL, "null out pointer");
+    *out_dev = nullptr;
+    if (bytes == 0) return fail(MGQ_ERR_SHAPE, "zero-sized buffer");
+    void *p = nullptr;
+    MGQ_CUDA(cudaMalloc(&p, bytes));
+    const int rc = cuda_check((int)cudaMemset(p, 0, bytes), "cudaMemset", __FILE__, __LINE__);
+    if (rc != MGQ_OK) { cudaFree(p); return rc; }
+    *out_dev = p;
+    return MGQ_OK;
+}
+
+int mgq_buffer_destroy(void *dev)
+{
+    if (!dev) return MGQ_OK;
+    MGQ_CUDA(cudaFree(dev));
+    return MGQ_OK;
+}
+
+int mgq_buffer_upload(void *dev, const void *host, size_t bytes, void *stream)
+{
+    if (!dev || !host) return fail(MGQ_ERR_NULL, "null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    MGQ_CUDA(cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, s));
+    MGQ_CUDA(cudaStreamSynchronize(s));          // the reference's upload is synchronous
+    return MGQ_OK;
+}
+
+int mgq_buffer_download(const void *dev, void *host, size_t bytes, void *stream)
+{
+    if (!dev || !host) return fail(MGQ_ERR_NULL, "null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    MGQ_CUDA(cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, s));
+    MGQ_CUDA(cudaStreamSynchronize(s));
+    return MGQ_OK;
+}
+
+int mgq_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
+             uint32_t m, uint32_t k, uint32_t n, void *stream)
+{
+    if (int rc = check_matmul_args(fmt, x, w, y, m, k, n)) return rc;
+    if (m > MGQ_GEMV_MAX_M) return fail(MGQ_ERR_SHAPE, "gemv takes at most %d rows, got %u", MGQ_GEMV_MAX_M, m);
+    return launch_gemv(fmt, x, w, addend, y, m, k, n, stream);
+}
+
+int mgq_gemm(int fmt, const void *a, int a_dtype, const void *w, const float *addend, float *c,
+             uint32_t m, uint32_t k, uint32_t n, void *stream)
+{
+    if (int rc = check_matmul_args(fmt, a, w, c, m, k, n)) return rc;
+    if (a_dtype != MGQ_A_F32 && a_dtype != MGQ_A_BF16) return fail(MGQ_ERR_FORMAT, "activation dtype %d is not f32/bf16", a_dtype);
+    return launch_gemm(fmt, a, a_dtype, w, addend, c, m, k, n, stream);
+}
+
+int mgq_matmul(int fmt, const void *a, int a_dtype, const void *w, const float *addend, float *c,
+               uint32_t m, uint32_t k, uint32_t n, void *stream)
+{
+    if (a_dtype == MGQ_A_F32 && m <= MGQ_GEMV_MAX_M)
+        return mgq_gemv(fmt, static_cast<const float *>(a), w, addend, c, m, k, n, stream);
+    return mgq_gemm(fmt, a, a_dtype, w, addend, c, m, k, n, stream);
+}
+
+int mgq_matmul_host(int fmt, const void *a_host, int a_dtype, const void *w_dev, const float *addend_host,
+                    float *c_host, uint32_t m, uint32_t k, uint32_t n)
+{
+    if (int rc = check_matmul_args(fmt, a_host, w_dev, c_host, m, k, n)) return rc;
+    if (a_dtype != MGQ_A_F32 && a_dtype != MGQ_A_BF16) return fail(MGQ_ERR_FORMAT, "activation dtype %d is not f32/bf16", a_dtype);
+    const size_t a_bytes = (size_t)m * k * (a_dtype == MGQ_A_BF16 ? 2 : 4), c_bytes = (size_t)m * n * 4;
+    void *a_dev = nullptr, *c_dev = nullptr, *d_dev = nullptr;
+    int rc = MGQ_OK;
+    auto cleanup = [&] { cudaFree(a_dev); cudaFree(c_dev); cudaFree(d_dev); };
+    if ((rc = cuda_check((int)cudaMalloc(&a_dev, a_bytes), "cudaMalloc", __FILE__, __LINE__))) { cleanup(); return rc; }
+    if ((rc = cuda_check((int)cudaMalloc(&c_dev, c_bytes), "cudaMalloc", __FILE__, __LINE__))) { cleanup(); return rc; }
+    if (addend_host && (rc = cuda_check((int)cudaMalloc(&d_dev, c_bytes), "cudaMalloc", __FILE__, __LINE__))) { cleanup(); return rc; }
+    rc = cuda_check((int)cudaMemcpyAsync(a_dev, a_host, a_bytes, cudaMemcpyHostToDevice, 0), "H2D", __FILE__, __LINE__);
+    if (!rc && addend_host)
+        rc = cuda_check((int)cudaMemcpyAsync(d_dev, addend_host, c_bytes, cudaMemcpyHostToDevice, 0), "H2D", __FILE__, __LINE__);
+    if (!rc) rc = mgq_matmul(fmt, a_dev, a_dtype, w_dev, static_cast<const float *>(d_dev), static_cast<float *>(c_dev), m, k, n, nullptr);
+    if (!rc) rc = cuda_check((int)cudaMemcpyAsync(c_host, c_dev, c_bytes, cudaMemcpyDeviceToHost, 0), "D2H", __FILE__, __LINE__);
+    if (!rc) rc = cuda_check((int)cudaStreamSynchronize(0), "sync", __FILE__, __LINE__);
+    cleanup();
+    return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,508 @@
+// Dequantize-fused GEMV for Q4/Q8 weights on sm_100a:  y[m,n] = x[m,k] . dequant(W)[k,n] (+ addend).
+//
+// Stands in for meganeura's MatMulGemv / MatMulGemvAdd dispatches (src/compile.rs:1390-1406,
+// 1498-1509) with the weight semantics of dequant_q4 / dequant_q8 (src/codegen.rs:748-805).
+//
+// The kernel is HBM-bound and uses no tensor cores.  Design:
+//
+//  * In the reference layout all 32-element blocks of one output column are contiguous
+//    (block = n*(K/32) + k/32), so consecutive threads take consecutive blocks of the packed
+//    stream: thread t of a CTA owns block-in-column b = t % bpc of column (t / bpc) of the
+//    current group of `cpi` columns, and every iteration advances by cpi columns.  The CTA
+//    therefore sweeps the weight bytes linearly and every byte is read exactly once.
+//  * b is fixed per thread, so the 32 activations a thread needs stay in registers for the
+//    whole kernel (no shared-memory traffic for x in the inner loop).
+//  * Weights are brought in with cp.async into a multi-stage shared-memory ring, so many KB
+//    per SM are in flight without holding registers.  Q4: each thread copies its own 16
+//    nibble bytes + 4 header bytes (no barrier needed).  Q8: a 36-byte block is only 4-byte
+//    aligned, so each warp copies its 32 blocks (1152 contiguous bytes) as 16-byte pieces
+//    and lanes then read their block at a 36-byte stride (9 is odd: conflict-free).
+//  * Integer codes are turned into floats without conversion instructions: a masked code is
+//    reinterpreted as an f32 *subnormal* (code * 2^-149, times 16/256/4096 for codes taken in
+//    place from higher bit positions) and multiplied by an activation pre-scaled by the
+//    matching power of two, using packed two-wide f32 FMAs.  One logic op + half an FMA per
+//    weight.  Per-block scales are applied once per 32 products:
+//        Q4:  d * sum(x*nib) + m * sum(x)          Q8:  s * (sum(x*(q+128)) - 128*sum(x))
+//  * Column sums are finished through shared memory + warp shuffles in a fixed order that
+//    depends only on K, so a column's result does not depend on N or on its position in the
+//    grid (column shards reproduce the unsharded result bit for bit).
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+#include <vector>
+
+#include "mgq_internal.h"
+
+namespace mgq {
+namespace {
+
+constexpr int kRound = 4;                     // iterations per batched column reduction
+constexpr float kXScale = 0x1p64f;            // activations are pre-scaled by 2^64 (exact)
+constexpr float kUnscale = 0x1p85f;           // 2^(149-64): undoes subnormal * pre-scale
+constexpr uint32_t kQ8WarpStage = 1168;       // 32 blocks * 36 B + up to 12 B lead-in, 16-B multiple
+
+struct GemvParams {
+    const float *x;
+    const uint8_t *w;
+    const float *addend;
+    float *y;
+    uint32_t k, n, bpc;
+    uint32_t cpi;          // columns per iteration
+    uint32_t active;       // cpi * bpc threads carry a block
+    uint32_t red_shift;    // log2(lanes that finish one column sum)
+    uint32_t total_iters;  // ceil(n / cpi)
+    unsigned long long num_blocks;
+};
+
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem)
+{
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void *smem, const void *gmem)
+{
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 subn2(uint32_t a, uint32_t b) { return make_float2(__uint_as_float(a), __uint_as_float(b)); }
+
+// Loads the 32 activations of block b for MT rows, keeps their plain sum, and pre-scales them.
+// STEP is the bit distance between two codes that are read in place (4 for Q4, 8 for Q8);
+// PER is how many codes are taken from one 16-bit half (4 for Q4, 2 for Q8).
+template <int MT, int STEP, int PER>
+__device__ __forceinline__ void load_x(const GemvParams &p, uint32_t b, float2 (&xs)[MT][16], float (&xsum)[MT])
+{
+#pragma unroll
+    for (int r = 0; r < MT; r++) {
+        const float4 *xp = reinterpret_cast<const float4 *>(p.x + (size_t)r * p.k + 32u * b);
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float4 v = __ldg(xp + j);
+            s0 += v.x + v.y;
+            s1 += v.z + v.w;
+            const float e[4] = {v.x, v.y, v.z, v.w};
+            float o[4];
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const int pos = (4 * j + c) % PER;                    // position inside its 16-bit half
+                o[c] = e[c] * (kXScale / (float)(1u << (STEP * pos)));
+            }
+            xs[r][2 * j] = make_float2(o[0], o[1]);
+            xs[r][2 * j + 1] = make_float2(o[2], o[3]);
+        }
+        xsum[r] = s0 + s1;
+    }
+}
+
+// Finishes kRound*cpi column sums from per-thread partials and writes y.
+template <int MT>
+__device__ __forceinline__ void reduce_store(const GemvParams &p, float *red, const float (&part)[MT][kRound],
+                                             uint32_t it_base, uint32_t it_end)
+{
+    const uint32_t T = blockDim.x, t = threadIdx.x;
+#pragma unroll
+    for (int r = 0; r < MT; r++)
+#pragma unroll
+        for (int u = 0; u < kRound; u++) red[(r * kRound + u) * T + t] = part[r][u];
+    __syncthreads();
+    const uint32_t R = 1u << p.red_shift;
+    const uint32_t nslots = kRound * p.cpi;
+    for (uint32_t base = 0; base < (nslots << p.red_shift); base += T) {
+        const uint32_t idx = base + t;
+        const uint32_t slot = idx >> p.red_shift, li = idx & (R - 1);
+        const bool valid = slot < nslots;
+        const uint32_t u = valid ? slot / p.cpi : 0, cs = valid ? slot % p.cpi : 0;
+#pragma unroll
+        for (int r = 0; r < MT; r++) {
+            float s = 0.f;
+            if (valid) {
+                const float *src = red + (r * kRound + u) * T + cs * p.bpc;
+                for (uint32_t j = li; j < p.bpc; j += R) s += src[j];
+            }
+            for (uint32_t o = R >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            const uint32_t it = it_base + u;
+            const uint32_t col = it * p.cpi + cs;
+            if (valid && li == 0 && it < it_end && col < p.n) {
+                const size_t o = (size_t)r * p.n + col;
+                p.y[o] = p.addend ? s + p.addend[o] : s;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------ Q4
+
+template <int MT, int STAGES, int TMAX>
+__global__ void __launch_bounds__(TMAX) gemv_q4_kernel(const GemvParams p)
+{
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t T = blockDim.x, t = threadIdx.x;
+    uint4 *s_nib = reinterpret_cast<uint4 *>(smem);                                  // [STAGES][T]
+    uint32_t *s_hdr = reinterpret_cast<uint32_t *>(smem + (size_t)STAGES * T * 16);  // [STAGES][T]
+    float *s_red = reinterpret_cast<float *>(smem + (size_t)STAGES * T * 20);        // [2][MT][kRound][T]
+
+    const uint32_t it0 = (uint32_t)((unsigned long long)blockIdx.x * p.total_iters / gridDim.x);
+    const uint32_t it1 = (uint32_t)((unsigned long long)(blockIdx.x + 1) * p.total_iters / gridDim.x);
+    const uint32_t n_it = it1 - it0;
+    const bool has_block = t < p.active;
+    const uint32_t b = t % p.bpc, csub = t / p.bpc;
+    const uint32_t *g_hdr = reinterpret_cast<const uint32_t *>(p.w);
+    const uint4 *g_nib = reinterpret_cast<const uint4 *>(p.w + p.num_blocks * 4);
+
+    auto prefetch = [&](uint32_t i) {
+        if (i < n_it && has_block && (it0 + i) * p.cpi + csub < p.n) {
+            const unsigned long long g = (unsigned long long)(it0 + i) * p.active + t;   // = col*bpc + b
+            cp_async16(&s_nib[(i % STAGES) * T + t], &g_nib[g]);
+            cp_async4(&s_hdr[(i % STAGES) * T + t], &g_hdr[g]);
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; s++) prefetch(s);      // weights first: they depend on nothing
+
+    float2 xs[MT][16];
+    float xsum[MT];
+    load_x<MT, 4, 4>(p, b, xs, xsum);
+
+    const uint32_t rounds = (n_it + kRound - 1) / kRound;
+    for (uint32_t round = 0; round < rounds; round++) {
+        float part[MT][kRound];
+#pragma unroll
+        for (int u = 0; u < kRound; u++) {
+            const uint32_t i = round * kRound + u;
+            prefetch(i + STAGES - 1);
+            cp_async_wait<STAGES - 1>();
+#pragma unroll
+            for (int r = 0; r < MT; r++) part[r][u] = 0.f;
+            if (i < n_it && has_block && (it0 + i) * p.cpi + csub < p.n) {
+                const uint4 q = s_nib[(i % STAGES) * T + t];
+                const uint32_t h = s_hdr[(i % STAGES) * T + t];
+                const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&h));   // (d, m), IEEE
+                const uint32_t wv[4] = {q.x, q.y, q.z, q.w};
+                float2 a0[MT], a1[MT];
+#pragma unroll
+                for (int r = 0; r < MT; r++) a0[r] = a1[r] = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint32_t lo = wv[j], hi = wv[j] >> 16;
+                    const float2 v0 = subn2(lo & 0xFu, lo & 0xF0u), v1 = subn2(lo & 0xF00u, lo & 0xF000u);
+                    const float2 v2 = subn2(hi & 0xFu, hi & 0xF0u), v3 = subn2(hi & 0xF00u, hi & 0xF000u);
+#pragma unroll
+                    for (int r = 0; r < MT; r++) {
+                        a0[r] = fma2(v0, xs[r][4 * j + 0], a0[r]);
+                        a1[r] = fma2(v1, xs[r][4 * j + 1], a1[r]);
+                        a0[r] = fma2(v2, xs[r][4 * j + 2], a0[r]);
+                        a1[r] = fma2(v3, xs[r][4 * j + 3], a1[r]);
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < MT; r++) {
+                    const float dot = (a0[r].x + a0[r].y) + (a1[r].x + a1[r].y);
+                    part[r][u] = fmaf(dm.x * kUnscale, dot, dm.y * xsum[r]);
+                }
+            }
+        }
+        reduce_store<MT>(p, s_red + (size_t)(round & 1) * MT * kRound * T, part, it0 + round * kRound, it1);
+    }
+    cp_async_wait<0>();
+}
+
+// ------------------------------------------------------------------------------------ Q8
+
+template <int MT, int STAGES, int TMAX>
+__global__ void __launch_bounds__(TMAX) gemv_q8_kernel(const GemvParams p)
+{
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t T = blockDim.x, t = threadIdx.x, lane = t & 31u, warp = t >> 5, W = T >> 5;
+    uint8_t *s_w = smem + (size_t)warp * STAGES * kQ8WarpStage;                        // this warp's ring
+    float *s_red = reinterpret_cast<float *>(smem + (size_t)W * STAGES * kQ8WarpStage);  // [2][MT][kRound][T]
+
+    const uint32_t it0 = (uint32_t)((unsigned long long)blockIdx.x * p.total_iters / gridDim.x);
+    const uint32_t it1 = (uint32_t)((unsigned long long)(blockIdx.x + 1) * p.total_iters / gridDim.x);
+    const uint32_t n_it = it1 - it0;
+    const uint32_t b = t % p.bpc;
+
+    // Blocks this warp owns in iteration `it`: [first, first+cnt) of the packed stream.
+    auto warp_span = [&](uint32_t it, unsigned long long &first, uint32_t &cnt) {
+        const uint32_t cols = min(p.cpi, p.n - it * p.cpi);
+        const uint32_t live = cols * p.bpc;
+        const uint32_t w0 = warp * 32u;
+        cnt = live > w0 ? min(32u, live - w0) : 0u;
+        first = (unsigned long long)it * p.active + w0;
+    };
+    auto prefetch = [&](uint32_t i) {
+        if (i < n_it) {
+            unsigned long long first;
+            uint32_t cnt;
+            warp_span(it0 + i, first, cnt);
+            if (cnt) {
+                const unsigned long long byte0 = first * 36ull;
+                const uint32_t lead = (uint32_t)(byte0 & 15ull);
+                const uint8_t *src = p.w + (byte0 - lead);
+                const uint32_t n16 = (lead + cnt * 36u + 15u) >> 4;      // stays inside the buffer: its size is a 16-B multiple
+                uint8_t *dst = s_w + (i % STAGES) * kQ8WarpStage;
+                for (uint32_t c = lane; c < n16; c += 32u) cp_async16(dst + 16u * c, src + 16ull * c);
+            }
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; s++) prefetch(s);
+
+    float2 xs[MT][16];
+    float xsum[MT];
+    load_x<MT, 8, 2>(p, b, xs, xsum);
+
+    const uint32_t rounds = (n_it + kRound - 1) / kRound;
+    for (uint32_t round = 0; round < rounds; round++) {
+        float part[MT][kRound];
+#pragma unroll
+        for (int u = 0; u < kRound; u++) {
+            const uint32_t i = round * kRound + u;
+            __syncwarp();                                   // every lane is done reading the stage refilled next
+            prefetch(i + STAGES - 1);
+            cp_async_wait<STAGES - 1>();
+            __syncwarp();                                   // other lanes' copies for stage i are visible
+#pragma unroll
+            for (int r = 0; r < MT; r++) part[r][u] = 0.f;
+            if (i < n_it) {
+                unsigned long long first;
+                uint32_t cnt;
+                warp_span(it0 + i, first, cnt);
+                if (lane < cnt) {
+                    const uint32_t lead = (uint32_t)((first * 36ull) & 15ull);
+                    const uint32_t *bp = reinterpret_cast<const uint32_t *>(s_w + (i % STAGES) * kQ8WarpStage + lead + 36u * lane);
+                    const uint32_t sw = bp[0];
+                    const float scale = __half2float(__ushort_as_half((unsigned short)(sw & 0xFFFFu)));
+                    float2 a0[MT], a1[MT];
+#pragma unroll
+                    for (int r = 0; r < MT; r++) a0[r] = a1[r] = make_float2(0.f, 0.f);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const uint32_t lo = bp[1 + j], hi = lo >> 16;
+                        // (q ^ 0x80) is q + 128 as an unsigned byte
+                        const float2 v0 = subn2((lo ^ 0x80u) & 0xFFu, (lo ^ 0x8000u) & 0xFF00u);
+                        const float2 v1 = subn2((hi ^ 0x80u) & 0xFFu, (hi ^ 0x8000u) & 0xFF00u);
+#pragma unroll
+                        for (int r = 0; r < MT; r++) {
+                            a0[r] = fma2(v0, xs[r][2 * j + 0], a0[r]);
+                            a1[r] = fma2(v1, xs[r][2 * j + 1], a1[r]);
+                        }
+                    }
+#pragma unroll
+                    for (int r = 0; r < MT; r++) {
+                        const float dot = (a0[r].x + a0[r].y) + (a1[r].x + a1[r].y);
+                        part[r][u] = fmaf(scale * kUnscale, dot, -128.f * scale * xsum[r]);
+                    }
+                }
+            }
+        }
+        reduce_store<MT>(p, s_red + (size_t)(round & 1) * MT * kRound * T, part, it0 + round * kRound, it1);
+    }
+    cp_async_wait<0>();
+}
+
+// ------------------------------------------------------------------------------ generic path
+
+// Any K (multiple of 32), any N, any alignment of the nibble region: one warp per column, plain
+// 4-byte loads.  Used only for shapes the streaming kernels do not take (K > 32768, or a packed
+// buffer whose size is not a multiple of 16 bytes).
+template <int FMT>
+__global__ void __launch_bounds__(256) gemv_generic_kernel(const GemvParams p, uint32_t m)
+{
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t col = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (col >= p.n) return;
+    const uint32_t *w32 = reinterpret_cast<const uint32_t *>(p.w);
+    for (uint32_t r = 0; r < m; r++) {
+        const float *x = p.x + (size_t)r * p.k;
+        float acc = 0.f;
+        for (uint32_t b = lane; b < p.bpc; b += 32u) {
+            const unsigned long long g = (unsigned long long)col * p.bpc + b;
+            float dot = 0.f, xsum = 0.f;
+            if (FMT == MGQ_FMT_Q4) {
+                const uint32_t h = w32[g];
+                const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&h));
+                const uint32_t *nb = w32 + p.num_blocks + g * 4;
+                for (int j = 0; j < 4; j++) {
+                    const uint32_t wv = nb[j];
+                    for (int e = 0; e < 8; e++) {
+                        const float xv = x[32u * b + 8 * j + e];
+                        dot = fmaf((float)((wv >> (4 * e)) & 0xFu), xv, dot);
+                        xsum += xv;
+                    }
+                }
+                acc += fmaf(dm.x, dot, dm.y * xsum);
+            } else {
+                const uint32_t *bp = w32 + g * 9;
+                const float scale = __half2float(__ushort_as_half((unsigned short)(bp[0] & 0xFFFFu)));
+                for (int j = 0; j < 8; j++) {
+                    const uint32_t wv = bp[1 + j];
+                    for (int e = 0; e < 4; e++)
+                        dot = fmaf((float)(int)(signed char)((wv >> (8 * e)) & 0xFFu), x[32u * b + 4 * j + e], dot);
+                }
+                acc += scale * dot;
+            }
+        }
+        for (uint32_t o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) {
+            const size_t o = (size_t)r * p.n + col;
+            p.y[o] = p.addend ? acc + p.addend[o] : acc;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------ launch logic
+
+struct Config {
+    uint32_t threads, cpi, red_shift;
+    int stages;
+};
+
+// Depends on K only, so that a column's summation order is the same for every N.
+Config choose_config(uint32_t bpc)
+{
+    Config c{};
+    if (bpc <= 256) {
+        uint32_t best_t = 128;
+        double best_u = 0.0;
+        for (uint32_t t = 128; t <= 256; t += 32) {
+            if (t < bpc) continue;
+            const double util = (double)((t / bpc) * bpc) / t;
+            if (util > best_u + 1e-9) { best_u = util; best_t = t; }
+        }
+        c.threads = best_t;
+    } else {
+        c.threads = (bpc + 31u) & ~31u;
+    }
+    c.cpi = c.threads / bpc;
+    c.stages = c.threads <= 256 ? 8 : 4;
+    uint32_t lanes = bpc / 4;                       // about four partials per finishing lane
+    c.red_shift = 0;
+    while ((2u << c.red_shift) <= lanes && c.red_shift < 5) c.red_shift++;
+    return c;
+}
+
+size_t smem_bytes(int fmt, const Config &c, int mt)
+{
+    const size_t red = (size_t)2 * mt * kRound * c.threads * sizeof(float);
+    if (fmt == MGQ_FMT_Q4) return (size_t)c.stages * c.threads * 20 + red;
+    return (size_t)(c.threads / 32) * c.stages * kQ8WarpStage + red;
+}
+
+using KernelFn = void (*)(const GemvParams);
+
+KernelFn pick_kernel(int fmt, int mt, const Config &c)
+{
+    if (fmt == MGQ_FMT_Q4) {
+        if (c.threads <= 256) return mt == 2 ? gemv_q4_kernel<2, 8, 256> : gemv_q4_kernel<1, 8, 256>;
+        if (c.threads <= 512) return mt == 2 ? gemv_q4_kernel<2, 4, 512> : gemv_q4_kernel<1, 4, 512>;
+        return mt == 1 ? gemv_q4_kernel<1, 4, 1024> : nullptr;
+    }
+    if (c.threads <= 256) return mt == 2 ? gemv_q8_kernel<2, 8, 256> : gemv_q8_kernel<1, 8, 256>;
+    if (c.threads <= 512) return mt == 2 ? gemv_q8_kernel<2, 4, 512> : gemv_q8_kernel<1, 4, 512>;
+    return mt == 1 ? gemv_q8_kernel<1, 4, 1024> : nullptr;
+}
+
+struct DeviceInfo {
+    int sms = 0;
+    bool ok = false;
+};
+
+int device_info(DeviceInfo &out)
+{
+    static std::mutex mu;
+    static DeviceInfo cache[64];
+    int dev = 0;
+    MGQ_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 0 || dev >= 64) return fail(MGQ_ERR_CUDA, "device index %d out of range", dev);
+    if (!cache[dev].ok) {
+        MGQ_CUDA(cudaDeviceGetAttribute(&cache[dev].sms, cudaDevAttrMultiProcessorCount, dev));
+        cache[dev].ok = true;
+    }
+    out = cache[dev];
+    return MGQ_OK;
+}
+
+// Opts the kernel into its dynamic shared memory size and returns resident CTAs per SM.
+// Both calls cost microseconds, so the answer is remembered per (device, kernel, shape).
+int kernel_occupancy(KernelFn fn, uint32_t threads, size_t smem, int &occ)
+{
+    struct Entry { int dev; KernelFn fn; uint32_t threads; size_t smem; int occ; };
+    static std::mutex mu;
+    static std::vector<Entry> seen;
+    int dev = 0;
+    MGQ_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    for (const Entry &e : seen)
+        if (e.dev == dev && e.fn == fn && e.threads == threads && e.smem == smem) { occ = e.occ; return MGQ_OK; }
+    MGQ_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MGQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, (int)threads, smem));
+    if (occ < 1) return fail(MGQ_ERR_CUDA, "GEMV kernel does not fit on an SM (threads=%u smem=%zu)", threads, smem);
+    seen.push_back({dev, fn, threads, smem, occ});
+    return MGQ_OK;
+}
+
+}  // namespace
+
+int launch_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
+                uint32_t m, uint32_t k, uint32_t n, void *stream_v)
+{
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const uint32_t bpc = k / 32;
+    GemvParams p{};
+    p.k = k; p.n = n; p.bpc = bpc;
+    p.num_blocks = (unsigned long long)bpc * n;
+    p.w = static_cast<const uint8_t *>(w);
+
+    const bool streamable = bpc <= 1024 && (p.num_blocks % 4 == 0) &&
+                            (reinterpret_cast<uintptr_t>(x) % 16 == 0);
+    if (!streamable) {
+        p.x = x; p.addend = addend; p.y = y;
+        const uint32_t warps = 8, grid = (n + warps - 1) / warps;
+        if (fmt == MGQ_FMT_Q4) gemv_generic_kernel<MGQ_FMT_Q4><<<grid, warps * 32, 0, stream>>>(p, m);
+        else                   gemv_generic_kernel<MGQ_FMT_Q8><<<grid, warps * 32, 0, stream>>>(p, m);
+        MGQ_CUDA(cudaGetLastError());
+        return MGQ_OK;
+    }
+
+    const Config cfg = choose_config(bpc);
+    p.cpi = cfg.cpi;
+    p.active = cfg.cpi * bpc;
+    p.red_shift = cfg.red_shift;
+    p.total_iters = (n + cfg.cpi - 1) / cfg.cpi;
+    DeviceInfo di;
+    if (int rc = device_info(di)) return rc;
+
+    // Rows are processed two at a time (their activations live in registers); more rows re-read W.
+    for (uint32_t r0 = 0; r0 < m;) {
+        int mt = (m - r0 >= 2 && cfg.threads <= 512) ? 2 : 1;
+        KernelFn fn = pick_kernel(fmt, mt, cfg);
+        if (!fn) return fail(MGQ_ERR_SHAPE, "no GEMV kernel for K=%u", k);
+        const size_t smem = smem_bytes(fmt, cfg, mt);
+        int occ = 0;
+        if (int rc = kernel_occupancy(fn, cfg.threads, smem, occ)) return rc;
+        uint32_t grid = (uint32_t)di.sms * (uint32_t)occ;
+        if (grid > p.total_iters) grid = p.total_iters;
+        p.x = x + (size_t)r0 * k;
+        p.addend = addend ? addend + (size_t)r0 * n : nullptr;
+        p.y = y + (size_t)r0 * n;
+        fn<<<grid, cfg.threads, smem, stream>>>(p);
+        MGQ_CUDA(cudaGetLastError());
+        r0 += mt;
+    }
+    return MGQ_OK;
+}
+
+}  // namespace mgq

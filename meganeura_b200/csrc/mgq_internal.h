@@ -1,0 +1,31 @@
+// Internal helpers shared by the libmgq translation units (not part of the C ABI).
+#pragma once
+#include <cstdarg>
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/mgq.h"
+
+namespace mgq {
+
+// Records a printf-style message for mgq_last_error() on this thread and returns `code`.
+int fail(int code, const char *fmt, ...);
+
+// cudaError_t -> status; records file/line and the CUDA error string on failure.
+int cuda_check(int cuda_err, const char *what, const char *file, int line);
+
+inline bool is_quant(int fmt) { return fmt == MGQ_FMT_Q4 || fmt == MGQ_FMT_Q8; }
+
+// Launchers implemented in the .cu files (all pointers are device pointers).
+int launch_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
+                uint32_t m, uint32_t k, uint32_t n, void *stream);
+int launch_gemm(int fmt, const void *a, int a_dtype, const void *w, const float *addend, float *c,
+                uint32_t m, uint32_t k, uint32_t n, void *stream);
+
+}  // namespace mgq
+
+#define MGQ_CUDA(expr)                                                                 \
+    do {                                                                               \
+        int _rc = ::mgq::cuda_check((int)(expr), #expr, __FILE__, __LINE__);           \
+        if (_rc != MGQ_OK) return _rc;                                                 \
+    } while (0)

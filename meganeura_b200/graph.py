@@ -1,0 +1,146 @@
+"""Graph / build_inference_session / Session with meganeura's names, over the C ABI.
+
+The graph, the plan and the session live in C++ (csrc/mgq_session.cpp); this module only holds
+handles.  Method names and argument meaning follow meganeura (src/graph.rs:714-795,
+src/train.rs:380-389, src/runtime.rs:2327-2345, 2612-2643, 2786-2791, 2835-2959) so tests read
+like the reference's (tests/gemv_parity.rs, tests/gpu_smoke.rs:2680-2771).
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from enum import IntEnum
+
+import numpy as np
+
+from ._lib import check, last_error, lib, MgqError
+
+
+class ShaderEntry(IntEnum):
+    MatMul = 0
+    FusedMatMulAdd = 1
+    MatMulGemv = 2
+    MatMulGemvAdd = 3
+    Add = 4
+
+
+class WeightFormat(IntEnum):
+    F32 = 0
+    F16 = 1
+    Q4 = 2
+    Q8 = 3
+
+
+@dataclass
+class Dispatch:
+    shader: ShaderEntry
+    workgroups: tuple
+    params: tuple
+    weight_format: WeightFormat
+    label: str
+
+
+@dataclass
+class ExecutionPlan:
+    dispatches: list
+
+
+def _shape(shape):
+    arr = (ctypes.c_size_t * len(shape))(*[int(s) for s in shape])
+    return arr, len(shape)
+
+
+def _node(rc: int) -> int:
+    if rc < 0:
+        raise MgqError(-rc, last_error())
+    return rc
+
+
+class Graph:
+    def __init__(self):
+        self._h = lib.mgq_graph_new()
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib.mgq_graph_free(self._h)
+            self._h = None
+
+    def input(self, name: str, shape) -> int:
+        return _node(lib.mgq_graph_input(self._h, name.encode(), *_shape(shape)))
+
+    def parameter(self, name: str, shape) -> int:
+        return _node(lib.mgq_graph_parameter(self._h, name.encode(), *_shape(shape)))
+
+    def parameter_q4(self, name: str, shape) -> int:
+        return _node(lib.mgq_graph_parameter_q4(self._h, name.encode(), *_shape(shape)))
+
+    def parameter_q8(self, name: str, shape) -> int:
+        return _node(lib.mgq_graph_parameter_q8(self._h, name.encode(), *_shape(shape)))
+
+    def matmul(self, a: int, b: int) -> int:
+        return _node(lib.mgq_graph_matmul(self._h, a, b))
+
+    def add(self, a: int, b: int) -> int:
+        return _node(lib.mgq_graph_add(self._h, a, b))
+
+    def set_outputs(self, ids) -> None:
+        arr = (ctypes.c_int * len(ids))(*ids)
+        check(lib.mgq_graph_set_outputs(self._h, arr, len(ids)))
+
+
+class Session:
+    def __init__(self, handle):
+        self._h = handle
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib.mgq_session_free(self._h)
+            self._h = None
+
+    def set_parameter(self, name: str, data) -> None:
+        data = np.ascontiguousarray(data, dtype=np.float32).reshape(-1)
+        check(lib.mgq_session_set_parameter(self._h, name.encode(), data.ctypes.data, data.size))
+
+    def upload_param(self, name: str, raw) -> None:
+        raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+        check(lib.mgq_session_upload_param(self._h, name.encode(), raw.ctypes.data, raw.size))
+
+    def set_input(self, name: str, data) -> None:
+        data = np.ascontiguousarray(data, dtype=np.float32).reshape(-1)
+        check(lib.mgq_session_set_input(self._h, name.encode(), data.ctypes.data, data.size))
+
+    def step(self) -> None:
+        check(lib.mgq_session_step(self._h))
+
+    def wait(self) -> None:
+        check(lib.mgq_session_wait(self._h))
+
+    def read_output(self, length: int) -> np.ndarray:
+        out = np.empty(length, dtype=np.float32)
+        check(lib.mgq_session_read_output(self._h, out.ctypes.data, length))
+        return out
+
+    def read_output_by_index(self, index: int, length: int) -> np.ndarray:
+        out = np.empty(length, dtype=np.float32)
+        check(lib.mgq_session_read_output_by_index(self._h, index, out.ctypes.data, length))
+        return out
+
+    def plan(self) -> ExecutionPlan:
+        count = lib.mgq_session_num_dispatches(self._h)
+        dispatches = []
+        for i in range(count):
+            shader, wf = ctypes.c_int(), ctypes.c_int()
+            wg, pr = (ctypes.c_uint32 * 3)(), (ctypes.c_uint32 * 4)()
+            label = ctypes.create_string_buffer(128)
+            check(lib.mgq_session_dispatch_info(self._h, i, ctypes.byref(shader), wg, pr, ctypes.byref(wf), label, 128))
+            dispatches.append(Dispatch(ShaderEntry(shader.value), tuple(wg), tuple(pr), WeightFormat(wf.value), label.value.decode()))
+        return ExecutionPlan(dispatches)
+
+    def launch_count(self) -> int:
+        return int(lib.mgq_session_launch_count(self._h))
+
+
+def build_inference_session(graph: Graph) -> Session:
+    handle = ctypes.c_void_p()
+    check(lib.mgq_build_inference_session(graph._h, ctypes.byref(handle)))
+    return Session(handle)

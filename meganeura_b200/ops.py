@@ -1,0 +1,94 @@
+"""Array-level entry points over the C ABI (numpy for host data, torch for device data).
+
+These are thin argument marshallers: every computation happens in libmgq.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from . import _lib
+from ._lib import A_BF16, A_F32, FMT_Q4, FMT_Q8, check, lib
+
+
+def packed_bytes(fmt: int, k: int, n: int) -> int:
+    return int(lib.mgq_packed_bytes(fmt, k, n))
+
+
+def quantize(fmt: int, w: np.ndarray) -> np.ndarray:
+    """Host quantizer: row-major [K,N] f32 -> packed bytes (quantize_q4_0 / quantize_q8_0)."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    if w.ndim != 2:
+        raise ValueError("weights must be 2-D [K, N]")
+    k, n = w.shape
+    out = np.empty(packed_bytes(fmt, k, n) if k % 32 == 0 else 1, dtype=np.uint8)
+    fn = lib.mgq_quantize_q4 if fmt == FMT_Q4 else lib.mgq_quantize_q8
+    check(fn(w.ctypes.data, k, n, out.ctypes.data))
+    return out
+
+
+def dequantize(fmt: int, packed: np.ndarray, k: int, n: int) -> np.ndarray:
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    out = np.empty((k, n), dtype=np.float32)
+    fn = lib.mgq_dequantize_q4 if fmt == FMT_Q4 else lib.mgq_dequantize_q8
+    check(fn(packed.ctypes.data, k, n, out.ctypes.data))
+    return out
+
+
+def shard_columns(fmt: int, packed: np.ndarray, k: int, n: int, n0: int, n1: int) -> np.ndarray:
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    out = np.empty(packed_bytes(fmt, k, max(n1 - n0, 0)) or 1, dtype=np.uint8)
+    check(lib.mgq_shard_columns(fmt, packed.ctypes.data, k, n, n0, n1, out.ctypes.data))
+    return out
+
+
+def _stream_ptr(stream=None):
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return s.cuda_stream
+
+
+def matmul(fmt: int, a, w, k: int, n: int, addend=None, out=None, stream=None, route: str = "auto"):
+    """c = a . dequant(w) (+ addend) on torch CUDA tensors.
+
+    a: [m,k] float32 or bfloat16; w: uint8 tensor holding the packed weight; returns float32 [m,n].
+    route: "auto" (mgq_matmul), "gemv" (mgq_gemv) or "gemm" (mgq_gemm).
+    """
+    import torch
+    if not (a.is_cuda and w.is_cuda):
+        raise ValueError("matmul takes CUDA tensors; the library has no CPU path")
+    a2 = a.reshape(-1, k)
+    if not a2.is_contiguous():
+        a2 = a2.contiguous()
+    m = a2.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float32, device=a.device)
+    a_dtype = A_BF16 if a2.dtype == torch.bfloat16 else A_F32
+    if a2.dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError("activations must be float32 or bfloat16")
+    add_p = addend.data_ptr() if addend is not None else None
+    sp = _stream_ptr(stream)
+    if route == "gemv":
+        check(lib.mgq_gemv(fmt, a2.data_ptr(), w.data_ptr(), add_p, out.data_ptr(), m, k, n, sp))
+    elif route == "gemm":
+        check(lib.mgq_gemm(fmt, a2.data_ptr(), a_dtype, w.data_ptr(), add_p, out.data_ptr(), m, k, n, sp))
+    else:
+        check(lib.mgq_matmul(fmt, a2.data_ptr(), a_dtype, w.data_ptr(), add_p, out.data_ptr(), m, k, n, sp))
+    return out
+
+
+def matmul_host(fmt: int, a: np.ndarray, w_dev_ptr: int, k: int, n: int, addend: np.ndarray | None = None) -> np.ndarray:
+    """Host activations in, host result out, device-resident weight (mgq_matmul_host)."""
+    a = np.ascontiguousarray(a, dtype=np.float32).reshape(-1, k)
+    m = a.shape[0]
+    out = np.empty((m, n), dtype=np.float32)
+    add_p = None
+    if addend is not None:
+        addend = np.ascontiguousarray(addend, dtype=np.float32)
+        add_p = addend.ctypes.data
+    check(lib.mgq_matmul_host(fmt, a.ctypes.data, A_F32, w_dev_ptr, add_p, out.ctypes.data, m, k, n))
+    return out
+
+
+__all__ = ["packed_bytes", "quantize", "dequantize", "shard_columns", "matmul", "matmul_host",
+           "FMT_Q4", "FMT_Q8", "A_F32", "A_BF16"]
+_ = _lib

@@ -37,10 +37,9 @@
 namespace mgq {
 namespace {
 
-constexpr int kRound = 4;                     // iterations per batched column reduction
 constexpr float kXScale = 0x1p64f;            // activations are pre-scaled by 2^64 (exact)
 constexpr float kUnscale = 0x1p85f;           // 2^(149-64): undoes subnormal * pre-scale
-constexpr uint32_t kQ8WarpStage = 1168;       // 32 blocks * 36 B + up to 12 B lead-in, 16-B multiple
+constexpr uint32_t kQ8WarpStage = 1152;       // 32 blocks * 36 B per warp and stage
 
 struct GemvParams {
     const float *x;
@@ -49,9 +48,10 @@ struct GemvParams {
     float *y;
     uint32_t k, n, bpc;
     uint32_t cpi;          // columns per iteration
-    uint32_t active;       // cpi * bpc threads carry a block
-    uint32_t red_shift;    // log2(lanes that finish one column sum)
+    uint32_t active;       // cpi * bpc threads carry a block (a multiple of 4)
     uint32_t total_iters;  // ceil(n / cpi)
+    uint32_t red_shift;    // log2(lanes that finish one column sum)
+    uint32_t red_chunk;    // partials summed by each finishing lane = ceil(bpc / lanes)
     unsigned long long num_blocks;
 };
 
@@ -104,38 +104,112 @@ __device__ __forceinline__ void load_x(const GemvParams &p, uint32_t b, float2 (
     }
 }
 
-// Finishes kRound*cpi column sums from per-thread partials and writes y.
+// One 32-element block: sum over the block of x[i] * code[i] (times 2^-85), MT rows at once.
 template <int MT>
-__device__ __forceinline__ void reduce_store(const GemvParams &p, float *red, const float (&part)[MT][kRound],
-                                             uint32_t it_base, uint32_t it_end)
+__device__ __forceinline__ void dot_q4(const uint4 &q, const float2 (&xs)[MT][16], float (&dot)[MT])
+{
+    const uint32_t wv[4] = {q.x, q.y, q.z, q.w};
+    float2 a0[MT], a1[MT];
+#pragma unroll
+    for (int r = 0; r < MT; r++) a0[r] = a1[r] = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const uint32_t lo = wv[j], hi = wv[j] >> 16;
+        const float2 v0 = subn2(lo & 0xFu, lo & 0xF0u), v1 = subn2(lo & 0xF00u, lo & 0xF000u);
+        const float2 v2 = subn2(hi & 0xFu, hi & 0xF0u), v3 = subn2(hi & 0xF00u, hi & 0xF000u);
+#pragma unroll
+        for (int r = 0; r < MT; r++) {
+            a0[r] = fma2(v0, xs[r][4 * j + 0], a0[r]);
+            a1[r] = fma2(v1, xs[r][4 * j + 1], a1[r]);
+            a0[r] = fma2(v2, xs[r][4 * j + 2], a0[r]);
+            a1[r] = fma2(v3, xs[r][4 * j + 3], a1[r]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < MT; r++) dot[r] = (a0[r].x + a0[r].y) + (a1[r].x + a1[r].y);
+}
+
+// bp points at the 8 code words of a Q8 block; codes are read as (q + 128), an unsigned byte.
+template <int MT>
+__device__ __forceinline__ void dot_q8(const uint32_t *bp, const float2 (&xs)[MT][16], float (&dot)[MT])
+{
+    float2 a0[MT], a1[MT];
+#pragma unroll
+    for (int r = 0; r < MT; r++) a0[r] = a1[r] = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const uint32_t lo = bp[j] ^ 0x80808080u, hi = lo >> 16;
+        const float2 v0 = subn2(lo & 0xFFu, lo & 0xFF00u);
+        const float2 v1 = subn2(hi & 0xFFu, hi & 0xFF00u);
+#pragma unroll
+        for (int r = 0; r < MT; r++) {
+            a0[r] = fma2(v0, xs[r][2 * j + 0], a0[r]);
+            a1[r] = fma2(v1, xs[r][2 * j + 1], a1[r]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < MT; r++) dot[r] = (a0[r].x + a0[r].y) + (a1[r].x + a1[r].y);
+}
+
+// Which column sum a thread finishes after each round; the same for every round, so it is
+// worked out once.  A round holds ROUND*cpi columns; each is finished by 2^red_shift
+// neighbouring lanes that first add up a contiguous run of red_chunk partials each.
+struct ReduceSlot {
+    uint32_t src;        // float offset of this lane's run inside one row of the staging array
+    uint32_t cnt;        // partials in the run (0: lane idle)
+    uint32_t iter;       // iteration inside the round the column belongs to
+    uint32_t cs;         // column inside that iteration
+    bool writer;         // lane that stores the finished sum
+    bool vec;            // run is float4-readable
+};
+
+template <int ROUND>
+__device__ __forceinline__ ReduceSlot make_slot(const GemvParams &p)
+{
+    const uint32_t T = blockDim.x, t = threadIdx.x;
+    const uint32_t R = 1u << p.red_shift;
+    const uint32_t slot = t >> p.red_shift, li = t & (R - 1);
+    ReduceSlot s{};
+    if (slot < ROUND * p.cpi) {
+        s.iter = slot / p.cpi;
+        s.cs = slot % p.cpi;
+        const uint32_t first = li * p.red_chunk;
+        s.cnt = first < p.bpc ? min(p.red_chunk, p.bpc - first) : 0u;
+        s.src = s.iter * T + s.cs * p.bpc + first;
+        s.writer = li == 0;
+        s.vec = (p.bpc % 4 == 0) && (p.red_chunk % 4 == 0);
+    }
+    return s;
+}
+
+template <int MT, int ROUND>
+__device__ __forceinline__ void reduce_store(const GemvParams &p, const ReduceSlot &slot, float *red,
+                                             const float (&part)[MT][ROUND], uint32_t it_base, uint32_t it_end)
 {
     const uint32_t T = blockDim.x, t = threadIdx.x;
 #pragma unroll
     for (int r = 0; r < MT; r++)
 #pragma unroll
-        for (int u = 0; u < kRound; u++) red[(r * kRound + u) * T + t] = part[r][u];
+        for (int u = 0; u < ROUND; u++) red[(r * ROUND + u) * T + t] = part[r][u];
     __syncthreads();
-    const uint32_t R = 1u << p.red_shift;
-    const uint32_t nslots = kRound * p.cpi;
-    for (uint32_t base = 0; base < (nslots << p.red_shift); base += T) {
-        const uint32_t idx = base + t;
-        const uint32_t slot = idx >> p.red_shift, li = idx & (R - 1);
-        const bool valid = slot < nslots;
-        const uint32_t u = valid ? slot / p.cpi : 0, cs = valid ? slot % p.cpi : 0;
 #pragma unroll
-        for (int r = 0; r < MT; r++) {
-            float s = 0.f;
-            if (valid) {
-                const float *src = red + (r * kRound + u) * T + cs * p.bpc;
-                for (uint32_t j = li; j < p.bpc; j += R) s += src[j];
+    for (int r = 0; r < MT; r++) {
+        const float *src = red + r * ROUND * T + slot.src;
+        float s = 0.f;
+        if (slot.vec) {
+            for (uint32_t j = 0; j < slot.cnt; j += 4) {
+                const float4 v = *reinterpret_cast<const float4 *>(src + j);
+                s += (v.x + v.y) + (v.z + v.w);
             }
-            for (uint32_t o = R >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            const uint32_t it = it_base + u;
-            const uint32_t col = it * p.cpi + cs;
-            if (valid && li == 0 && it < it_end && col < p.n) {
-                const size_t o = (size_t)r * p.n + col;
-                p.y[o] = p.addend ? s + p.addend[o] : s;
-            }
+        } else {
+            for (uint32_t j = 0; j < slot.cnt; j++) s += src[j];
+        }
+        for (uint32_t o = (1u << p.red_shift) >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        const uint32_t it = it_base + slot.iter;
+        const uint32_t col = it * p.cpi + slot.cs;
+        if (slot.writer && it < it_end && col < p.n) {
+            const size_t o = (size_t)r * p.n + col;
+            p.y[o] = p.addend ? s + p.addend[o] : s;
         }
     }
 }
@@ -147,72 +221,79 @@ __global__ void __launch_bounds__(TMAX) gemv_q4_kernel(const GemvParams p)
 {
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t T = blockDim.x, t = threadIdx.x;
-    uint4 *s_nib = reinterpret_cast<uint4 *>(smem);                                  // [STAGES][T]
-    uint32_t *s_hdr = reinterpret_cast<uint32_t *>(smem + (size_t)STAGES * T * 16);  // [STAGES][T]
-    float *s_red = reinterpret_cast<float *>(smem + (size_t)STAGES * T * 20);        // [2][MT][kRound][T]
+    uint4 *s_nib = reinterpret_cast<uint4 *>(smem) + t;                                   // [STAGES][T], own slot
+    uint32_t *s_hdr = reinterpret_cast<uint32_t *>(smem + (size_t)STAGES * T * 16) + t;   // [STAGES][T], own slot
+    float *s_red = reinterpret_cast<float *>(smem + (size_t)STAGES * T * 20);             // [2][MT][STAGES][T]
 
     const uint32_t it0 = (uint32_t)((unsigned long long)blockIdx.x * p.total_iters / gridDim.x);
     const uint32_t it1 = (uint32_t)((unsigned long long)(blockIdx.x + 1) * p.total_iters / gridDim.x);
     const uint32_t n_it = it1 - it0;
     const bool has_block = t < p.active;
     const uint32_t b = t % p.bpc, csub = t / p.bpc;
-    const uint32_t *g_hdr = reinterpret_cast<const uint32_t *>(p.w);
-    const uint4 *g_nib = reinterpret_cast<const uint4 *>(p.w + p.num_blocks * 4);
+    // iterations in which this thread has a column: all of them, except that the very last
+    // iteration of the matrix may hold fewer than cpi columns
+    uint32_t my_n = has_block ? n_it : 0u;
+    if (has_block && it1 == p.total_iters && n_it > 0 && (p.total_iters - 1) * p.cpi + csub >= p.n) my_n = n_it - 1;
 
-    auto prefetch = [&](uint32_t i) {
-        if (i < n_it && has_block && (it0 + i) * p.cpi + csub < p.n) {
-            const unsigned long long g = (unsigned long long)(it0 + i) * p.active + t;   // = col*bpc + b
-            cp_async16(&s_nib[(i % STAGES) * T + t], &g_nib[g]);
-            cp_async4(&s_hdr[(i % STAGES) * T + t], &g_hdr[g]);
+    const unsigned long long g0 = (unsigned long long)it0 * p.active + t;                // = col*bpc + b
+    const uint32_t *hdr_next = reinterpret_cast<const uint32_t *>(p.w) + g0;
+    const uint4 *nib_next = reinterpret_cast<const uint4 *>(p.w + p.num_blocks * 4) + g0;
+    const uint32_t stride = p.active;
+
+    auto issue = [&](int stage, bool ok) {
+        if (ok) {
+            cp_async16(s_nib + stage * T, nib_next);
+            cp_async4(s_hdr + stage * T, hdr_next);
         }
+        nib_next += stride;
+        hdr_next += stride;
         cp_async_commit();
     };
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; s++) prefetch(s);      // weights first: they depend on nothing
+    for (int s = 0; s < STAGES - 1; s++) issue(s, (uint32_t)s < my_n);     // weights first: they depend on nothing
 
     float2 xs[MT][16];
     float xsum[MT];
     load_x<MT, 4, 4>(p, b, xs, xsum);
+    const ReduceSlot slot = make_slot<STAGES>(p);
 
-    const uint32_t rounds = (n_it + kRound - 1) / kRound;
-    for (uint32_t round = 0; round < rounds; round++) {
-        float part[MT][kRound];
+    auto block_sum = [&](int stage, float (&out)[MT]) {
+        const uint4 q = s_nib[stage * T];
+        const uint32_t h = s_hdr[stage * T];
+        const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&h));       // (d, m), IEEE
+        float dot[MT];
+        dot_q4<MT>(q, xs, dot);
 #pragma unroll
-        for (int u = 0; u < kRound; u++) {
-            const uint32_t i = round * kRound + u;
-            prefetch(i + STAGES - 1);
-            cp_async_wait<STAGES - 1>();
+        for (int r = 0; r < MT; r++) out[r] = fmaf(dm.x * kUnscale, dot[r], dm.y * xsum[r]);
+    };
+
+    uint32_t round = 0;
+    for (uint32_t i = 0; i < n_it; i += STAGES, round++) {
+        float part[MT][STAGES];
+        if (i + 2 * STAGES - 1 <= my_n) {                  // whole round and everything it prefetches is in range
 #pragma unroll
-            for (int r = 0; r < MT; r++) part[r][u] = 0.f;
-            if (i < n_it && has_block && (it0 + i) * p.cpi + csub < p.n) {
-                const uint4 q = s_nib[(i % STAGES) * T + t];
-                const uint32_t h = s_hdr[(i % STAGES) * T + t];
-                const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&h));   // (d, m), IEEE
-                const uint32_t wv[4] = {q.x, q.y, q.z, q.w};
-                float2 a0[MT], a1[MT];
+            for (int u = 0; u < STAGES; u++) {
+                issue((u + STAGES - 1) % STAGES, true);
+                cp_async_wait<STAGES - 1>();
+                float out[MT];
+                block_sum(u, out);
 #pragma unroll
-                for (int r = 0; r < MT; r++) a0[r] = a1[r] = make_float2(0.f, 0.f);
+                for (int r = 0; r < MT; r++) part[r][u] = out[r];
+            }
+        } else {
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const uint32_t lo = wv[j], hi = wv[j] >> 16;
-                    const float2 v0 = subn2(lo & 0xFu, lo & 0xF0u), v1 = subn2(lo & 0xF00u, lo & 0xF000u);
-                    const float2 v2 = subn2(hi & 0xFu, hi & 0xF0u), v3 = subn2(hi & 0xF00u, hi & 0xF000u);
+            for (int u = 0; u < STAGES; u++) {
+                issue((u + STAGES - 1) % STAGES, i + u + STAGES - 1 < my_n);
+                cp_async_wait<STAGES - 1>();
+                float out[MT];
 #pragma unroll
-                    for (int r = 0; r < MT; r++) {
-                        a0[r] = fma2(v0, xs[r][4 * j + 0], a0[r]);
-                        a1[r] = fma2(v1, xs[r][4 * j + 1], a1[r]);
-                        a0[r] = fma2(v2, xs[r][4 * j + 2], a0[r]);
-                        a1[r] = fma2(v3, xs[r][4 * j + 3], a1[r]);
-                    }
-                }
+                for (int r = 0; r < MT; r++) out[r] = 0.f;
+                if (i + u < my_n) block_sum(u, out);
 #pragma unroll
-                for (int r = 0; r < MT; r++) {
-                    const float dot = (a0[r].x + a0[r].y) + (a1[r].x + a1[r].y);
-                    part[r][u] = fmaf(dm.x * kUnscale, dot, dm.y * xsum[r]);
-                }
+                for (int r = 0; r < MT; r++) part[r][u] = out[r];
             }
         }
-        reduce_store<MT>(p, s_red + (size_t)(round & 1) * MT * kRound * T, part, it0 + round * kRound, it1);
+        reduce_store<MT, STAGES>(p, slot, s_red + (size_t)(round & 1) * MT * STAGES * T, part, it0 + i, it1);
     }
     cp_async_wait<0>();
 }
@@ -224,90 +305,75 @@ __global__ void __launch_bounds__(TMAX) gemv_q8_kernel(const GemvParams p)
 {
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t T = blockDim.x, t = threadIdx.x, lane = t & 31u, warp = t >> 5, W = T >> 5;
-    uint8_t *s_w = smem + (size_t)warp * STAGES * kQ8WarpStage;                        // this warp's ring
-    float *s_red = reinterpret_cast<float *>(smem + (size_t)W * STAGES * kQ8WarpStage);  // [2][MT][kRound][T]
+    uint8_t *s_w = smem + (size_t)warp * STAGES * kQ8WarpStage;                         // this warp's ring
+    float *s_red = reinterpret_cast<float *>(smem + (size_t)W * STAGES * kQ8WarpStage);   // [2][MT][STAGES][T]
 
     const uint32_t it0 = (uint32_t)((unsigned long long)blockIdx.x * p.total_iters / gridDim.x);
     const uint32_t it1 = (uint32_t)((unsigned long long)(blockIdx.x + 1) * p.total_iters / gridDim.x);
     const uint32_t n_it = it1 - it0;
-    const uint32_t b = t % p.bpc;
+    const bool has_block = t < p.active;
+    const uint32_t b = t % p.bpc, csub = t / p.bpc;
+    uint32_t my_n = has_block ? n_it : 0u;
+    if (has_block && it1 == p.total_iters && n_it > 0 && (p.total_iters - 1) * p.cpi + csub >= p.n) my_n = n_it - 1;
 
-    // Blocks this warp owns in iteration `it`: [first, first+cnt) of the packed stream.
-    auto warp_span = [&](uint32_t it, unsigned long long &first, uint32_t &cnt) {
-        const uint32_t cols = min(p.cpi, p.n - it * p.cpi);
-        const uint32_t live = cols * p.bpc;
-        const uint32_t w0 = warp * 32u;
-        cnt = live > w0 ? min(32u, live - w0) : 0u;
-        first = (unsigned long long)it * p.active + w0;
-    };
-    auto prefetch = [&](uint32_t i) {
-        if (i < n_it) {
-            unsigned long long first;
-            uint32_t cnt;
-            warp_span(it0 + i, first, cnt);
-            if (cnt) {
-                const unsigned long long byte0 = first * 36ull;
-                const uint32_t lead = (uint32_t)(byte0 & 15ull);
-                const uint8_t *src = p.w + (byte0 - lead);
-                const uint32_t n16 = (lead + cnt * 36u + 15u) >> 4;      // stays inside the buffer: its size is a 16-B multiple
-                uint8_t *dst = s_w + (i % STAGES) * kQ8WarpStage;
-                for (uint32_t c = lane; c < n16; c += 32u) cp_async16(dst + 16u * c, src + 16ull * c);
-            }
+    // A warp owns 32 consecutive blocks of each iteration: `full` of them in every iteration, and
+    // `last` of them in the final iteration of the matrix (which may hold fewer columns).  active
+    // is a multiple of 4 and 4 blocks are 144 B, so every source address is 16-byte aligned.
+    const uint32_t w0 = warp * 32u;
+    const uint32_t full = p.active > w0 ? min(32u, p.active - w0) : 0u;
+    const uint32_t last_live = (p.n - (p.total_iters - 1) * p.cpi) * p.bpc;
+    const uint32_t last = last_live > w0 ? min(32u, last_live - w0) : 0u;
+    const bool ends_matrix = it1 == p.total_iters;
+    const uint8_t *src_next = p.w + ((unsigned long long)it0 * p.active + w0) * 36ull + 16u * lane;
+    const uint32_t stride = p.active * 36u;
+
+    auto issue = [&](int stage, uint32_t iter, bool in_range) {       // iter: index inside this CTA's range
+        if (in_range) {
+            const uint32_t cnt = (ends_matrix && iter == n_it - 1) ? last : full;
+            const uint32_t pieces = (cnt * 36u + 15u) >> 4;
+            uint8_t *dst = s_w + stage * kQ8WarpStage + 16u * lane;
+            if (lane < pieces) cp_async16(dst, src_next);
+            if (lane + 32u < pieces) cp_async16(dst + 512, src_next + 512);
+            if (lane + 64u < pieces) cp_async16(dst + 1024, src_next + 1024);
         }
+        src_next += stride;
         cp_async_commit();
     };
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; s++) prefetch(s);
+    for (int s = 0; s < STAGES - 1; s++) issue(s, (uint32_t)s, (uint32_t)s < n_it);
 
     float2 xs[MT][16];
     float xsum[MT];
     load_x<MT, 8, 2>(p, b, xs, xsum);
+    const ReduceSlot slot = make_slot<STAGES>(p);
 
-    const uint32_t rounds = (n_it + kRound - 1) / kRound;
-    for (uint32_t round = 0; round < rounds; round++) {
-        float part[MT][kRound];
+    auto block_sum = [&](int stage, float (&out)[MT]) {
+        const uint32_t *bp = reinterpret_cast<const uint32_t *>(s_w + stage * kQ8WarpStage + 36u * lane);
+        const uint32_t sw = bp[0];
+        const float scale = __half2float(__ushort_as_half((unsigned short)(sw & 0xFFFFu)));
+        float dot[MT];
+        dot_q8<MT>(bp + 1, xs, dot);
 #pragma unroll
-        for (int u = 0; u < kRound; u++) {
-            const uint32_t i = round * kRound + u;
+        for (int r = 0; r < MT; r++) out[r] = fmaf(scale * kUnscale, dot[r], -128.f * scale * xsum[r]);
+    };
+
+    uint32_t round = 0;
+    for (uint32_t i = 0; i < n_it; i += STAGES, round++) {
+        float part[MT][STAGES];
+#pragma unroll
+        for (int u = 0; u < STAGES; u++) {
             __syncwarp();                                   // every lane is done reading the stage refilled next
-            prefetch(i + STAGES - 1);
+            issue((u + STAGES - 1) % STAGES, i + u + STAGES - 1, i + u + STAGES - 1 < n_it);
             cp_async_wait<STAGES - 1>();
-            __syncwarp();                                   // other lanes' copies for stage i are visible
+            __syncwarp();                                   // the other lanes' copies for this stage are visible
+            float out[MT];
 #pragma unroll
-            for (int r = 0; r < MT; r++) part[r][u] = 0.f;
-            if (i < n_it) {
-                unsigned long long first;
-                uint32_t cnt;
-                warp_span(it0 + i, first, cnt);
-                if (lane < cnt) {
-                    const uint32_t lead = (uint32_t)((first * 36ull) & 15ull);
-                    const uint32_t *bp = reinterpret_cast<const uint32_t *>(s_w + (i % STAGES) * kQ8WarpStage + lead + 36u * lane);
-                    const uint32_t sw = bp[0];
-                    const float scale = __half2float(__ushort_as_half((unsigned short)(sw & 0xFFFFu)));
-                    float2 a0[MT], a1[MT];
+            for (int r = 0; r < MT; r++) out[r] = 0.f;
+            if (i + u < my_n) block_sum(u, out);
 #pragma unroll
-                    for (int r = 0; r < MT; r++) a0[r] = a1[r] = make_float2(0.f, 0.f);
-#pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const uint32_t lo = bp[1 + j], hi = lo >> 16;
-                        // (q ^ 0x80) is q + 128 as an unsigned byte
-                        const float2 v0 = subn2((lo ^ 0x80u) & 0xFFu, (lo ^ 0x8000u) & 0xFF00u);
-                        const float2 v1 = subn2((hi ^ 0x80u) & 0xFFu, (hi ^ 0x8000u) & 0xFF00u);
-#pragma unroll
-                        for (int r = 0; r < MT; r++) {
-                            a0[r] = fma2(v0, xs[r][2 * j + 0], a0[r]);
-                            a1[r] = fma2(v1, xs[r][2 * j + 1], a1[r]);
-                        }
-                    }
-#pragma unroll
-                    for (int r = 0; r < MT; r++) {
-                        const float dot = (a0[r].x + a0[r].y) + (a1[r].x + a1[r].y);
-                        part[r][u] = fmaf(scale * kUnscale, dot, -128.f * scale * xsum[r]);
-                    }
-                }
-            }
+            for (int r = 0; r < MT; r++) part[r][u] = out[r];
         }
-        reduce_store<MT>(p, s_red + (size_t)(round & 1) * MT * kRound * T, part, it0 + round * kRound, it1);
+        reduce_store<MT, STAGES>(p, slot, s_red + (size_t)(round & 1) * MT * STAGES * T, part, it0 + i, it1);
     }
     cp_async_wait<0>();
 }
@@ -316,7 +382,7 @@ __global__ void __launch_bounds__(TMAX) gemv_q8_kernel(const GemvParams p)
 
 // Any K (multiple of 32), any N, any alignment of the nibble region: one warp per column, plain
 // 4-byte loads.  Used only for shapes the streaming kernels do not take (K > 32768, or a packed
-// buffer whose size is not a multiple of 16 bytes).
+// buffer whose size is not a multiple of 16 bytes, K < 256).
 template <int FMT>
 __global__ void __launch_bounds__(256) gemv_generic_kernel(const GemvParams p, uint32_t m)
 {
@@ -365,37 +431,49 @@ __global__ void __launch_bounds__(256) gemv_generic_kernel(const GemvParams p, u
 // ------------------------------------------------------------------------------ launch logic
 
 struct Config {
-    uint32_t threads, cpi, red_shift;
+    uint32_t threads, cpi, red_shift, red_chunk;
     int stages;
 };
+
+// Largest column count per iteration that fits `threads` and keeps cpi*bpc a multiple of 4
+// (so that a Q8 warp's 36-byte blocks always start on a 16-byte boundary).
+uint32_t columns_for(uint32_t threads, uint32_t bpc)
+{
+    uint32_t cpi = threads / bpc;
+    const uint32_t need = bpc % 4 == 0 ? 1u : (bpc % 2 == 0 ? 2u : 4u);
+    return cpi - cpi % need;
+}
 
 // Depends on K only, so that a column's summation order is the same for every N.
 Config choose_config(uint32_t bpc)
 {
     Config c{};
     if (bpc <= 256) {
-        uint32_t best_t = 128;
-        double best_u = 0.0;
+        uint32_t best_t = 0;
+        double best_u = -1.0;
         for (uint32_t t = 128; t <= 256; t += 32) {
-            if (t < bpc) continue;
-            const double util = (double)((t / bpc) * bpc) / t;
+            const double util = (double)(columns_for(t, bpc) * bpc) / t;
             if (util > best_u + 1e-9) { best_u = util; best_t = t; }
         }
         c.threads = best_t;
     } else {
         c.threads = (bpc + 31u) & ~31u;
     }
-    c.cpi = c.threads / bpc;
-    c.stages = c.threads <= 256 ? 8 : 4;
-    uint32_t lanes = bpc / 4;                       // about four partials per finishing lane
+    c.cpi = columns_for(c.threads, bpc);
+    c.stages = c.threads <= 512 ? 8 : 4;
+    // finishing lanes per column: a power of two, at most 32, with stages*cpi*lanes <= threads
+    const uint32_t slots = (uint32_t)c.stages * c.cpi;
     c.red_shift = 0;
-    while ((2u << c.red_shift) <= lanes && c.red_shift < 5) c.red_shift++;
+    while (c.red_shift < 5 && (slots << (c.red_shift + 1)) <= c.threads && (2u << c.red_shift) <= bpc) c.red_shift++;
+    const uint32_t lanes = 1u << c.red_shift;
+    c.red_chunk = (bpc + lanes - 1) / lanes;
+    if (c.red_chunk % 4 != 0 && bpc % 4 == 0 && c.red_chunk > 4) c.red_chunk = (c.red_chunk + 3u) & ~3u;
     return c;
 }
 
 size_t smem_bytes(int fmt, const Config &c, int mt)
 {
-    const size_t red = (size_t)2 * mt * kRound * c.threads * sizeof(float);
+    const size_t red = (size_t)2 * mt * c.stages * c.threads * sizeof(float);
     if (fmt == MGQ_FMT_Q4) return (size_t)c.stages * c.threads * 20 + red;
     return (size_t)(c.threads / 32) * c.stages * kQ8WarpStage + red;
 }
@@ -406,11 +484,11 @@ KernelFn pick_kernel(int fmt, int mt, const Config &c)
 {
     if (fmt == MGQ_FMT_Q4) {
         if (c.threads <= 256) return mt == 2 ? gemv_q4_kernel<2, 8, 256> : gemv_q4_kernel<1, 8, 256>;
-        if (c.threads <= 512) return mt == 2 ? gemv_q4_kernel<2, 4, 512> : gemv_q4_kernel<1, 4, 512>;
+        if (c.threads <= 512) return mt == 2 ? gemv_q4_kernel<2, 8, 512> : gemv_q4_kernel<1, 8, 512>;
         return mt == 1 ? gemv_q4_kernel<1, 4, 1024> : nullptr;
     }
     if (c.threads <= 256) return mt == 2 ? gemv_q8_kernel<2, 8, 256> : gemv_q8_kernel<1, 8, 256>;
-    if (c.threads <= 512) return mt == 2 ? gemv_q8_kernel<2, 4, 512> : gemv_q8_kernel<1, 4, 512>;
+    if (c.threads <= 512) return mt == 2 ? gemv_q8_kernel<2, 8, 512> : gemv_q8_kernel<1, 8, 512>;
     return mt == 1 ? gemv_q8_kernel<1, 4, 1024> : nullptr;
 }
 
@@ -435,8 +513,10 @@ int device_info(DeviceInfo &out)
     return MGQ_OK;
 }
 
-// Opts the kernel into its dynamic shared memory size and returns resident CTAs per SM.
-// Both calls cost microseconds, so the answer is remembered per (device, kernel, shape).
+// Returns resident CTAs per SM for (kernel, threads, smem).  The first use of a kernel on a
+// device opts it into the device's largest dynamic shared memory size (one setting per kernel:
+// a later, smaller request must not lower it).  Answers are remembered: both calls cost
+// microseconds.
 int kernel_occupancy(KernelFn fn, uint32_t threads, size_t smem, int &occ)
 {
     struct Entry { int dev; KernelFn fn; uint32_t threads; size_t smem; int occ; };
@@ -445,9 +525,16 @@ int kernel_occupancy(KernelFn fn, uint32_t threads, size_t smem, int &occ)
     int dev = 0;
     MGQ_CUDA(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> lock(mu);
-    for (const Entry &e : seen)
-        if (e.dev == dev && e.fn == fn && e.threads == threads && e.smem == smem) { occ = e.occ; return MGQ_OK; }
-    MGQ_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    bool opted_in = false;
+    for (const Entry &e : seen) {
+        if (e.dev != dev || e.fn != fn) continue;
+        opted_in = true;
+        if (e.threads == threads && e.smem == smem) { occ = e.occ; return MGQ_OK; }
+    }
+    int optin = 0;
+    MGQ_CUDA(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    if (smem > (size_t)optin) return fail(MGQ_ERR_SHAPE, "GEMV needs %zu B of shared memory, device allows %d", smem, optin);
+    if (!opted_in) MGQ_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, optin));
     MGQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, (int)threads, smem));
     if (occ < 1) return fail(MGQ_ERR_CUDA, "GEMV kernel does not fit on an SM (threads=%u smem=%zu)", threads, smem);
     seen.push_back({dev, fn, threads, smem, occ});
@@ -466,7 +553,7 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
     p.num_blocks = (unsigned long long)bpc * n;
     p.w = static_cast<const uint8_t *>(w);
 
-    const bool streamable = bpc <= 1024 && (p.num_blocks % 4 == 0) &&
+    const bool streamable = bpc >= 8 && bpc <= 1024 && (p.num_blocks % 4 == 0) &&
                             (reinterpret_cast<uintptr_t>(x) % 16 == 0);
     if (!streamable) {
         p.x = x; p.addend = addend; p.y = y;
@@ -481,6 +568,7 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
     p.cpi = cfg.cpi;
     p.active = cfg.cpi * bpc;
     p.red_shift = cfg.red_shift;
+    p.red_chunk = cfg.red_chunk;
     p.total_iters = (n + cfg.cpi - 1) / cfg.cpi;
     DeviceInfo di;
     if (int rc = device_info(di)) return rc;

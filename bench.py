@@ -3,8 +3,8 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch M] [--fmt q4|q8] [--impl reference]
 
-Workload: every quantized GEMV of one Qwen3-8B-shaped decode token (36 layers x {q,k,v,o,gate|up,
-down} + lm_head, 217 launches, 4.73 GB of packed Q4 weights), column-sharded over N GPUs with
+Workload: every quantized GEMV of one Qwen3-8B-shaped decode token (36 layers x {q|k|v, o, gate|up,
+down} + lm_head, 145 launches, 4.73 GB of packed Q4 weights), column-sharded over N GPUs with
 an all-gather after each exchange point.  A step is one token; `value` is the algorithmic bytes
 all ranks move per step divided by the step time (max over ranks, CUDA events, barrier and
 synchronize on both sides).  Weights are resident; per-step weight bytes exceed L2 by 4-37x, so
@@ -192,7 +192,7 @@ def run_reference(args, shape, fmt):
 def workload_config(shape, fmt, batch, gpus):
     return {
         "workload": f"{shape.name}-shaped decode token, all {'Q4' if fmt == 2 else 'Q8'} GEMVs "
-                    f"({shape.layers} layers x q,k,v,o,gate|up,down + lm_head), batch {batch}",
+                    f"({shape.layers} layers x q|k|v,o,gate|up,down + lm_head), batch {batch}",
         "weights": "packed codes uniform, f16 block scales log-uniform [1e-3,1e-1], offset 8 (Q4); seeded",
         "activations": "f32 N(0,1), seeded",
         "parallelism": f"columns sharded x{gpus}, NCCL all-gather at 4 points per layer + logits" if gpus > 1 else "single GPU",

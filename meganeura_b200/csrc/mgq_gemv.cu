@@ -17,18 +17,22 @@
 //    nibble bytes + 4 header bytes (no barrier needed).  Q8: a 36-byte block is only 4-byte
 //    aligned, so each warp copies its 32 blocks (1152 contiguous bytes) as 16-byte pieces
 //    and lanes then read their block at a 36-byte stride (9 is odd: conflict-free).
-//  * Integer codes are turned into floats without conversion instructions: a masked code is
-//    reinterpreted as an f32 *subnormal* (code * 2^-149, times 16/256/4096 for codes taken in
-//    place from higher bit positions) and multiplied by an activation pre-scaled by the
-//    matching power of two, using packed two-wide f32 FMAs.  One logic op + half an FMA per
-//    weight.  Per-block scales are applied once per 32 products:
-//        Q4:  d * sum(x*nib) + m * sum(x)          Q8:  s * (sum(x*(q+128)) - 128*sum(x))
+//  * The 32 products of a block are integer dot products (dp4a, full rate on sm_100 while
+//    logic ops and int->float conversions are not).  The block's activations are held as
+//    block-fixed-point: X[i] = round(x[i] * 2^(21-E)), 2^E <= max|x| < 2^(E+1), |X| <= 2^22,
+//    split into three byte planes (two unsigned, the top one signed).  Q8 codes are already
+//    int8x4 words; Q4 needs three logic ops per eight nibbles.  Within a block the sum is
+//    exact integer arithmetic; the three plane sums are recombined in f32 and the per-block
+//    scale is applied once per 32 products, accumulating over blocks in f32:
+//        Q4:  d * sum(x*nib) + m * sum(x)          Q8:  s * sum(x*q)
+//    The fixed-point step costs at most 2^-22 of the block's largest |x| per activation.
 //  * Column sums are finished through shared memory + warp shuffles in a fixed order that
 //    depends only on K, so a column's result does not depend on N or on its position in the
 //    grid (column shards reproduce the unsharded result bit for bit).
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -37,8 +41,6 @@
 namespace mgq {
 namespace {
 
-constexpr float kXScale = 0x1p64f;            // activations are pre-scaled by 2^64 (exact)
-constexpr float kUnscale = 0x1p85f;           // 2^(149-64): undoes subnormal * pre-scale
 constexpr uint32_t kQ8WarpStage = 1152;       // 32 blocks * 36 B per warp and stage
 
 struct GemvParams {
@@ -53,7 +55,22 @@ struct GemvParams {
     uint32_t red_shift;    // log2(lanes that finish one column sum)
     uint32_t red_chunk;    // partials summed by each finishing lane = ceil(bpc / lanes)
     unsigned long long num_blocks;
+#ifdef MGQ_GEMV_TRACE
+    unsigned long long *trace;   // [gridDim.x][4] globaltimer stamps: start, after dependency wait, first block done, end
+#endif
 };
+
+#ifdef MGQ_GEMV_TRACE
+__device__ __forceinline__ unsigned long long now_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define MGQ_STAMP(p, slot) do { if ((p).trace && threadIdx.x == 0) (p).trace[blockIdx.x * 4 + (slot)] = now_ns(); } while (0)
+#else
+#define MGQ_STAMP(p, slot) do { } while (0)
+#endif
 
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem)
 {
@@ -72,83 +89,122 @@ __device__ __forceinline__ void cp_async_wait()
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
-__device__ __forceinline__ float2 subn2(uint32_t a, uint32_t b) { return make_float2(__uint_as_float(a), __uint_as_float(b)); }
+// Programmatic dependent launch: a GEMV launched with the stream-serialization attribute may
+// start while the previous kernel of the stream is still draining.  Everything before
+// grid_dependency_wait() must not touch memory that an earlier kernel writes: only the packed
+// weights (immutable after upload) are fetched there.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
-// Loads the 32 activations of block b for MT rows, keeps their plain sum, and pre-scales them.
-// STEP is the bit distance between two codes that are read in place (4 for Q4, 8 for Q8);
-// PER is how many codes are taken from one 16-bit half (4 for Q4, 2 for Q8).
-template <int MT, int STEP, int PER>
-__device__ __forceinline__ void load_x(const GemvParams &p, uint32_t b, float2 (&xs)[MT][16], float (&xsum)[MT])
+// dp4a with mixed signedness (a: packed codes, b: packed activation bytes).
+__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c)
 {
-#pragma unroll
-    for (int r = 0; r < MT; r++) {
-        const float4 *xp = reinterpret_cast<const float4 *>(p.x + (size_t)r * p.k + 32u * b);
-        float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const float4 v = __ldg(xp + j);
-            s0 += v.x + v.y;
-            s1 += v.z + v.w;
-            const float e[4] = {v.x, v.y, v.z, v.w};
-            float o[4];
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                const int pos = (4 * j + c) % PER;                    // position inside its 16-bit half
-                o[c] = e[c] * (kXScale / (float)(1u << (STEP * pos)));
-            }
-            xs[r][2 * j] = make_float2(o[0], o[1]);
-            xs[r][2 * j + 1] = make_float2(o[2], o[3]);
-        }
-        xsum[r] = s0 + s1;
-    }
+    int d;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c)
+{
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_su(uint32_t a, uint32_t b, int c)
+{
+    int d;
+    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c)
+{
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
 }
 
-// One 32-element block: sum over the block of x[i] * code[i] (times 2^-85), MT rows at once.
-template <int MT>
-__device__ __forceinline__ void dot_q4(const uint4 &q, const float2 (&xs)[MT][16], float (&dot)[MT])
-{
-    const uint32_t wv[4] = {q.x, q.y, q.z, q.w};
-    float2 a0[MT], a1[MT];
-#pragma unroll
-    for (int r = 0; r < MT; r++) a0[r] = a1[r] = make_float2(0.f, 0.f);
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        const uint32_t lo = wv[j], hi = wv[j] >> 16;
-        const float2 v0 = subn2(lo & 0xFu, lo & 0xF0u), v1 = subn2(lo & 0xF00u, lo & 0xF000u);
-        const float2 v2 = subn2(hi & 0xFu, hi & 0xF0u), v3 = subn2(hi & 0xF00u, hi & 0xF000u);
-#pragma unroll
-        for (int r = 0; r < MT; r++) {
-            a0[r] = fma2(v0, xs[r][4 * j + 0], a0[r]);
-            a1[r] = fma2(v1, xs[r][4 * j + 1], a1[r]);
-            a0[r] = fma2(v2, xs[r][4 * j + 2], a0[r]);
-            a1[r] = fma2(v3, xs[r][4 * j + 3], a1[r]);
-        }
-    }
-#pragma unroll
-    for (int r = 0; r < MT; r++) dot[r] = (a0[r].x + a0[r].y) + (a1[r].x + a1[r].y);
-}
+// The 32 activations of one block as three byte planes, packed four to a word in the order
+// the codes come out of the packed weight words.
+struct XBlock {
+    uint32_t p0[8], p1[8], p2[8];   // plane 0, 1: unsigned bytes; plane 2: signed bytes
+    float inv;                      // 2^(E-21): turns the integer dot product back into x units
+    float sum;                      // plain f32 sum of the 32 activations (for Q4's "+ m")
+};
 
-// bp points at the 8 code words of a Q8 block; codes are read as (q + 128), an unsigned byte.
-template <int MT>
-__device__ __forceinline__ void dot_q8(const uint32_t *bp, const float2 (&xs)[MT][16], float (&dot)[MT])
+// ORDER 0 (Q8): word j holds elements 4j .. 4j+3.
+// ORDER 1 (Q4): word 2j holds elements 8j+{0,2,4,6} (low nibbles of nibble word j),
+//               word 2j+1 holds elements 8j+{1,3,5,7} (high nibbles).
+template <int ORDER>
+__device__ __forceinline__ void load_x(const float *xrow, uint32_t b, XBlock &xb)
 {
-    float2 a0[MT], a1[MT];
-#pragma unroll
-    for (int r = 0; r < MT; r++) a0[r] = a1[r] = make_float2(0.f, 0.f);
+    const float4 *xp = reinterpret_cast<const float4 *>(xrow + 32u * b);
+    float v[32];
 #pragma unroll
     for (int j = 0; j < 8; j++) {
-        const uint32_t lo = bp[j] ^ 0x80808080u, hi = lo >> 16;
-        const float2 v0 = subn2(lo & 0xFFu, lo & 0xFF00u);
-        const float2 v1 = subn2(hi & 0xFFu, hi & 0xFF00u);
-#pragma unroll
-        for (int r = 0; r < MT; r++) {
-            a0[r] = fma2(v0, xs[r][2 * j + 0], a0[r]);
-            a1[r] = fma2(v1, xs[r][2 * j + 1], a1[r]);
-        }
+        const float4 t = __ldg(xp + j);
+        v[4 * j + 0] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
     }
+    float amax = 0.f, s0 = 0.f, s1 = 0.f;
 #pragma unroll
-    for (int r = 0; r < MT; r++) dot[r] = (a0[r].x + a0[r].y) + (a1[r].x + a1[r].y);
+    for (int i = 0; i < 32; i += 2) {
+        amax = fmaxf(amax, fmaxf(fabsf(v[i]), fabsf(v[i + 1])));
+        s0 += v[i];
+        s1 += v[i + 1];
+    }
+    xb.sum = s0 + s1;
+    // biased exponent of the largest magnitude, clamped so that both 2^(21-E) and 2^(E-21) are normal
+    uint32_t eb = (__float_as_uint(amax) >> 23) & 0xFFu;
+    const bool finite = eb != 0xFFu;
+    eb = min(max(eb, 24u), 254u);
+    const float scale = __uint_as_float((275u - eb) << 23);           // 2^(21-E)
+    xb.inv = finite ? __uint_as_float((eb - 21u) << 23) : __int_as_float(0x7FC00000);   // 2^(E-21), NaN for inf/NaN input
+    // x*scale + 1.5*2^23 leaves X + 2^22 in the low 23 mantissa bits (|X| <= 2^22): bytes 0..2 of the
+    // float's bit pattern are the planes, the top one offset by 64.
+    uint32_t bits[32];
+#pragma unroll
+    for (int i = 0; i < 32; i++) bits[i] = __float_as_uint(fmaf(v[i], scale, 12582912.f));
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
+        int e0, e1, e2, e3;
+        if (ORDER == 0) { e0 = 4 * w; e1 = e0 + 1; e2 = e0 + 2; e3 = e0 + 3; }
+        else            { e0 = 8 * (w >> 1) + (w & 1); e1 = e0 + 2; e2 = e0 + 4; e3 = e0 + 6; }
+        const uint32_t a = bits[e0], bb = bits[e1], c = bits[e2], d = bits[e3];
+        xb.p0[w] = __byte_perm(__byte_perm(a, bb, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+        xb.p1[w] = __byte_perm(__byte_perm(a, bb, 0x0051), __byte_perm(c, d, 0x0051), 0x5410);
+        const uint32_t top = __byte_perm(__byte_perm(a, bb, 0x0062), __byte_perm(c, d, 0x0062), 0x5410);
+        xb.p2[w] = (top + 0x40404040u) ^ 0x80808080u;                  // (u + 64) - 128 = u - 64 as int8; u <= 127: no carries
+    }
+}
+
+// Exact sum over one block of X[i] * code[i], returned in f32 (planes recombined with two FMAs).
+__device__ __forceinline__ float dot_q4(const uint4 &q, const XBlock &xb)
+{
+    const uint32_t wv[4] = {q.x, q.y, q.z, q.w};
+    int a0 = 0, a1 = 0, a2 = 0;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const uint32_t lo = wv[j] & 0x0F0F0F0Fu, hi = (wv[j] >> 4) & 0x0F0F0F0Fu;
+        a0 = dp4a_uu(lo, xb.p0[2 * j], a0);
+        a1 = dp4a_uu(lo, xb.p1[2 * j], a1);
+        a2 = dp4a_us(lo, xb.p2[2 * j], a2);
+        a0 = dp4a_uu(hi, xb.p0[2 * j + 1], a0);
+        a1 = dp4a_uu(hi, xb.p1[2 * j + 1], a1);
+        a2 = dp4a_us(hi, xb.p2[2 * j + 1], a2);
+    }
+    return fmaf((float)a2, 65536.f, fmaf((float)a1, 256.f, (float)a0));
+}
+
+// bp points at the 8 code words (int8 x 4) of a Q8 block.
+__device__ __forceinline__ float dot_q8(const uint32_t *bp, const XBlock &xb)
+{
+    int a0 = 0, a1 = 0, a2 = 0;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const uint32_t c = bp[j];
+        a0 = dp4a_su(c, xb.p0[j], a0);
+        a1 = dp4a_su(c, xb.p1[j], a1);
+        a2 = dp4a_ss(c, xb.p2[j], a2);
+    }
+    return fmaf((float)a2, 65536.f, fmaf((float)a1, 256.f, (float)a0));
 }
 
 // Which column sum a thread finishes after each round; the same for every round, so it is
@@ -224,6 +280,7 @@ __global__ void __launch_bounds__(TMAX) gemv_q4_kernel(const GemvParams p)
     uint4 *s_nib = reinterpret_cast<uint4 *>(smem) + t;                                   // [STAGES][T], own slot
     uint32_t *s_hdr = reinterpret_cast<uint32_t *>(smem + (size_t)STAGES * T * 16) + t;   // [STAGES][T], own slot
     float *s_red = reinterpret_cast<float *>(smem + (size_t)STAGES * T * 20);             // [2][MT][STAGES][T]
+    MGQ_STAMP(p, 0);
 
     const uint32_t it0 = (uint32_t)((unsigned long long)blockIdx.x * p.total_iters / gridDim.x);
     const uint32_t it1 = (uint32_t)((unsigned long long)(blockIdx.x + 1) * p.total_iters / gridDim.x);
@@ -251,20 +308,21 @@ __global__ void __launch_bounds__(TMAX) gemv_q4_kernel(const GemvParams p)
     };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) issue(s, (uint32_t)s < my_n);     // weights first: they depend on nothing
+    grid_launch_dependents();
+    grid_dependency_wait();                                                 // x, addend and y belong to earlier kernels
+    MGQ_STAMP(p, 1);
 
-    float2 xs[MT][16];
-    float xsum[MT];
-    load_x<MT, 4, 4>(p, b, xs, xsum);
+    XBlock xb[MT];
+#pragma unroll
+    for (int r = 0; r < MT; r++) load_x<1>(p.x + (size_t)r * p.k, b, xb[r]);
     const ReduceSlot slot = make_slot<STAGES>(p);
 
     auto block_sum = [&](int stage, float (&out)[MT]) {
         const uint4 q = s_nib[stage * T];
         const uint32_t h = s_hdr[stage * T];
         const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&h));       // (d, m), IEEE
-        float dot[MT];
-        dot_q4<MT>(q, xs, dot);
 #pragma unroll
-        for (int r = 0; r < MT; r++) out[r] = fmaf(dm.x * kUnscale, dot[r], dm.y * xsum[r]);
+        for (int r = 0; r < MT; r++) out[r] = fmaf(dm.x * xb[r].inv, dot_q4(q, xb[r]), dm.y * xb[r].sum);
     };
 
     uint32_t round = 0;
@@ -293,9 +351,11 @@ __global__ void __launch_bounds__(TMAX) gemv_q4_kernel(const GemvParams p)
                 for (int r = 0; r < MT; r++) part[r][u] = out[r];
             }
         }
+        if (round == 0) MGQ_STAMP(p, 2);
         reduce_store<MT, STAGES>(p, slot, s_red + (size_t)(round & 1) * MT * STAGES * T, part, it0 + i, it1);
     }
     cp_async_wait<0>();
+    MGQ_STAMP(p, 3);
 }
 
 // ------------------------------------------------------------------------------------ Q8
@@ -341,20 +401,20 @@ __global__ void __launch_bounds__(TMAX) gemv_q8_kernel(const GemvParams p)
     };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) issue(s, (uint32_t)s, (uint32_t)s < n_it);
+    grid_launch_dependents();
+    grid_dependency_wait();
 
-    float2 xs[MT][16];
-    float xsum[MT];
-    load_x<MT, 8, 2>(p, b, xs, xsum);
+    XBlock xb[MT];
+#pragma unroll
+    for (int r = 0; r < MT; r++) load_x<0>(p.x + (size_t)r * p.k, b, xb[r]);
     const ReduceSlot slot = make_slot<STAGES>(p);
 
     auto block_sum = [&](int stage, float (&out)[MT]) {
         const uint32_t *bp = reinterpret_cast<const uint32_t *>(s_w + stage * kQ8WarpStage + 36u * lane);
         const uint32_t sw = bp[0];
         const float scale = __half2float(__ushort_as_half((unsigned short)(sw & 0xFFFFu)));
-        float dot[MT];
-        dot_q8<MT>(bp + 1, xs, dot);
 #pragma unroll
-        for (int r = 0; r < MT; r++) out[r] = fmaf(scale * kUnscale, dot[r], -128.f * scale * xsum[r]);
+        for (int r = 0; r < MT; r++) out[r] = scale * xb[r].inv * dot_q8(bp + 1, xb[r]);
     };
 
     uint32_t round = 0;
@@ -541,7 +601,27 @@ int kernel_occupancy(KernelFn fn, uint32_t threads, size_t smem, int &occ)
     return MGQ_OK;
 }
 
+// MGQ_SERIAL_DISPATCH=1 turns programmatic dependent launch off (every kernel then starts only
+// after its predecessor has finished), like the reference's MEGANEURA_SERIAL_DISPATCH debugging
+// switch (src/runtime.rs:1703-1707).
+bool overlap_allowed()
+{
+    static const bool allowed = [] {
+        const char *v = std::getenv("MGQ_SERIAL_DISPATCH");
+        return !(v && v[0] == '1');
+    }();
+    return allowed;
+}
+
+#ifdef MGQ_GEMV_TRACE
+unsigned long long *g_trace = nullptr;
+#endif
+
 }  // namespace
+
+#ifdef MGQ_GEMV_TRACE
+extern "C" void mgq_debug_set_trace(unsigned long long *dev_buffer) { g_trace = dev_buffer; }
+#endif
 
 int launch_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
                 uint32_t m, uint32_t k, uint32_t n, void *stream_v)
@@ -586,8 +666,21 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
         p.x = x + (size_t)r0 * k;
         p.addend = addend ? addend + (size_t)r0 * n : nullptr;
         p.y = y + (size_t)r0 * n;
-        fn<<<grid, cfg.threads, smem, stream>>>(p);
-        MGQ_CUDA(cudaGetLastError());
+#ifdef MGQ_GEMV_TRACE
+        p.trace = g_trace;
+        if (g_trace) g_trace += (size_t)grid * 4;
+#endif
+        cudaLaunchConfig_t lc{};
+        lc.gridDim = dim3(grid, 1, 1);
+        lc.blockDim = dim3(cfg.threads, 1, 1);
+        lc.dynamicSmemBytes = smem;
+        lc.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        lc.attrs = attr;
+        lc.numAttrs = overlap_allowed() ? 1 : 0;
+        MGQ_CUDA(cudaLaunchKernelEx(&lc, fn, p));
         r0 += mt;
     }
     return MGQ_OK;

@@ -1,6 +1,6 @@
 """The quantized GEMVs of one decode token, column-sharded over the GPUs of a node.
 
-A decode step of a transformer is, per layer, the projections q, k, v, o (+ residual), the
+A decode step of a transformer is, per layer, the projections q|k|v, o (+ residual), the
 concatenated gate|up projection and the down projection (+ residual), then the lm_head -- the
 shapes of meganeura's Qwen3 example (examples/qwen3.rs:243-322) and of its SmolLM2 decode graph
 (src/models/smollm2.rs:337-408) after the MatMul+Add and SwiGLU-concat fusions.  This module
@@ -8,10 +8,10 @@ runs exactly those dequantize-fused GEMVs, in model order, through the C ABI.
 
 The operators that connect the GEMVs in the model (RMSNorm, RoPE, attention, SwiGLU) are not
 part of this library yet, so every GEMV reads a fixed seeded activation vector of the right
-length; the exchange steps of the column-sharded model are kept: after the attention block's
-projections, after o, after gate|up (the activated half) and after down, the per-rank output
-slices are all-gathered so that every rank holds the full vector, and the lm_head logits are
-gathered once per token.
+length; the exchange steps of the column-sharded model are kept: after q|k|v (a vector of the
+attention output's size), after o, after gate|up (the activated half) and after down, the
+per-rank output slices are all-gathered so that every rank holds the full vector, and the
+lm_head logits are gathered once per token.
 """
 from __future__ import annotations
 
@@ -40,28 +40,38 @@ SMOLLM2_135M = ModelShape("smollm2-135m", 30, 576, 576, 192, 1536, 49152)
 
 @dataclass(frozen=True)
 class GemvSpec:
-    name: str          # q, k, v, o, gate_up, down, lm_head
+    name: str          # qkv (or q, k, v), o, gate_up, down, lm_head
     k: int
     n: int
-    groups: int        # column groups that are sharded separately (2 for gate|up)
+    groups: tuple      # widths of the column groups that are sharded separately (q|k|v, gate|up)
     residual: bool     # fused "+ src" addend (MatMulGemvAdd)
-    gather: str        # "", "full" (gather all columns) or "half" (gather the first group only)
+    gather: str        # "" or "first": all-gather this rank's slice of the first column group
     src: str           # which activation vector it reads: "h" (hidden) or "f" (ffn)
 
 
-def layer_specs(s: ModelShape) -> list[GemvSpec]:
-    return [
-        GemvSpec("q", s.hidden, s.q_dim, 1, False, "full", "h"),      # stands for the attention output exchange
-        GemvSpec("k", s.hidden, s.kv_dim, 1, False, "", "h"),
-        GemvSpec("v", s.hidden, s.kv_dim, 1, False, "", "h"),
-        GemvSpec("o", s.q_dim, s.hidden, 1, True, "full", "h"),
-        GemvSpec("gate_up", s.hidden, 2 * s.ffn, 2, False, "half", "h"),
-        GemvSpec("down", s.ffn, s.hidden, 1, True, "full", "f"),
+def layer_specs(s: ModelShape, fuse_qkv: bool = True) -> list[GemvSpec]:
+    """The quantized GEMVs of one layer, in launch order.
+
+    q, k and v read the same vector, so by default they run as one GEMV over the horizontally
+    concatenated weight q|k|v -- the transform the reference applies to gate|up
+    (HorizontalConcat derived parameter, src/optimize.rs:776-879; blocks never span columns, so
+    the concatenation is byte-identical to the three packed weights side by side).
+    """
+    if fuse_qkv:
+        attn = [GemvSpec("qkv", s.hidden, s.q_dim + 2 * s.kv_dim, (s.q_dim, s.kv_dim, s.kv_dim), False, "first", "h")]
+    else:
+        attn = [GemvSpec("q", s.hidden, s.q_dim, (s.q_dim,), False, "first", "h"),
+                GemvSpec("k", s.hidden, s.kv_dim, (s.kv_dim,), False, "", "h"),
+                GemvSpec("v", s.hidden, s.kv_dim, (s.kv_dim,), False, "", "h")]
+    return attn + [
+        GemvSpec("o", s.q_dim, s.hidden, (s.hidden,), True, "first", "h"),
+        GemvSpec("gate_up", s.hidden, 2 * s.ffn, (s.ffn, s.ffn), False, "first", "h"),
+        GemvSpec("down", s.ffn, s.hidden, (s.hidden,), True, "first", "f"),
     ]
 
 
 def head_spec(s: ModelShape) -> GemvSpec:
-    return GemvSpec("lm_head", s.hidden, s.vocab, 1, False, "full", "h")
+    return GemvSpec("lm_head", s.hidden, s.vocab, (s.vocab,), False, "first", "h")
 
 
 def gemv_bytes(fmt: int, m: int, k: int, n: int, residual: bool) -> int:
@@ -113,26 +123,29 @@ class DecodeGemvChain:
         import torch
         world, rank = self.world, self.rank
         n_loc = sp.n // world
-        gn = sp.n // sp.groups
-        # a seeded base of a few hundred columns, sliced for this rank, then tiled on the device
-        per_group_loc = gn // world
-        reps = 1
-        for r in range(max(1, per_group_loc // 256), 0, -1):
-            if per_group_loc % r == 0 and (per_group_loc // r) % 4 == 0:
-                reps = r
-                break
-        base_cols = per_group_loc // reps
-        parts = []
-        for g in range(sp.groups):
+        parts, widths = [], []
+        for g, gw in enumerate(sp.groups):
+            # this rank's slice of the group: a seeded base of a few hundred columns, tiled on the device
+            per_loc = gw // world
+            if gw % world != 0 or per_loc % 4 != 0:
+                raise ValueError(f"{sp.name}: group of {gw} columns cannot be split over {world} ranks in multiples of 4")
+            reps = 1
+            for r in range(max(1, per_loc // 256), 0, -1):
+                if per_loc % r == 0 and (per_loc // r) % 4 == 0:
+                    reps = r
+                    break
+            base_cols = per_loc // reps
             base = synth.synth_weights(self.fmt, sp.k, base_cols, seed * 7919 + rank * 131 + g)
             parts.append(synth.tile_columns(self.fmt, torch.from_numpy(base).to(self.device), sp.k, base_cols, reps))
-        if sp.groups == 1:
+            widths.append(per_loc)
+        if len(parts) == 1:
             w = parts[0]
         elif self.fmt == FMT_Q8:
             w = torch.cat(parts)
-        else:
-            nb = (sp.k // 32) * per_group_loc
-            w = torch.cat([p[: nb * 4] for p in parts] + [p[nb * 4:] for p in parts])
+        else:                                              # Q4: all headers first, then all nibbles
+            bpc = sp.k // 32
+            w = torch.cat([p[: bpc * wd * 4] for p, wd in zip(parts, widths)] +
+                          [p[bpc * wd * 4:] for p, wd in zip(parts, widths)])
         assert w.numel() == ops.packed_bytes(self.fmt, sp.k, n_loc)
         y = torch.zeros((self.m, n_loc), dtype=torch.float32, device=self.device)
         addend = None
@@ -141,7 +154,7 @@ class DecodeGemvChain:
         full = None
         gather_cols = 0
         if world > 1 and sp.gather:
-            gather_cols = n_loc if sp.gather == "full" else n_loc // sp.groups
+            gather_cols = widths[0]
             full = torch.zeros((world * self.m * gather_cols,), dtype=torch.float32, device=self.device)
         return {"spec": sp, "w": w, "y": y, "addend": addend, "full": full, "gather_cols": gather_cols, "n_loc": n_loc}
 

@@ -25,22 +25,32 @@ def shard_range(n: int, rank: int, world: int) -> tuple[int, int]:
     return rank * per, (rank + 1) * per
 
 
-def shard_packed(fmt: int, packed: np.ndarray, k: int, n: int, rank: int, world: int, groups: int = 1) -> np.ndarray:
+def _group_sizes(n: int, groups) -> list[int]:
+    if isinstance(groups, int):
+        if n % groups != 0:
+            raise ValueError("column groups must be equal")
+        return [n // groups] * groups
+    sizes = [int(g) for g in groups]
+    if sum(sizes) != n:
+        raise ValueError("group sizes must add up to N")
+    return sizes
+
+
+def shard_packed(fmt: int, packed: np.ndarray, k: int, n: int, rank: int, world: int, groups=1) -> np.ndarray:
     """This rank's columns of a packed [k, n] host weight, as one self-contained packed weight.
 
-    With groups > 1 the weight is a concatenation of `groups` equal column groups; the rank takes
-    its slice of each group and the slices are concatenated in group order.
+    `groups` is a count of equal column groups or a list of group widths (q|k|v, gate|up): the
+    rank takes its slice of each group and the slices are concatenated in group order.
     """
-    if n % groups != 0:
-        raise ValueError("column groups must be equal")
-    gn = n // groups
-    if (gn // world) % 4 != 0 or gn % world != 0:
-        raise ValueError(f"each rank's slice of a group must be a multiple of 4 columns (N={gn}, world={world})")
-    parts = []
-    for g in range(groups):
+    sizes = _group_sizes(n, groups)
+    parts, start = [], 0
+    for gn in sizes:
+        if gn % world != 0 or (gn // world) % 4 != 0:
+            raise ValueError(f"each rank's slice of a group must be a multiple of 4 columns (N={gn}, world={world})")
         n0, n1 = shard_range(gn, rank, world)
-        parts.append(ops.shard_columns(fmt, packed, k, n, g * gn + n0, g * gn + n1))
-    if groups == 1:
+        parts.append(ops.shard_columns(fmt, packed, k, n, start + n0, start + n1))
+        start += gn
+    if len(parts) == 1:
         return parts[0]
     return concat_columns(fmt, parts, k)
 
@@ -65,14 +75,17 @@ class GatherPlan:
     """Where each rank's slice lands in the gathered [m, n] output (row-major)."""
     n: int
     world: int
-    groups: int = 1
+    groups: object = 1          # count of equal groups, or a list of group widths
+
+    def sizes(self) -> list[int]:
+        return _group_sizes(self.n, self.groups)
 
     def columns(self, rank: int) -> np.ndarray:
-        gn = self.n // self.groups
-        out = []
-        for g in range(self.groups):
+        out, start = [], 0
+        for gn in self.sizes():
             n0, n1 = shard_range(gn, rank, self.world)
-            out.append(np.arange(g * gn + n0, g * gn + n1))
+            out.append(np.arange(start + n0, start + n1))
+            start += gn
         return np.concatenate(out)
 
 
@@ -92,11 +105,16 @@ def all_gather_columns(local, plan: GatherPlan, group=None, out=None):
         return local
     flat = torch.empty((world, m, per), dtype=local.dtype, device=local.device)
     dist.all_gather_into_tensor(flat.view(-1), local.contiguous().view(-1), group=group)
-    if plan.groups == 1:
+    sizes = plan.sizes()
+    if len(sizes) == 1:
         res = flat.permute(1, 0, 2).reshape(m, plan.n)
     else:
-        gper = per // plan.groups
-        res = flat.view(world, m, plan.groups, gper).permute(1, 2, 0, 3).reshape(m, plan.n)
+        pieces, off = [], 0
+        for gn in sizes:                                  # slice of group g from every rank, in rank order
+            w = gn // world
+            pieces.append(flat[:, :, off:off + w].permute(1, 0, 2).reshape(m, gn))
+            off += w
+        res = torch.cat(pieces, dim=1)
     if out is not None:
         out.copy_(res)
         return out

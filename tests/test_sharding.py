@@ -23,7 +23,7 @@ def test_synth_matches_oracle_generator():
 
 
 @pytest.mark.parametrize("fmt", [O.FMT_Q4, O.FMT_Q8])
-@pytest.mark.parametrize("groups", [1, 2])
+@pytest.mark.parametrize("groups", [1, 2, (32, 16, 16)])
 def test_shard_packed_selects_the_planned_columns(fmt, groups):
     k, n, world = 64, 64, 4
     w = synth.synth_weights(fmt, k, n, 3)
@@ -84,7 +84,7 @@ def _gloo_worker(rank, world, port, fmt, groups, m, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("groups,m", [(1, 1), (2, 1), (1, 3), (2, 2)])
+@pytest.mark.parametrize("groups,m", [(1, 1), (2, 1), (1, 3), (2, 2), ((32, 16, 16), 2)])
 def test_all_gather_reassembles_columns_gloo(groups, m):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")

@@ -211,6 +211,7 @@ def main():
     ap.add_argument("--model", choices=["qwen3-8b", "smollm2-135m"], default="qwen3-8b")
     ap.add_argument("--impl", choices=["mgq", "reference"], default="mgq")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--plan-kernel", action="store_true", help="run the token as one persistent plan kernel instead of one kernel per GEMV")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "mgq" else args.warmup
 
@@ -236,7 +237,8 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    chain = dc.DecodeGemvChain(shape, fmt, batch=args.batch, rank=rank, world=world, seed=0)
+    chain = dc.DecodeGemvChain(shape, fmt, batch=args.batch, rank=rank, world=world, seed=0,
+                               use_plan=args.plan_kernel)
     captured = chain.capture()
 
     def barrier():

@@ -53,6 +53,15 @@ typedef enum mgq_status {
 const char *mgq_last_error(void);
 const char *mgq_version(void);
 
+/* Runtime options, the counterpart of meganeura's ad-hoc environment switches
+ * (MEGANEURA_SERIAL_DISPATCH, src/runtime.rs:1703-1707).  0 means "automatic" for the tunables.
+ *   "gemv.serial_dispatch"      1: every GEMV starts only after its predecessor has finished
+ *                               (no programmatic dependent launch); also MGQ_SERIAL_DISPATCH=1
+ *   "gemv.columns_per_thread"   1, 2 or 4 columns per thread and pipeline stage
+ *   "gemv.ctas_per_sm"          CTAs per SM a GEMV grid is sized for (default 3)
+ *   "plan.columns_per_thread"   1, 2 or 4 for plans created afterwards (default 2: two CTAs per SM) */
+int mgq_set_option(const char *name, long value);
+
 /* ---- format: TensorType::size_bytes for quantized dtypes (src/graph.rs:52-68) ---------- */
 size_t mgq_packed_bytes(int fmt, size_t k, size_t n);
 
@@ -103,6 +112,34 @@ int mgq_matmul(int fmt, const void *a, int a_dtype, const void *w, const float *
  * the set_input -> step -> wait -> read_output round trip of a one-node session. */
 int mgq_matmul_host(int fmt, const void *a_host, int a_dtype, const void *w_dev, const float *addend_host,
                     float *c_host, uint32_t m, uint32_t k, uint32_t n);
+
+/* ---- plan kernel: a static list of single-row GEMVs run by ONE persistent cooperative launch.
+ * Stands in for Session::step replaying ExecutionPlan.dispatches in barrier groups inside one
+ * submission (src/runtime.rs:2843-2959; barrier groups 1202-1256).  The weight pipeline runs
+ * across op boundaries; op i starts reading its activations only after ops [0, wait_for) have
+ * completed on every CTA (wait_for = 0: no dependency; wait_for = i: depends on the op before it).
+ * All pointers are device pointers and must stay valid for the plan's lifetime.
+ * Limits: m = 1, 256 <= K <= 12288, K*N/32 a multiple of 4, 16-byte aligned w and x. */
+typedef struct mgq_plan mgq_plan;
+typedef struct mgq_plan_op {
+    int fmt;                 /* MGQ_FMT_Q4 / MGQ_FMT_Q8 */
+    const float *x;          /* [1, k] */
+    const void *w;           /* packed [k, n] */
+    const float *addend;     /* [1, n] or NULL */
+    float *y;                /* [1, n] */
+    uint32_t m, k, n;
+    uint32_t wait_for;       /* number of leading ops that must be complete before this one starts */
+} mgq_plan_op;
+
+int mgq_plan_create(const mgq_plan_op *ops, size_t count, mgq_plan **out);
+/* Enqueues the whole list as one kernel on `stream` (capturable in a CUDA graph). */
+int mgq_plan_launch(mgq_plan *plan, void *stream);
+/* Synchronises `stream` and returns MGQ_ERR_TIMEOUT if a grid barrier of an earlier launch gave
+ * up waiting (every device-side wait is bounded; results of such a launch are undefined). */
+int mgq_plan_check(mgq_plan *plan, void *stream);
+int mgq_plan_info(const mgq_plan *plan, uint32_t *grid, uint32_t *threads, uint32_t *columns_per_thread,
+                  size_t *smem_bytes);
+void mgq_plan_destroy(mgq_plan *plan);
 
 /* ---- Graph / Session surface (src/graph.rs:714-795, src/train.rs:380-389,
  *      src/runtime.rs:2327-2345, 2496-2550, 2612-2643, 2786-2791, 2835-2959).

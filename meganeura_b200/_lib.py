@@ -47,6 +47,7 @@ _szp = ctypes.POINTER(ctypes.c_size_t)
 SIGNATURES = {
     "mgq_last_error": (ctypes.c_char_p, []),
     "mgq_version": (ctypes.c_char_p, []),
+    "mgq_set_option": (_int, [ctypes.c_char_p, ctypes.c_long]),
     "mgq_packed_bytes": (_sz, [_int, _sz, _sz]),
     "mgq_quantize_q4": (_int, [_vp, _sz, _sz, _vp]),
     "mgq_quantize_q8": (_int, [_vp, _sz, _sz, _vp]),
@@ -61,6 +62,11 @@ SIGNATURES = {
     "mgq_gemm": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_matmul": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_matmul_host": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32]),
+    "mgq_plan_create": (_int, [_vp, _sz, ctypes.POINTER(_vp)]),
+    "mgq_plan_launch": (_int, [_vp, _vp]),
+    "mgq_plan_check": (_int, [_vp, _vp]),
+    "mgq_plan_info": (_int, [_vp, ctypes.POINTER(_u32), ctypes.POINTER(_u32), ctypes.POINTER(_u32), _szp]),
+    "mgq_plan_destroy": (None, [_vp]),
     "mgq_graph_new": (_vp, []),
     "mgq_graph_free": (None, [_vp]),
     "mgq_graph_input": (_int, [_vp, ctypes.c_char_p, _szp, _sz]),
@@ -89,6 +95,12 @@ for _name, (_res, _args) in SIGNATURES.items():
     _fn = getattr(lib, _name)
     _fn.restype = _res
     _fn.argtypes = _args
+
+
+class PlanOp(ctypes.Structure):
+    """mgq_plan_op"""
+    _fields_ = [("fmt", ctypes.c_int), ("x", _vp), ("w", _vp), ("addend", _vp), ("y", _vp),
+                ("m", _u32), ("k", _u32), ("n", _u32), ("wait_for", _u32)]
 
 
 def last_error() -> str:

@@ -1,6 +1,8 @@
 // C ABI entry points that touch the device: buffers, argument checking and kernel routing.
 #include <cuda_runtime.h>
 
+#include <cstring>
+
 #include "mgq_internal.h"
 
 namespace mgq {
@@ -64,6 +66,13 @@ int mgq_buffer_download(const void *dev, void *host, size_t bytes, void *stream)
     MGQ_CUDA(cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, s));
     MGQ_CUDA(cudaStreamSynchronize(s));
     return MGQ_OK;
+}
+
+int mgq_set_option(const char *name, long value)
+{
+    if (!name) return fail(MGQ_ERR_NULL, "null option name");
+    if (!std::strncmp(name, "plan.", 5)) return set_plan_option(name, value);
+    return set_gemv_option(name, value);
 }
 
 int mgq_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,

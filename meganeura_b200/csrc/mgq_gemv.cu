@@ -33,281 +33,67 @@
 #include <cuda_runtime.h>
 
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <vector>
 
+#include "mgq_gemv_device.cuh"
 #include "mgq_internal.h"
 
 namespace mgq {
 namespace {
 
-constexpr uint32_t kQ8WarpStage = 1152;       // 32 blocks * 36 B per warp and stage
-
-struct GemvParams {
-    const float *x;
-    const uint8_t *w;
-    const float *addend;
-    float *y;
-    uint32_t k, n, bpc;
-    uint32_t cpi;          // columns per iteration
-    uint32_t active;       // cpi * bpc threads carry a block (a multiple of 4)
-    uint32_t total_iters;  // ceil(n / cpi)
-    uint32_t red_shift;    // log2(lanes that finish one column sum)
-    uint32_t red_chunk;    // partials summed by each finishing lane = ceil(bpc / lanes)
-    unsigned long long num_blocks;
-#ifdef MGQ_GEMV_TRACE
-    unsigned long long *trace;   // [gridDim.x][4] globaltimer stamps: start, after dependency wait, first block done, end
-#endif
-};
-
-#ifdef MGQ_GEMV_TRACE
-__device__ __forceinline__ unsigned long long now_ns()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define MGQ_STAMP(p, slot) do { if ((p).trace && threadIdx.x == 0) (p).trace[blockIdx.x * 4 + (slot)] = now_ns(); } while (0)
-#else
-#define MGQ_STAMP(p, slot) do { } while (0)
-#endif
-
-__device__ __forceinline__ void cp_async16(void *smem, const void *gmem)
-{
-    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async4(void *smem, const void *gmem)
-{
-    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait()
-{
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
-}
-
-// Programmatic dependent launch: a GEMV launched with the stream-serialization attribute may
-// start while the previous kernel of the stream is still draining.  Everything before
-// grid_dependency_wait() must not touch memory that an earlier kernel writes: only the packed
-// weights (immutable after upload) are fetched there.
-__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
-__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
-
-// dp4a with mixed signedness (a: packed codes, b: packed activation bytes).
-__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c)
-{
-    int d;
-    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c)
-{
-    int d;
-    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-__device__ __forceinline__ int dp4a_su(uint32_t a, uint32_t b, int c)
-{
-    int d;
-    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c)
-{
-    int d;
-    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-
-// The 32 activations of one block as three byte planes, packed four to a word in the order
-// the codes come out of the packed weight words.
-struct XBlock {
-    uint32_t p0[8], p1[8], p2[8];   // plane 0, 1: unsigned bytes; plane 2: signed bytes
-    float inv;                      // 2^(E-21): turns the integer dot product back into x units
-    float sum;                      // plain f32 sum of the 32 activations (for Q4's "+ m")
-};
-
-// ORDER 0 (Q8): word j holds elements 4j .. 4j+3.
-// ORDER 1 (Q4): word 2j holds elements 8j+{0,2,4,6} (low nibbles of nibble word j),
-//               word 2j+1 holds elements 8j+{1,3,5,7} (high nibbles).
-template <int ORDER>
-__device__ __forceinline__ void load_x(const float *xrow, uint32_t b, XBlock &xb)
-{
-    const float4 *xp = reinterpret_cast<const float4 *>(xrow + 32u * b);
-    float v[32];
-#pragma unroll
-    for (int j = 0; j < 8; j++) {
-        const float4 t = __ldg(xp + j);
-        v[4 * j + 0] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
-    }
-    float amax = 0.f, s0 = 0.f, s1 = 0.f;
-#pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-        amax = fmaxf(amax, fmaxf(fabsf(v[i]), fabsf(v[i + 1])));
-        s0 += v[i];
-        s1 += v[i + 1];
-    }
-    xb.sum = s0 + s1;
-    // biased exponent of the largest magnitude, clamped so that both 2^(21-E) and 2^(E-21) are normal
-    uint32_t eb = (__float_as_uint(amax) >> 23) & 0xFFu;
-    const bool finite = eb != 0xFFu;
-    eb = min(max(eb, 24u), 254u);
-    const float scale = __uint_as_float((275u - eb) << 23);           // 2^(21-E)
-    xb.inv = finite ? __uint_as_float((eb - 21u) << 23) : __int_as_float(0x7FC00000);   // 2^(E-21), NaN for inf/NaN input
-    // x*scale + 1.5*2^23 leaves X + 2^22 in the low 23 mantissa bits (|X| <= 2^22): bytes 0..2 of the
-    // float's bit pattern are the planes, the top one offset by 64.
-    uint32_t bits[32];
-#pragma unroll
-    for (int i = 0; i < 32; i++) bits[i] = __float_as_uint(fmaf(v[i], scale, 12582912.f));
-#pragma unroll
-    for (int w = 0; w < 8; w++) {
-        int e0, e1, e2, e3;
-        if (ORDER == 0) { e0 = 4 * w; e1 = e0 + 1; e2 = e0 + 2; e3 = e0 + 3; }
-        else            { e0 = 8 * (w >> 1) + (w & 1); e1 = e0 + 2; e2 = e0 + 4; e3 = e0 + 6; }
-        const uint32_t a = bits[e0], bb = bits[e1], c = bits[e2], d = bits[e3];
-        xb.p0[w] = __byte_perm(__byte_perm(a, bb, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
-        xb.p1[w] = __byte_perm(__byte_perm(a, bb, 0x0051), __byte_perm(c, d, 0x0051), 0x5410);
-        const uint32_t top = __byte_perm(__byte_perm(a, bb, 0x0062), __byte_perm(c, d, 0x0062), 0x5410);
-        xb.p2[w] = (top + 0x40404040u) ^ 0x80808080u;                  // (u + 64) - 128 = u - 64 as int8; u <= 127: no carries
-    }
-}
-
-// Exact sum over one block of X[i] * code[i], returned in f32 (planes recombined with two FMAs).
-__device__ __forceinline__ float dot_q4(const uint4 &q, const XBlock &xb)
-{
-    const uint32_t wv[4] = {q.x, q.y, q.z, q.w};
-    int a0 = 0, a1 = 0, a2 = 0;
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        const uint32_t lo = wv[j] & 0x0F0F0F0Fu, hi = (wv[j] >> 4) & 0x0F0F0F0Fu;
-        a0 = dp4a_uu(lo, xb.p0[2 * j], a0);
-        a1 = dp4a_uu(lo, xb.p1[2 * j], a1);
-        a2 = dp4a_us(lo, xb.p2[2 * j], a2);
-        a0 = dp4a_uu(hi, xb.p0[2 * j + 1], a0);
-        a1 = dp4a_uu(hi, xb.p1[2 * j + 1], a1);
-        a2 = dp4a_us(hi, xb.p2[2 * j + 1], a2);
-    }
-    return fmaf((float)a2, 65536.f, fmaf((float)a1, 256.f, (float)a0));
-}
-
-// bp points at the 8 code words (int8 x 4) of a Q8 block.
-__device__ __forceinline__ float dot_q8(const uint32_t *bp, const XBlock &xb)
-{
-    int a0 = 0, a1 = 0, a2 = 0;
-#pragma unroll
-    for (int j = 0; j < 8; j++) {
-        const uint32_t c = bp[j];
-        a0 = dp4a_su(c, xb.p0[j], a0);
-        a1 = dp4a_su(c, xb.p1[j], a1);
-        a2 = dp4a_ss(c, xb.p2[j], a2);
-    }
-    return fmaf((float)a2, 65536.f, fmaf((float)a1, 256.f, (float)a0));
-}
-
-// Which column sum a thread finishes after each round; the same for every round, so it is
-// worked out once.  A round holds ROUND*cpi columns; each is finished by 2^red_shift
-// neighbouring lanes that first add up a contiguous run of red_chunk partials each.
-struct ReduceSlot {
-    uint32_t src;        // float offset of this lane's run inside one row of the staging array
-    uint32_t cnt;        // partials in the run (0: lane idle)
-    uint32_t iter;       // iteration inside the round the column belongs to
-    uint32_t cs;         // column inside that iteration
-    bool writer;         // lane that stores the finished sum
-    bool vec;            // run is float4-readable
-};
-
-template <int ROUND>
-__device__ __forceinline__ ReduceSlot make_slot(const GemvParams &p)
-{
-    const uint32_t T = blockDim.x, t = threadIdx.x;
-    const uint32_t R = 1u << p.red_shift;
-    const uint32_t slot = t >> p.red_shift, li = t & (R - 1);
-    ReduceSlot s{};
-    if (slot < ROUND * p.cpi) {
-        s.iter = slot / p.cpi;
-        s.cs = slot % p.cpi;
-        const uint32_t first = li * p.red_chunk;
-        s.cnt = first < p.bpc ? min(p.red_chunk, p.bpc - first) : 0u;
-        s.src = s.iter * T + s.cs * p.bpc + first;
-        s.writer = li == 0;
-        s.vec = (p.bpc % 4 == 0) && (p.red_chunk % 4 == 0);
-    }
-    return s;
-}
-
-template <int MT, int ROUND>
-__device__ __forceinline__ void reduce_store(const GemvParams &p, const ReduceSlot &slot, float *red,
-                                             const float (&part)[MT][ROUND], uint32_t it_base, uint32_t it_end)
-{
-    const uint32_t T = blockDim.x, t = threadIdx.x;
-#pragma unroll
-    for (int r = 0; r < MT; r++)
-#pragma unroll
-        for (int u = 0; u < ROUND; u++) red[(r * ROUND + u) * T + t] = part[r][u];
-    __syncthreads();
-#pragma unroll
-    for (int r = 0; r < MT; r++) {
-        const float *src = red + r * ROUND * T + slot.src;
-        float s = 0.f;
-        if (slot.vec) {
-            for (uint32_t j = 0; j < slot.cnt; j += 4) {
-                const float4 v = *reinterpret_cast<const float4 *>(src + j);
-                s += (v.x + v.y) + (v.z + v.w);
-            }
-        } else {
-            for (uint32_t j = 0; j < slot.cnt; j++) s += src[j];
-        }
-        for (uint32_t o = (1u << p.red_shift) >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        const uint32_t it = it_base + slot.iter;
-        const uint32_t col = it * p.cpi + slot.cs;
-        if (slot.writer && it < it_end && col < p.n) {
-            const size_t o = (size_t)r * p.n + col;
-            p.y[o] = p.addend ? s + p.addend[o] : s;
-        }
-    }
-}
+using namespace dev;
 
 // ------------------------------------------------------------------------------------ Q4
 
-template <int MT, int STAGES, int TMAX>
+// A "group" is cpi consecutive columns: one block for each of the `active` threads.  A CTA owns
+// the groups [g0, g1); a pipeline stage holds C consecutive groups, so a thread works on C
+// columns with the same activations before it touches the ring again.
+constexpr int kStages = 4;
+
+template <int MT, int C, int TMAX>
 __global__ void __launch_bounds__(TMAX) gemv_q4_kernel(const GemvParams p)
 {
+    constexpr int STAGES = kStages, ROUND = kStages * C;
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t T = blockDim.x, t = threadIdx.x;
-    uint4 *s_nib = reinterpret_cast<uint4 *>(smem) + t;                                   // [STAGES][T], own slot
-    uint32_t *s_hdr = reinterpret_cast<uint32_t *>(smem + (size_t)STAGES * T * 16) + t;   // [STAGES][T], own slot
-    float *s_red = reinterpret_cast<float *>(smem + (size_t)STAGES * T * 20);             // [2][MT][STAGES][T]
+    uint4 *s_nib = reinterpret_cast<uint4 *>(smem) + t;                                  // [STAGES*C][T], own slot
+    uint32_t *s_hdr = reinterpret_cast<uint32_t *>(smem + (size_t)ROUND * T * 16) + t;   // [STAGES*C][T], own slot
+    float *s_red = reinterpret_cast<float *>(smem + (size_t)ROUND * T * 20);             // [2][MT][ROUND][T]
     MGQ_STAMP(p, 0);
 
-    const uint32_t it0 = (uint32_t)((unsigned long long)blockIdx.x * p.total_iters / gridDim.x);
-    const uint32_t it1 = (uint32_t)((unsigned long long)(blockIdx.x + 1) * p.total_iters / gridDim.x);
-    const uint32_t n_it = it1 - it0;
+    const uint32_t g0 = (uint32_t)((unsigned long long)blockIdx.x * p.total_iters / gridDim.x);
+    const uint32_t g1 = (uint32_t)((unsigned long long)(blockIdx.x + 1) * p.total_iters / gridDim.x);
+    const uint32_t n_g = g1 - g0;
     const bool has_block = t < p.active;
     const uint32_t b = t % p.bpc, csub = t / p.bpc;
-    // iterations in which this thread has a column: all of them, except that the very last
-    // iteration of the matrix may hold fewer than cpi columns
-    uint32_t my_n = has_block ? n_it : 0u;
-    if (has_block && it1 == p.total_iters && n_it > 0 && (p.total_iters - 1) * p.cpi + csub >= p.n) my_n = n_it - 1;
+    // groups in which this thread has a column: all of them, except that the very last group of
+    // the matrix may hold fewer than cpi columns
+    uint32_t my_n = has_block ? n_g : 0u;
+    if (has_block && g1 == p.total_iters && n_g > 0 && (p.total_iters - 1) * p.cpi + csub >= p.n) my_n = n_g - 1;
 
-    const unsigned long long g0 = (unsigned long long)it0 * p.active + t;                // = col*bpc + b
-    const uint32_t *hdr_next = reinterpret_cast<const uint32_t *>(p.w) + g0;
-    const uint4 *nib_next = reinterpret_cast<const uint4 *>(p.w + p.num_blocks * 4) + g0;
+    const unsigned long long first = (unsigned long long)g0 * p.active + t;              // = col*bpc + b
+    const uint32_t *hdr_next = reinterpret_cast<const uint32_t *>(p.w) + first;
+    const uint4 *nib_next = reinterpret_cast<const uint4 *>(p.w + p.num_blocks * 4) + first;
     const uint32_t stride = p.active;
+    uint32_t g_next = 0;                                                                 // next group to fetch
 
-    auto issue = [&](int stage, bool ok) {
-        if (ok) {
-            cp_async16(s_nib + stage * T, nib_next);
-            cp_async4(s_hdr + stage * T, hdr_next);
+    auto issue = [&](int stage, bool checked) {
+#pragma unroll
+        for (int j = 0; j < C; j++) {
+            if (!checked || g_next + j < my_n) {
+                cp_async16(s_nib + (stage * C + j) * T, nib_next);
+                cp_async4(s_hdr + (stage * C + j) * T, hdr_next);
+            }
+            nib_next += stride;
+            hdr_next += stride;
         }
-        nib_next += stride;
-        hdr_next += stride;
+        g_next += C;
         cp_async_commit();
     };
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; s++) issue(s, (uint32_t)s < my_n);     // weights first: they depend on nothing
+    for (int s = 0; s < STAGES - 1; s++) issue(s, true);                    // weights first: they depend on nothing
     grid_launch_dependents();
     grid_dependency_wait();                                                 // x, addend and y belong to earlier kernels
     MGQ_STAMP(p, 1);
@@ -315,44 +101,36 @@ __global__ void __launch_bounds__(TMAX) gemv_q4_kernel(const GemvParams p)
     XBlock xb[MT];
 #pragma unroll
     for (int r = 0; r < MT; r++) load_x<1>(p.x + (size_t)r * p.k, b, xb[r]);
-    const ReduceSlot slot = make_slot<STAGES>(p);
+    const ReduceSlot slot = make_slot<ROUND>(p);
 
-    auto block_sum = [&](int stage, float (&out)[MT]) {
-        const uint4 q = s_nib[stage * T];
-        const uint32_t h = s_hdr[stage * T];
+    auto block_sum = [&](int idx, float (&out)[MT]) {
+        const uint4 q = s_nib[idx * T];
+        const uint32_t h = s_hdr[idx * T];
         const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&h));       // (d, m), IEEE
 #pragma unroll
         for (int r = 0; r < MT; r++) out[r] = fmaf(dm.x * xb[r].inv, dot_q4(q, xb[r]), dm.y * xb[r].sum);
     };
 
     uint32_t round = 0;
-    for (uint32_t i = 0; i < n_it; i += STAGES, round++) {
-        float part[MT][STAGES];
-        if (i + 2 * STAGES - 1 <= my_n) {                  // whole round and everything it prefetches is in range
+    for (uint32_t g = 0; g < n_g; g += ROUND, round++) {
+        float part[MT][ROUND];
+        const bool all_in_range = g + 2 * ROUND - C <= my_n;   // this round and everything it prefetches
 #pragma unroll
-            for (int u = 0; u < STAGES; u++) {
-                issue((u + STAGES - 1) % STAGES, true);
-                cp_async_wait<STAGES - 1>();
-                float out[MT];
-                block_sum(u, out);
+        for (int u = 0; u < STAGES; u++) {
+            issue((u + STAGES - 1) % STAGES, !all_in_range);
+            cp_async_wait<STAGES - 1>();
 #pragma unroll
-                for (int r = 0; r < MT; r++) part[r][u] = out[r];
-            }
-        } else {
-#pragma unroll
-            for (int u = 0; u < STAGES; u++) {
-                issue((u + STAGES - 1) % STAGES, i + u + STAGES - 1 < my_n);
-                cp_async_wait<STAGES - 1>();
+            for (int j = 0; j < C; j++) {
                 float out[MT];
 #pragma unroll
                 for (int r = 0; r < MT; r++) out[r] = 0.f;
-                if (i + u < my_n) block_sum(u, out);
+                if (all_in_range || g + u * C + j < my_n) block_sum(u * C + j, out);
 #pragma unroll
-                for (int r = 0; r < MT; r++) part[r][u] = out[r];
+                for (int r = 0; r < MT; r++) part[r][u * C + j] = out[r];
             }
         }
         if (round == 0) MGQ_STAMP(p, 2);
-        reduce_store<MT, STAGES>(p, slot, s_red + (size_t)(round & 1) * MT * STAGES * T, part, it0 + i, it1);
+        reduce_store<MT, ROUND>(p, slot, s_red + (size_t)(round & 1) * MT * ROUND * T, part, g0 + g, g1);
     }
     cp_async_wait<0>();
     MGQ_STAMP(p, 3);
@@ -360,57 +138,66 @@ __global__ void __launch_bounds__(TMAX) gemv_q4_kernel(const GemvParams p)
 
 // ------------------------------------------------------------------------------------ Q8
 
-template <int MT, int STAGES, int TMAX>
+template <int MT, int C, int TMAX>
 __global__ void __launch_bounds__(TMAX) gemv_q8_kernel(const GemvParams p)
 {
+    constexpr int STAGES = kStages, ROUND = kStages * C;
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t T = blockDim.x, t = threadIdx.x, lane = t & 31u, warp = t >> 5, W = T >> 5;
-    uint8_t *s_w = smem + (size_t)warp * STAGES * kQ8WarpStage;                         // this warp's ring
-    float *s_red = reinterpret_cast<float *>(smem + (size_t)W * STAGES * kQ8WarpStage);   // [2][MT][STAGES][T]
+    uint8_t *s_w = smem + (size_t)warp * ROUND * kQ8WarpStage;                          // this warp's ring [STAGES*C][1152]
+    float *s_red = reinterpret_cast<float *>(smem + (size_t)W * ROUND * kQ8WarpStage);    // [2][MT][ROUND][T]
+    MGQ_STAMP(p, 0);
 
-    const uint32_t it0 = (uint32_t)((unsigned long long)blockIdx.x * p.total_iters / gridDim.x);
-    const uint32_t it1 = (uint32_t)((unsigned long long)(blockIdx.x + 1) * p.total_iters / gridDim.x);
-    const uint32_t n_it = it1 - it0;
+    const uint32_t g0 = (uint32_t)((unsigned long long)blockIdx.x * p.total_iters / gridDim.x);
+    const uint32_t g1 = (uint32_t)((unsigned long long)(blockIdx.x + 1) * p.total_iters / gridDim.x);
+    const uint32_t n_g = g1 - g0;
     const bool has_block = t < p.active;
     const uint32_t b = t % p.bpc, csub = t / p.bpc;
-    uint32_t my_n = has_block ? n_it : 0u;
-    if (has_block && it1 == p.total_iters && n_it > 0 && (p.total_iters - 1) * p.cpi + csub >= p.n) my_n = n_it - 1;
+    uint32_t my_n = has_block ? n_g : 0u;
+    if (has_block && g1 == p.total_iters && n_g > 0 && (p.total_iters - 1) * p.cpi + csub >= p.n) my_n = n_g - 1;
 
-    // A warp owns 32 consecutive blocks of each iteration: `full` of them in every iteration, and
-    // `last` of them in the final iteration of the matrix (which may hold fewer columns).  active
-    // is a multiple of 4 and 4 blocks are 144 B, so every source address is 16-byte aligned.
+    // A warp owns 32 consecutive blocks of each group: `full` of them in every group, and `last`
+    // of them in the final group of the matrix (which may hold fewer columns).  active is a
+    // multiple of 4 and 4 blocks are 144 B, so every source address is 16-byte aligned.
     const uint32_t w0 = warp * 32u;
     const uint32_t full = p.active > w0 ? min(32u, p.active - w0) : 0u;
     const uint32_t last_live = (p.n - (p.total_iters - 1) * p.cpi) * p.bpc;
     const uint32_t last = last_live > w0 ? min(32u, last_live - w0) : 0u;
-    const bool ends_matrix = it1 == p.total_iters;
-    const uint8_t *src_next = p.w + ((unsigned long long)it0 * p.active + w0) * 36ull + 16u * lane;
+    const uint32_t last_group = g1 == p.total_iters ? n_g - 1 : 0xFFFFFFFFu;             // index inside this CTA's range
+    const uint8_t *src_next = p.w + ((unsigned long long)g0 * p.active + w0) * 36ull + 16u * lane;
     const uint32_t stride = p.active * 36u;
+    uint32_t g_next = 0;
 
-    auto issue = [&](int stage, uint32_t iter, bool in_range) {       // iter: index inside this CTA's range
-        if (in_range) {
-            const uint32_t cnt = (ends_matrix && iter == n_it - 1) ? last : full;
-            const uint32_t pieces = (cnt * 36u + 15u) >> 4;
-            uint8_t *dst = s_w + stage * kQ8WarpStage + 16u * lane;
-            if (lane < pieces) cp_async16(dst, src_next);
-            if (lane + 32u < pieces) cp_async16(dst + 512, src_next + 512);
-            if (lane + 64u < pieces) cp_async16(dst + 1024, src_next + 1024);
+    auto issue = [&](int stage) {
+#pragma unroll
+        for (int j = 0; j < C; j++) {
+            const uint32_t gi = g_next + j;
+            if (gi < n_g) {
+                const uint32_t cnt = gi == last_group ? last : full;
+                const uint32_t pieces = (cnt * 36u + 15u) >> 4;
+                uint8_t *dst = s_w + (stage * C + j) * kQ8WarpStage + 16u * lane;
+                if (lane < pieces) cp_async16(dst, src_next);
+                if (lane + 32u < pieces) cp_async16(dst + 512, src_next + 512);
+                if (lane + 64u < pieces) cp_async16(dst + 1024, src_next + 1024);
+            }
+            src_next += stride;
         }
-        src_next += stride;
+        g_next += C;
         cp_async_commit();
     };
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; s++) issue(s, (uint32_t)s, (uint32_t)s < n_it);
+    for (int s = 0; s < STAGES - 1; s++) issue(s);
     grid_launch_dependents();
     grid_dependency_wait();
+    MGQ_STAMP(p, 1);
 
     XBlock xb[MT];
 #pragma unroll
     for (int r = 0; r < MT; r++) load_x<0>(p.x + (size_t)r * p.k, b, xb[r]);
-    const ReduceSlot slot = make_slot<STAGES>(p);
+    const ReduceSlot slot = make_slot<ROUND>(p);
 
-    auto block_sum = [&](int stage, float (&out)[MT]) {
-        const uint32_t *bp = reinterpret_cast<const uint32_t *>(s_w + stage * kQ8WarpStage + 36u * lane);
+    auto block_sum = [&](int idx, float (&out)[MT]) {
+        const uint32_t *bp = reinterpret_cast<const uint32_t *>(s_w + idx * kQ8WarpStage + 36u * lane);
         const uint32_t sw = bp[0];
         const float scale = __half2float(__ushort_as_half((unsigned short)(sw & 0xFFFFu)));
 #pragma unroll
@@ -418,24 +205,29 @@ __global__ void __launch_bounds__(TMAX) gemv_q8_kernel(const GemvParams p)
     };
 
     uint32_t round = 0;
-    for (uint32_t i = 0; i < n_it; i += STAGES, round++) {
-        float part[MT][STAGES];
+    for (uint32_t g = 0; g < n_g; g += ROUND, round++) {
+        float part[MT][ROUND];
 #pragma unroll
         for (int u = 0; u < STAGES; u++) {
             __syncwarp();                                   // every lane is done reading the stage refilled next
-            issue((u + STAGES - 1) % STAGES, i + u + STAGES - 1, i + u + STAGES - 1 < n_it);
+            issue((u + STAGES - 1) % STAGES);
             cp_async_wait<STAGES - 1>();
             __syncwarp();                                   // the other lanes' copies for this stage are visible
-            float out[MT];
 #pragma unroll
-            for (int r = 0; r < MT; r++) out[r] = 0.f;
-            if (i + u < my_n) block_sum(u, out);
+            for (int j = 0; j < C; j++) {
+                float out[MT];
 #pragma unroll
-            for (int r = 0; r < MT; r++) part[r][u] = out[r];
+                for (int r = 0; r < MT; r++) out[r] = 0.f;
+                if (g + u * C + j < my_n) block_sum(u * C + j, out);
+#pragma unroll
+                for (int r = 0; r < MT; r++) part[r][u * C + j] = out[r];
+            }
         }
-        reduce_store<MT, STAGES>(p, slot, s_red + (size_t)(round & 1) * MT * STAGES * T, part, it0 + i, it1);
+        if (round == 0) MGQ_STAMP(p, 2);
+        reduce_store<MT, ROUND>(p, slot, s_red + (size_t)(round & 1) * MT * ROUND * T, part, g0 + g, g1);
     }
     cp_async_wait<0>();
+    MGQ_STAMP(p, 3);
 }
 
 // ------------------------------------------------------------------------------ generic path
@@ -491,11 +283,18 @@ __global__ void __launch_bounds__(256) gemv_generic_kernel(const GemvParams p, u
 // ------------------------------------------------------------------------------ launch logic
 
 struct Config {
-    uint32_t threads, cpi, red_shift, red_chunk;
-    int stages;
+    uint32_t threads, cpi, cols_per_thread, red_shift, red_chunk;
 };
 
-// Largest column count per iteration that fits `threads` and keeps cpi*bpc a multiple of 4
+// Tunables (0 = automatic), settable through mgq_set_option.
+struct Tuning {
+    int cols_per_thread = 0;   // "gemv.columns_per_thread": 1, 2 or 4
+    int ctas_per_sm = 0;       // "gemv.ctas_per_sm"
+    int serial = -1;           // "gemv.serial_dispatch": 1 turns programmatic dependent launch off
+};
+Tuning g_tuning;
+
+// Largest column count per group that fits `threads` and keeps cpi*bpc a multiple of 4
 // (so that a Q8 warp's 36-byte blocks always start on a 16-byte boundary).
 uint32_t columns_for(uint32_t threads, uint32_t bpc)
 {
@@ -504,8 +303,18 @@ uint32_t columns_for(uint32_t threads, uint32_t bpc)
     return cpi - cpi % need;
 }
 
-// Depends on K only, so that a column's summation order is the same for every N.
-Config choose_config(uint32_t bpc)
+size_t smem_bytes(int fmt, uint32_t threads, int c, int mt)
+{
+    const size_t round = (size_t)kStages * c;
+    const size_t red = 2 * mt * round * threads * sizeof(float);
+    if (fmt == MGQ_FMT_Q4) return round * threads * 20 + red;
+    return (size_t)(threads / 32) * round * kQ8WarpStage + red;
+}
+
+// Thread count and summation order depend on K only, so that a column's result is the same for
+// every N (column shards reproduce the unsharded result bit for bit).  The number of columns a
+// thread handles per stage depends on N, but does not change any sum.
+Config choose_config(int fmt, uint32_t bpc, uint32_t n, int mt, int sms)
 {
     Config c{};
     if (bpc <= 256) {
@@ -520,36 +329,58 @@ Config choose_config(uint32_t bpc)
         c.threads = (bpc + 31u) & ~31u;
     }
     c.cpi = columns_for(c.threads, bpc);
-    c.stages = c.threads <= 512 ? 8 : 4;
-    // finishing lanes per column: a power of two, at most 32, with stages*cpi*lanes <= threads
-    const uint32_t slots = (uint32_t)c.stages * c.cpi;
+    const uint32_t groups = (n + c.cpi - 1) / c.cpi;
+    // columns per thread and stage: as many as keep every CTA of a two-per-SM grid busy, fit
+    // in ~100 KB of shared memory and leave one finishing lane per column of a round
+    int cols = 1;
+    for (int cand : {2}) {
+        if (g_tuning.cols_per_thread && cand != g_tuning.cols_per_thread) continue;
+        if (c.threads > 512) continue;
+        if ((uint32_t)(kStages * cand) * c.cpi > c.threads) continue;
+        if (smem_bytes(fmt, c.threads, cand, mt) > 100 * 1024) continue;
+        if (!g_tuning.cols_per_thread && groups / cand < 3u * (uint32_t)sms) continue;
+        cols = cand;
+        break;
+    }
+    c.cols_per_thread = (uint32_t)cols;
+    // finishing lanes per column: a power of two, at most 32, sized for the widest round
+    // (4 columns per thread) whatever `cols` is, so that the summation order depends on K only
+    const uint32_t slots = (uint32_t)(kStages * 4) * c.cpi;
     c.red_shift = 0;
     while (c.red_shift < 5 && (slots << (c.red_shift + 1)) <= c.threads && (2u << c.red_shift) <= bpc) c.red_shift++;
+    // (when even one lane per column does not fit the widest round, `cols` was capped above)
     const uint32_t lanes = 1u << c.red_shift;
     c.red_chunk = (bpc + lanes - 1) / lanes;
     if (c.red_chunk % 4 != 0 && bpc % 4 == 0 && c.red_chunk > 4) c.red_chunk = (c.red_chunk + 3u) & ~3u;
     return c;
 }
 
-size_t smem_bytes(int fmt, const Config &c, int mt)
-{
-    const size_t red = (size_t)2 * mt * c.stages * c.threads * sizeof(float);
-    if (fmt == MGQ_FMT_Q4) return (size_t)c.stages * c.threads * 20 + red;
-    return (size_t)(c.threads / 32) * c.stages * kQ8WarpStage + red;
-}
-
 using KernelFn = void (*)(const GemvParams);
+
+template <int MT, int C>
+KernelFn pick_by_threads(int fmt, uint32_t threads)
+{
+    if (fmt == MGQ_FMT_Q4) {
+        if (threads <= 256) return gemv_q4_kernel<MT, C, 256>;
+        if (threads <= 512) return gemv_q4_kernel<MT, C, 512>;
+        return nullptr;
+    }
+    if (threads <= 256) return gemv_q8_kernel<MT, C, 256>;
+    if (threads <= 512) return gemv_q8_kernel<MT, C, 512>;
+    return nullptr;
+}
 
 KernelFn pick_kernel(int fmt, int mt, const Config &c)
 {
-    if (fmt == MGQ_FMT_Q4) {
-        if (c.threads <= 256) return mt == 2 ? gemv_q4_kernel<2, 8, 256> : gemv_q4_kernel<1, 8, 256>;
-        if (c.threads <= 512) return mt == 2 ? gemv_q4_kernel<2, 8, 512> : gemv_q4_kernel<1, 8, 512>;
-        return mt == 1 ? gemv_q4_kernel<1, 4, 1024> : nullptr;
+    if (c.threads > 512) {
+        if (mt != 1 || c.cols_per_thread != 1) return nullptr;
+        return fmt == MGQ_FMT_Q4 ? (KernelFn)gemv_q4_kernel<1, 1, 1024> : (KernelFn)gemv_q8_kernel<1, 1, 1024>;
     }
-    if (c.threads <= 256) return mt == 2 ? gemv_q8_kernel<2, 8, 256> : gemv_q8_kernel<1, 8, 256>;
-    if (c.threads <= 512) return mt == 2 ? gemv_q8_kernel<2, 8, 512> : gemv_q8_kernel<1, 8, 512>;
-    return mt == 1 ? gemv_q8_kernel<1, 4, 1024> : nullptr;
+    switch (c.cols_per_thread) {
+        case 4: return mt == 2 ? pick_by_threads<2, 4>(fmt, c.threads) : pick_by_threads<1, 4>(fmt, c.threads);
+        case 2: return mt == 2 ? pick_by_threads<2, 2>(fmt, c.threads) : pick_by_threads<1, 2>(fmt, c.threads);
+        default: return mt == 2 ? pick_by_threads<2, 1>(fmt, c.threads) : pick_by_threads<1, 1>(fmt, c.threads);
+    }
 }
 
 struct DeviceInfo {
@@ -606,6 +437,7 @@ int kernel_occupancy(KernelFn fn, uint32_t threads, size_t smem, int &occ)
 // switch (src/runtime.rs:1703-1707).
 bool overlap_allowed()
 {
+    if (g_tuning.serial >= 0) return g_tuning.serial == 0;
     static const bool allowed = [] {
         const char *v = std::getenv("MGQ_SERIAL_DISPATCH");
         return !(v && v[0] == '1');
@@ -622,6 +454,22 @@ unsigned long long *g_trace = nullptr;
 #ifdef MGQ_GEMV_TRACE
 extern "C" void mgq_debug_set_trace(unsigned long long *dev_buffer) { g_trace = dev_buffer; }
 #endif
+
+int set_gemv_option(const char *name, long value)
+{
+    if (!std::strcmp(name, "gemv.columns_per_thread")) {
+        if (value != 0 && value != 1 && value != 2 && value != 4) return fail(MGQ_ERR_SHAPE, "%s must be 0, 1, 2 or 4", name);
+        g_tuning.cols_per_thread = (int)value;
+    } else if (!std::strcmp(name, "gemv.ctas_per_sm")) {
+        if (value < 0 || value > 32) return fail(MGQ_ERR_SHAPE, "%s out of range", name);
+        g_tuning.ctas_per_sm = (int)value;
+    } else if (!std::strcmp(name, "gemv.serial_dispatch")) {
+        g_tuning.serial = value < 0 ? -1 : (value ? 1 : 0);
+    } else {
+        return fail(MGQ_ERR_NAME, "unknown option: %s", name);
+    }
+    return MGQ_OK;
+}
 
 int launch_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
                 uint32_t m, uint32_t k, uint32_t n, void *stream_v)
@@ -644,31 +492,34 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
         return MGQ_OK;
     }
 
-    const Config cfg = choose_config(bpc);
-    p.cpi = cfg.cpi;
-    p.active = cfg.cpi * bpc;
-    p.red_shift = cfg.red_shift;
-    p.red_chunk = cfg.red_chunk;
-    p.total_iters = (n + cfg.cpi - 1) / cfg.cpi;
     DeviceInfo di;
     if (int rc = device_info(di)) return rc;
 
     // Rows are processed two at a time (their activations live in registers); more rows re-read W.
     for (uint32_t r0 = 0; r0 < m;) {
-        int mt = (m - r0 >= 2 && cfg.threads <= 512) ? 2 : 1;
+        const int mt = (m - r0 >= 2 && bpc <= 512) ? 2 : 1;
+        const Config cfg = choose_config(fmt, bpc, n, mt, di.sms);
+        p.cpi = cfg.cpi;
+        p.active = cfg.cpi * bpc;
+        p.red_shift = cfg.red_shift;
+        p.red_chunk = cfg.red_chunk;
+        p.total_iters = (n + cfg.cpi - 1) / cfg.cpi;
         KernelFn fn = pick_kernel(fmt, mt, cfg);
         if (!fn) return fail(MGQ_ERR_SHAPE, "no GEMV kernel for K=%u", k);
-        const size_t smem = smem_bytes(fmt, cfg, mt);
+        const size_t smem = smem_bytes(fmt, cfg.threads, (int)cfg.cols_per_thread, mt);
         int occ = 0;
         if (int rc = kernel_occupancy(fn, cfg.threads, smem, occ)) return rc;
-        uint32_t grid = (uint32_t)di.sms * (uint32_t)occ;
-        if (grid > p.total_iters) grid = p.total_iters;
+        int per_sm = g_tuning.ctas_per_sm > 0 ? g_tuning.ctas_per_sm : 3;
+        if (per_sm > occ) per_sm = occ;
+        uint32_t grid = (uint32_t)di.sms * (uint32_t)per_sm;
+        const uint32_t stages_total = (p.total_iters + cfg.cols_per_thread - 1) / cfg.cols_per_thread;
+        if (grid > stages_total) grid = stages_total;
         p.x = x + (size_t)r0 * k;
         p.addend = addend ? addend + (size_t)r0 * n : nullptr;
         p.y = y + (size_t)r0 * n;
 #ifdef MGQ_GEMV_TRACE
         p.trace = g_trace;
-        if (g_trace) g_trace += (size_t)grid * 4;
+        if (g_trace) g_trace += (size_t)4096 * 4;
 #endif
         cudaLaunchConfig_t lc{};
         lc.gridDim = dim3(grid, 1, 1);

@@ -19,6 +19,8 @@ inline bool is_quant(int fmt) { return fmt == MGQ_FMT_Q4 || fmt == MGQ_FMT_Q8; }
 // Launchers implemented in the .cu files (all pointers are device pointers).
 int launch_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
                 uint32_t m, uint32_t k, uint32_t n, void *stream);
+int set_gemv_option(const char *name, long value);
+int set_plan_option(const char *name, long value);
 int launch_gemm(int fmt, const void *a, int a_dtype, const void *w, const float *addend, float *c,
                 uint32_t m, uint32_t k, uint32_t n, void *stream);
 

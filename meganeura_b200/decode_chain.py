@@ -94,7 +94,7 @@ class DecodeGemvChain:
     """Device-resident column shards of every projection + the per-token launch sequence."""
 
     def __init__(self, shape: ModelShape, fmt: int = FMT_Q4, batch: int = 1, rank: int = 0, world: int = 1,
-                 layers: int | None = None, seed: int = 0, device=None, group=None):
+                 layers: int | None = None, seed: int = 0, device=None, group=None, use_plan: bool | None = None):
         import torch
         if fmt not in (FMT_Q4, FMT_Q8):
             raise ValueError("fmt must be Q4 or Q8")
@@ -104,6 +104,10 @@ class DecodeGemvChain:
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.launches_per_step = 0
         self.graph = None
+        self.plan = None
+        # use_plan=True runs the token as one persistent kernel (mgq_plan_*); the default is one
+        # kernel per GEMV chained by programmatic dependent launch, which is currently faster
+        self.use_plan = bool(use_plan) and world == 1 and batch == 1
         gen = torch.Generator(device="cpu").manual_seed(1000 + seed)
         # fixed activations (replicated on every rank) and residual slices
         self.x = {"h": torch.randn((batch, shape.hidden), generator=gen).to(self.device),
@@ -160,8 +164,20 @@ class DecodeGemvChain:
 
     # ---------------------------------------------------------------- execution
 
+    def _build_plan(self):
+        # every GEMV consumes (a function of) its predecessor's output in the model, so each op
+        # waits for the one before it
+        self.plan = ops.Plan([(self.fmt, self.x[op["spec"].src], op["w"], op["addend"], op["y"],
+                               op["spec"].k, op["n_loc"], i) for i, op in enumerate(self.ops_list)])
+
     def _launch_all(self):
         import torch.distributed as dist
+        if self.use_plan:
+            if self.plan is None:
+                self._build_plan()
+            self.plan.launch()
+            self.launches_per_step = 1
+            return 1
         count = 0
         for op in self.ops_list:
             sp = op["spec"]

@@ -10,6 +10,11 @@ from . import _lib
 from ._lib import A_BF16, A_F32, FMT_Q4, FMT_Q8, check, lib
 
 
+def set_option(name: str, value: int) -> None:
+    """Runtime option of the library (mgq_set_option), e.g. "gemv.serial_dispatch"."""
+    check(lib.mgq_set_option(name.encode(), int(value)))
+
+
 def packed_bytes(fmt: int, k: int, n: int) -> int:
     return int(lib.mgq_packed_bytes(fmt, k, n))
 
@@ -76,6 +81,44 @@ def matmul(fmt: int, a, w, k: int, n: int, addend=None, out=None, stream=None, r
     return out
 
 
+class Plan:
+    """A static list of single-row GEMVs executed by one persistent kernel (mgq_plan_*).
+
+    ops: iterable of (fmt, x, w, addend_or_None, y, k, n, wait_for) with torch CUDA tensors; the
+    tensors are kept alive by the plan.
+    """
+
+    def __init__(self, ops_list):
+        import ctypes
+        self._keep = []
+        arr = (_lib.PlanOp * len(ops_list))()
+        for i, (fmt, x, w, addend, y, k, n, wait_for) in enumerate(ops_list):
+            self._keep.append((x, w, addend, y))
+            arr[i] = _lib.PlanOp(fmt, x.data_ptr(), w.data_ptr(), addend.data_ptr() if addend is not None else None,
+                                 y.data_ptr(), 1, k, n, wait_for)
+        handle = ctypes.c_void_p()
+        check(lib.mgq_plan_create(arr, len(ops_list), ctypes.byref(handle)))
+        self._h = handle
+        self.count = len(ops_list)
+
+    def launch(self, stream=None) -> None:
+        check(lib.mgq_plan_launch(self._h, _stream_ptr(stream)))
+
+    def check(self, stream=None) -> None:
+        check(lib.mgq_plan_check(self._h, _stream_ptr(stream)))
+
+    def info(self) -> dict:
+        import ctypes
+        g, t, c, s = ctypes.c_uint32(), ctypes.c_uint32(), ctypes.c_uint32(), ctypes.c_size_t()
+        check(lib.mgq_plan_info(self._h, ctypes.byref(g), ctypes.byref(t), ctypes.byref(c), ctypes.byref(s)))
+        return {"grid": g.value, "threads": t.value, "columns_per_thread": c.value, "smem_bytes": s.value}
+
+    def __del__(self):
+        if getattr(self, "_h", None) and lib is not None:
+            lib.mgq_plan_destroy(self._h)
+            self._h = None
+
+
 def matmul_host(fmt: int, a: np.ndarray, w_dev_ptr: int, k: int, n: int, addend: np.ndarray | None = None) -> np.ndarray:
     """Host activations in, host result out, device-resident weight (mgq_matmul_host)."""
     a = np.ascontiguousarray(a, dtype=np.float32).reshape(-1, k)
@@ -89,6 +132,6 @@ def matmul_host(fmt: int, a: np.ndarray, w_dev_ptr: int, k: int, n: int, addend:
     return out
 
 
-__all__ = ["packed_bytes", "quantize", "dequantize", "shard_columns", "matmul", "matmul_host",
+__all__ = ["Plan", "set_option", "packed_bytes", "quantize", "dequantize", "shard_columns", "matmul", "matmul_host",
            "FMT_Q4", "FMT_Q8", "A_F32", "A_BF16"]
 _ = _lib

@@ -308,8 +308,10 @@ def main():
 
 
 # DRAM bytes per launch of the GEMV kernel (dram__bytes_read.sum + dram__bytes_write.sum averaged
-# over the launches of one token, single ncu pass); the capture is summarised under profiles/.
-NCU_TRAFFIC = {"q4": None, "q8": None}
+# over 298 launches of the default workload, single ncu pass; summary:
+# profiles/gemv_q4_qwen3_decode_launch_list.md).  Only meaningful for the default Qwen3-8B-shaped
+# Q4 workload with one launch per GEMV.
+NCU_TRAFFIC = {"q4": 32620000, "q8": None}
 
 if __name__ == "__main__":
     main()

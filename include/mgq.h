@@ -59,7 +59,8 @@ const char *mgq_version(void);
  *                               (no programmatic dependent launch); also MGQ_SERIAL_DISPATCH=1
  *   "gemv.columns_per_thread"   1, 2 or 4 columns per thread and pipeline stage
  *   "gemv.ctas_per_sm"          CTAs per SM a GEMV grid is sized for (default 3)
- *   "plan.columns_per_thread"   1, 2 or 4 for plans created afterwards (default 2: two CTAs per SM) */
+ *   "plan.columns_per_thread"   1, 2 or 4 for plans created afterwards (default 2: two CTAs per SM)
+ *   "gemm.force_tiled"          1: never use the tcgen05 kernel (CUDA-core tiled kernel only) */
 int mgq_set_option(const char *name, long value);
 
 /* ---- format: TensorType::size_bytes for quantized dtypes (src/graph.rs:52-68) ---------- */
@@ -99,9 +100,16 @@ int mgq_gemv(int fmt, const float *x, const void *w, const float *addend, float 
 
 /* c[m,n] = a[m,k] . dequant(w)[k,n] (+ addend[m,n]); a is f32 or bf16 row-major, c is f32.
  * Stands in for the MatMul / FusedMatMulAdd dispatches with a quantized weight_format
- * (src/compile.rs:1408-1419, 1511-1522; src/shaders/matmul.wgsl:28-109). */
+ * (src/compile.rs:1408-1419, 1511-1522; src/shaders/matmul.wgsl:28-109).
+ * bf16 activations with m >= 64 and k % 128 == 0 run on the tensor cores (tcgen05, TMEM
+ * accumulator, TMA-fed activations, weights dequantized into bf16 hi+lo operand tiles); every
+ * other case runs the register-tiled CUDA-core kernel. */
 int mgq_gemm(int fmt, const void *a, int a_dtype, const void *w, const float *addend, float *c,
              uint32_t m, uint32_t k, uint32_t n, void *stream);
+
+/* Reports (and clears) a device-side timeout: every wait inside the tensor-core GEMM is bounded and
+ * raises a device error word when it runs out instead of hanging.  Synchronises the device. */
+int mgq_device_status(void);
 
 /* Routing wrapper: mgq_gemv when m <= MGQ_GEMV_MAX_M (f32 activations), else mgq_gemm. */
 int mgq_matmul(int fmt, const void *a, int a_dtype, const void *w, const float *addend, float *c,

@@ -58,6 +58,7 @@ SIGNATURES = {
     "mgq_buffer_destroy": (_int, [_vp]),
     "mgq_buffer_upload": (_int, [_vp, _vp, _sz, _vp]),
     "mgq_buffer_download": (_int, [_vp, _vp, _sz, _vp]),
+    "mgq_device_status": (_int, []),
     "mgq_gemv": (_int, [_int, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_gemm": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_matmul": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),

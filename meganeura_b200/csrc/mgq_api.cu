@@ -72,8 +72,11 @@ int mgq_set_option(const char *name, long value)
 {
     if (!name) return fail(MGQ_ERR_NULL, "null option name");
     if (!std::strncmp(name, "plan.", 5)) return set_plan_option(name, value);
+    if (!std::strncmp(name, "gemm.", 5)) return set_gemm_option(name, value);
     return set_gemv_option(name, value);
 }
+
+int mgq_device_status(void) { return tc_device_status(); }
 
 int mgq_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
              uint32_t m, uint32_t k, uint32_t n, void *stream)

@@ -12,6 +12,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cstring>
+
 #include "mgq_internal.h"
 
 namespace mgq {
@@ -110,9 +112,18 @@ __global__ void __launch_bounds__(256) gemm_tiled_kernel(const void *__restrict_
 
 }  // namespace
 
+static int g_force_tiled = 0;
+bool force_tiled() { return g_force_tiled != 0; }
+int set_gemm_option(const char *name, long value)
+{
+    if (!std::strcmp(name, "gemm.force_tiled")) { g_force_tiled = value ? 1 : 0; return MGQ_OK; }
+    return fail(MGQ_ERR_NAME, "unknown option: %s", name);
+}
+
 int launch_gemm(int fmt, const void *a, int a_dtype, const void *w, const float *addend, float *c,
                 uint32_t m, uint32_t k, uint32_t n, void *stream_v)
 {
+    if (gemm_tc_eligible(a_dtype, m, k, n, a) && !force_tiled()) return launch_gemm_tc(fmt, a, w, addend, c, m, k, n, stream_v);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM, 1), block(256, 1, 1);
     const uint8_t *w8 = static_cast<const uint8_t *>(w);

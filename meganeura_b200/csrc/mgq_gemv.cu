@@ -509,10 +509,14 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
         const size_t smem = smem_bytes(fmt, cfg.threads, (int)cfg.cols_per_thread, mt);
         int occ = 0;
         if (int rc = kernel_occupancy(fn, cfg.threads, smem, occ)) return rc;
+        const uint32_t stages_total = (p.total_iters + cfg.cols_per_thread - 1) / cfg.cols_per_thread;
+        // 3 CTAs per SM leave room for the next GEMV's CTAs to become resident and prefetch while this
+        // one drains; a long stream (>= 64 stages per CTA even at full occupancy) is better served by
+        // every warp the SM can hold
         int per_sm = g_tuning.ctas_per_sm > 0 ? g_tuning.ctas_per_sm : 3;
+        if (!g_tuning.ctas_per_sm && stages_total >= 64u * (uint32_t)di.sms * (uint32_t)occ) per_sm = occ;
         if (per_sm > occ) per_sm = occ;
         uint32_t grid = (uint32_t)di.sms * (uint32_t)per_sm;
-        const uint32_t stages_total = (p.total_iters + cfg.cols_per_thread - 1) / cfg.cols_per_thread;
         if (grid > stages_total) grid = stages_total;
         p.x = x + (size_t)r0 * k;
         p.addend = addend ? addend + (size_t)r0 * n : nullptr;

@@ -21,8 +21,16 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
                 uint32_t m, uint32_t k, uint32_t n, void *stream);
 int set_gemv_option(const char *name, long value);
 int set_plan_option(const char *name, long value);
+int set_gemm_option(const char *name, long value);
+bool force_tiled();
 int launch_gemm(int fmt, const void *a, int a_dtype, const void *w, const float *addend, float *c,
                 uint32_t m, uint32_t k, uint32_t n, void *stream);
+
+// Tensor-core GEMM (mgq_gemm_tc.cu): bf16 activations, M >= 64, K % 128 == 0.
+bool gemm_tc_eligible(int a_dtype, uint32_t m, uint32_t k, uint32_t n, const void *a);
+int launch_gemm_tc(int fmt, const void *a, const void *w, const float *addend, float *c,
+                   uint32_t m, uint32_t k, uint32_t n, void *stream);
+int tc_device_status();
 
 }  // namespace mgq
 

@@ -1,0 +1,115 @@
+"""Single-kernel timing cases (also the commands the ncu summaries under profiles/ were made with).
+
+    python -m meganeura_b200.kernel_cases gemv q4 4096x151936 [--launches 3] [--rows 1]
+    python -m meganeura_b200.kernel_cases gemm q8 512x4096x14336 [--launches 3]
+    python -m meganeura_b200.kernel_cases sweep q4            # the SmolLM2-135M decode shapes
+
+`gemv` rotates through enough distinct weight copies to exceed L2 several times over and replays
+the launches from a CUDA graph, so the printed GB/s is a streaming (cold-cache) figure; with
+--launches N it only issues N plain launches (what a profiler capture wants).
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from . import ops, synth
+from ._lib import FMT_Q4, FMT_Q8
+
+SMOLLM2_SHAPES = [(576, 576), (576, 192), (576, 1536), (1536, 576), (576, 49152), (576, 3072)]
+
+
+def _weights(fmt, k, n, seed=1):
+    base, n0, reps = synth.synth_weights_tiled(fmt, k, n, seed)
+    return synth.tile_columns(fmt, torch.from_numpy(base).cuda(), k, n0, reps)
+
+
+def gemv_case(fmt, k, n, rows=1, launches=0, peak_gbs=None):
+    w = _weights(fmt, k, n)
+    nbytes = w.numel()
+    copies = 1 if launches else max(2, min(64, int(600e6 // nbytes) + 1))
+    ws = [w] + [w.clone() for _ in range(copies - 1)]
+    x = torch.randn((rows, k), device="cuda")
+    y = torch.empty((rows, n), device="cuda")
+    for i in range(max(launches, 3)):
+        ops.matmul(fmt, x, ws[i % copies], k, n, out=y, route="gemv")
+    torch.cuda.synchronize()
+    if launches:
+        return None
+    per_graph = max(copies, 8)
+    graph, stream = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(per_graph):
+                ops.matmul(fmt, x, ws[i % copies], k, n, out=y, route="gemv")
+    alg = nbytes + 4 * rows * (k + n)
+    reps = max(3, int(30e3 / max(1.0, alg / 3e6 * per_graph)))
+    for _ in range(2):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (reps * per_graph)
+    gbs = alg / us / 1e3
+    tail = f" ({gbs / peak_gbs * 100:.1f}% of {peak_gbs:.0f})" if peak_gbs else ""
+    print(f"gemv {'Q4' if fmt == FMT_Q4 else 'Q8'} m={rows} {k}x{n}: {nbytes / 1e6:.2f} MB packed, {us:.2f} us/launch, "
+          f"{gbs:.1f} GB/s{tail}  [{copies} weight copies, {per_graph} launches per graph]")
+    return gbs
+
+
+def gemm_case(fmt, m, k, n, launches=0):
+    w = _weights(fmt, k, n)
+    a = torch.randn((m, k), device="cuda").to(torch.bfloat16)
+    c = torch.empty((m, n), device="cuda")
+    for _ in range(max(launches, 3)):
+        ops.matmul(fmt, a, w, k, n, out=c, route="gemm")
+    torch.cuda.synchronize()
+    ops.device_status()
+    if launches:
+        return None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        ops.matmul(fmt, a, w, k, n, out=c, route="gemm")
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / 20
+    tf = 2.0 * m * k * n / us / 1e6
+    print(f"gemm {'Q4' if fmt == FMT_Q4 else 'Q8'} bf16 {m}x{k}x{n}: {us:.1f} us, {tf:.1f} TFLOP/s "
+          f"(2*M*K*N; the kernel executes twice that for the hi/lo weight split)")
+    return tf
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kind", choices=["gemv", "gemm", "sweep"])
+    ap.add_argument("fmt", choices=["q4", "q8"])
+    ap.add_argument("shape", nargs="?", default="")
+    ap.add_argument("--launches", type=int, default=0)
+    ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--peak-gbs", type=float, default=None)
+    args = ap.parse_args()
+    fmt = FMT_Q4 if args.fmt == "q4" else FMT_Q8
+    warm = torch.randn(8192, 8192, device="cuda")          # bring the clocks up
+    for _ in range(10):
+        warm @ warm
+    torch.cuda.synchronize()
+    del warm
+    if args.kind == "sweep":
+        for k, n in SMOLLM2_SHAPES:
+            gemv_case(fmt, k, n, peak_gbs=args.peak_gbs)
+    elif args.kind == "gemv":
+        k, n = (int(v) for v in args.shape.split("x"))
+        gemv_case(fmt, k, n, rows=args.rows, launches=args.launches, peak_gbs=args.peak_gbs)
+    else:
+        m, k, n = (int(v) for v in args.shape.split("x"))
+        gemm_case(fmt, m, k, n, launches=args.launches)
+
+
+if __name__ == "__main__":
+    main()

@@ -15,6 +15,11 @@ def set_option(name: str, value: int) -> None:
     check(lib.mgq_set_option(name.encode(), int(value)))
 
 
+def device_status() -> None:
+    """Raises MgqError(MGQ_ERR_TIMEOUT) if a bounded device-side wait ran out (mgq_device_status)."""
+    check(lib.mgq_device_status())
+
+
 def packed_bytes(fmt: int, k: int, n: int) -> int:
     return int(lib.mgq_packed_bytes(fmt, k, n))
 
@@ -132,6 +137,6 @@ def matmul_host(fmt: int, a: np.ndarray, w_dev_ptr: int, k: int, n: int, addend:
     return out
 
 
-__all__ = ["Plan", "set_option", "packed_bytes", "quantize", "dequantize", "shard_columns", "matmul", "matmul_host",
+__all__ = ["Plan", "set_option", "device_status", "packed_bytes", "quantize", "dequantize", "shard_columns", "matmul", "matmul_host",
            "FMT_Q4", "FMT_Q8", "A_F32", "A_BF16"]
 _ = _lib

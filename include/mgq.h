@@ -149,6 +149,27 @@ int mgq_plan_info(const mgq_plan *plan, uint32_t *grid, uint32_t *threads, uint3
                   size_t *smem_bytes);
 void mgq_plan_destroy(mgq_plan *plan);
 
+/* Allocation-free variant of the plan kernel.  No counterpart in meganeura: the reference's
+ * session allocates all its buffers when it is built and has no second, allocation-free way to run.
+ *
+ * Runs `count` single-row GEMVs (same op rules as mgq_plan_create) as one persistent kernel on
+ * `stream` and returns when they have finished (it synchronises the stream; MGQ_ERR_TIMEOUT if a
+ * grid barrier gave up).  It never calls cudaMalloc/cudaFree or any allocating routine: the
+ * kernel's scratch -- op descriptors, barrier counters, error word -- is a fixed device array of
+ * MGQ_STATIC_PLAN_MAX_OPS entries (about 25 KB) that every GPU using the library holds until the
+ * process exits.  It is meant for callers that must not allocate on their execution path, e.g. a
+ * serving loop with a fixed device-memory budget or a host application that forbids cudaMalloc after
+ * start-up (it can synchronise the device and can fail when memory is tight).
+ *
+ *   - count > MGQ_STATIC_PLAN_MAX_OPS is rejected with MGQ_ERR_SIZE.
+ *   - The first call on each device looks up the array's device address and opts the kernels into
+ *     their shared-memory size; make that first call before starting any stream capture.
+ *   - All calls on a device share the one array, and it keeps the previous call's contents; the
+ *     entry point rewrites the descriptors and zeroes the counters itself, but two calls that
+ *     overlap on the same GPU (different streams or threads) race on it. */
+#define MGQ_STATIC_PLAN_MAX_OPS 256
+int mgq_plan_run_static(const mgq_plan_op *ops, size_t count, void *stream);
+
 /* ---- Graph / Session surface (src/graph.rs:714-795, src/train.rs:380-389,
  *      src/runtime.rs:2327-2345, 2496-2550, 2612-2643, 2786-2791, 2835-2959).
  *

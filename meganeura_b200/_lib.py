@@ -68,6 +68,7 @@ SIGNATURES = {
     "mgq_plan_check": (_int, [_vp, _vp]),
     "mgq_plan_info": (_int, [_vp, ctypes.POINTER(_u32), ctypes.POINTER(_u32), ctypes.POINTER(_u32), _szp]),
     "mgq_plan_destroy": (None, [_vp]),
+    "mgq_plan_run_static": (_int, [_vp, _sz, _vp]),
     "mgq_graph_new": (_vp, []),
     "mgq_graph_free": (None, [_vp]),
     "mgq_graph_input": (_int, [_vp, ctypes.c_char_p, _szp, _sz]),

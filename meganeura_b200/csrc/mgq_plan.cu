@@ -23,6 +23,7 @@
 #include <cuda_runtime.h>
 
 #include <cstring>
+#include <mutex>
 #include <type_traits>
 #include <vector>
 
@@ -435,3 +436,141 @@ void mgq_plan_destroy(mgq_plan *pl)
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------ allocation-free variant
+//
+// mgq_plan_run_static runs a short list of GEMVs through the same persistent kernel without
+// asking CUDA for memory.  It exists for hosts that are not allowed to allocate on their
+// execution path: an inference loop that was given a fixed device-memory budget at start-up, or a
+// plug-in host that forbids cudaMalloc/cudaFree after initialisation because those calls can
+// synchronise the whole device and can fail late when memory is tight.  Such a caller cannot use
+// mgq_plan_create (it allocates the descriptor table and the barrier counters).
+//
+// The kernel's scratch (descriptors, one arrival counter per op, the error word) lives in the
+// array below, which every GPU that loads this library carries until the process exits.  In host
+// code the array's name is only a stand-in; the device address comes from cudaGetSymbolAddress,
+// looked up once per device while that device is current.
+constexpr size_t kStaticMaxOps = MGQ_STATIC_PLAN_MAX_OPS;
+constexpr size_t kStaticOpsBytes = kStaticMaxOps * sizeof(mgq::PlanOp);
+constexpr size_t kStaticDoneBytes = kStaticMaxOps * sizeof(unsigned long long);
+constexpr size_t kStaticScratchBytes = kStaticOpsBytes + kStaticDoneBytes + 256;     // + error word (own 256-byte line)
+static __device__ __align__(256) unsigned char g_static_plan_scratch[kStaticScratchBytes];
+
+namespace {
+
+struct StaticSetup {
+    bool ready = false;
+    unsigned char *scratch = nullptr;     // device address of g_static_plan_scratch on this device
+    int sms = 0, optin = 0;
+    int occ[3] = {0, 0, 0};               // resident CTAs per SM for the 1-, 2- and 4-column kernels
+};
+
+// One-time, allocation-free preparation for the current device: symbol address, SM count, and the
+// shared-memory opt-in of the three kernel variants.
+int static_setup(StaticSetup *&out)
+{
+    static std::mutex mu;
+    static StaticSetup per_device[64];
+    int dev = 0;
+    MGQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return mgq::fail(MGQ_ERR_CUDA, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    StaticSetup &st = per_device[dev];
+    if (!st.ready) {
+        void *ptr = nullptr;
+        MGQ_CUDA(cudaGetSymbolAddress(&ptr, g_static_plan_scratch));
+        MGQ_CUDA(cudaDeviceGetAttribute(&st.sms, cudaDevAttrMultiProcessorCount, dev));
+        MGQ_CUDA(cudaDeviceGetAttribute(&st.optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        MGQ_CUDA(cudaFuncSetAttribute(mgq::plan_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, st.optin));
+        MGQ_CUDA(cudaFuncSetAttribute(mgq::plan_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, st.optin));
+        MGQ_CUDA(cudaFuncSetAttribute(mgq::plan_kernel<4, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, st.optin));
+        st.scratch = static_cast<unsigned char *>(ptr);
+        st.ready = true;
+    }
+    out = &st;
+    return MGQ_OK;
+}
+
+}  // namespace
+
+extern "C" int mgq_plan_run_static(const mgq_plan_op *ops, size_t count, void *stream_v)
+{
+    using namespace mgq;
+    if (!ops) return fail(MGQ_ERR_NULL, "null op list");
+    if (count == 0) return fail(MGQ_ERR_SHAPE, "empty op list");
+    if (count > kStaticMaxOps)
+        return fail(MGQ_ERR_SIZE, "mgq_plan_run_static takes at most %zu ops (its scratch is a fixed %zu-byte device array), got %zu; "
+                                  "use mgq_plan_create for longer lists", kStaticMaxOps, kStaticScratchBytes, count);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const uint32_t threads = 384;
+    static thread_local PlanOp host_ops[kStaticMaxOps];      // fixed host staging, no heap
+    bool any_q8 = false;
+    uint32_t max_cpi = 1;
+    for (size_t i = 0; i < count; i++) {
+        const mgq_plan_op &o = ops[i];
+        if (!o.x || !o.w || !o.y) return fail(MGQ_ERR_NULL, "op %zu: null operand pointer", i);
+        if (!is_quant(o.fmt)) return fail(MGQ_ERR_FORMAT, "op %zu: weight format %d is not Q4/Q8", i, o.fmt);
+        if (o.m != 1) return fail(MGQ_ERR_SHAPE, "op %zu: single-row GEMVs only (m=%u)", i, o.m);
+        if (o.k == 0 || o.n == 0 || o.k % 32 != 0) return fail(MGQ_ERR_SHAPE, "op %zu: bad shape k=%u n=%u", i, o.k, o.n);
+        const uint32_t bpc = o.k / 32;
+        const unsigned long long nb = (unsigned long long)bpc * o.n;
+        if (bpc < 8 || bpc > threads || nb % 4 != 0)
+            return fail(MGQ_ERR_SHAPE, "op %zu: K=%u N=%u is outside the plan kernel's range (256 <= K <= %u, K*N/32 %% 4 == 0)",
+                        i, o.k, o.n, threads * 32);
+        if (reinterpret_cast<uintptr_t>(o.w) % 16 != 0 || reinterpret_cast<uintptr_t>(o.x) % 16 != 0)
+            return fail(MGQ_ERR_ALIGN, "op %zu: weights and activations must be 16-byte aligned", i);
+        any_q8 |= o.fmt == MGQ_FMT_Q8;
+        PlanOp &d = host_ops[i];
+        std::memset(&d, 0, sizeof d);
+        d.p.x = o.x; d.p.w = static_cast<const uint8_t *>(o.w); d.p.addend = o.addend; d.p.y = o.y;
+        d.p.k = o.k; d.p.n = o.n; d.p.bpc = bpc;
+        d.p.cpi = columns_for(threads, bpc);
+        d.p.active = d.p.cpi * bpc;
+        d.p.total_iters = (o.n + d.p.cpi - 1) / d.p.cpi;
+        d.p.num_blocks = nb;
+        const uint32_t slots = (uint32_t)(kPlanStages * 4) * d.p.cpi;
+        d.p.red_shift = 0;
+        while (d.p.red_shift < 5 && (slots << (d.p.red_shift + 1)) <= threads && (2u << d.p.red_shift) <= bpc) d.p.red_shift++;
+        const uint32_t lanes = 1u << d.p.red_shift;
+        d.p.red_chunk = (bpc + lanes - 1) / lanes;
+        if (d.p.red_chunk % 4 != 0 && bpc % 4 == 0 && d.p.red_chunk > 4) d.p.red_chunk = (d.p.red_chunk + 3u) & ~3u;
+        d.fmt = (uint32_t)o.fmt;
+        d.wait_for = o.wait_for > i ? (uint32_t)i : o.wait_for;
+        max_cpi = d.p.cpi > max_cpi ? d.p.cpi : max_cpi;
+    }
+    StaticSetup *st = nullptr;
+    if (int rc = static_setup(st)) return rc;
+
+    // same kernel choice as mgq_plan_create's default: 2 columns per thread, 1 when a round would not fit
+    const uint32_t per_thread = any_q8 ? 36u : 20u;
+    const uint32_t cols = (uint32_t)(kPlanStages * 2) * max_cpi > threads ? 1u : 2u;
+    void *kernel = cols == 2 ? (void *)plan_kernel<2, 2> : (void *)plan_kernel<1, 2>;
+    const size_t smem = (size_t)kPlanStages * per_thread * threads * cols + (size_t)2 * kPlanStages * cols * threads * 4;
+    if (smem > (size_t)st->optin) return fail(MGQ_ERR_SHAPE, "plan needs %zu B of shared memory, device allows %d", smem, st->optin);
+    int &occ = st->occ[cols == 2 ? 1 : 0];
+    if (occ == 0) MGQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, (int)threads, smem));
+    if (occ < 1) return fail(MGQ_ERR_CUDA, "plan kernel does not fit on an SM");
+    const uint32_t grid = (uint32_t)st->sms * (uint32_t)occ;
+
+    // The array still holds the previous call's descriptors, counters and error word: overwrite the
+    // first, zero the other two.  All of it is ordered on `stream` before the kernel.
+    unsigned char *d_ops = st->scratch, *d_done = st->scratch + kStaticOpsBytes, *d_err = d_done + kStaticDoneBytes;
+    MGQ_CUDA(cudaMemcpyAsync(d_ops, host_ops, count * sizeof(PlanOp), cudaMemcpyHostToDevice, stream));
+    MGQ_CUDA(cudaMemsetAsync(d_done, 0, kStaticDoneBytes + 256, stream));
+    const PlanOp *k_ops = reinterpret_cast<const PlanOp *>(d_ops);
+    uint32_t n_ops = (uint32_t)count, step_bytes = per_thread * threads * cols;
+    unsigned long long *k_done = reinterpret_cast<unsigned long long *>(d_done);
+    unsigned int *k_err = reinterpret_cast<unsigned int *>(d_err);
+#ifdef MGQ_PLAN_TRACE
+    unsigned long long *trace = nullptr;
+    void *args[] = {&k_ops, &n_ops, &step_bytes, &k_done, &k_err, &trace};
+#else
+    void *args[] = {&k_ops, &n_ops, &step_bytes, &k_done, &k_err};
+#endif
+    MGQ_CUDA(cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(threads), args, smem, stream));
+    unsigned int err = 0;
+    MGQ_CUDA(cudaMemcpyAsync(&err, d_err, sizeof err, cudaMemcpyDeviceToHost, stream));
+    MGQ_CUDA(cudaStreamSynchronize(stream));
+    if (err) return fail(MGQ_ERR_TIMEOUT, "a grid barrier of the plan kernel ran out of its wait limit");
+    return MGQ_OK;
+}

@@ -296,15 +296,27 @@ def main():
                          "frac_of_nominal_8000": round(achieved / 8000.0, 4),
                          "kernel": "gemv_q4_kernel" if fmt == FMT_Q4 else "gemv_q8_kernel",
                          "bytes_per_launch": round(per_launch_bytes), "us_per_launch": round(per_launch_us, 3),
-                         "traffic": NCU_TRAFFIC.get(args.fmt)},
+                         "traffic": NCU_TRAFFIC.get(args.fmt) if (world == 1 and args.model == "qwen3-8b" and args.batch == 1
+                                                                   and not args.plan_kernel) else None},
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(shape, fmt)
         print(json.dumps(line))
     if world > 1:
+        # A captured graph that holds NCCL nodes must go before the communicator does (destroying the
+        # process group first blocks forever); a watchdog ends the process if teardown still stalls.
+        sys.stdout.flush()
         dist.barrier()
+        torch.cuda.synchronize()
+        chain.graph = None
+        del chain
+        torch.cuda.synchronize()
+        watchdog = threading.Timer(30.0, lambda: os._exit(0))
+        watchdog.daemon = True
+        watchdog.start()
         dist.destroy_process_group()
+        watchdog.cancel()
 
 
 # DRAM bytes per launch of the GEMV kernel (dram__bytes_read.sum + dram__bytes_write.sum averaged

@@ -189,13 +189,15 @@ def run_reference(args, shape, fmt):
 
 # ------------------------------------------------------------------------------- GPU arm
 
-def workload_config(shape, fmt, batch, gpus):
+def workload_config(shape, fmt, batch, gpus, exchange="peer"):
     return {
         "workload": f"{shape.name}-shaped decode token, all {'Q4' if fmt == 2 else 'Q8'} GEMVs "
                     f"({shape.layers} layers x q|k|v,o,gate|up,down + lm_head), batch {batch}",
         "weights": "packed codes uniform, f16 block scales log-uniform [1e-3,1e-1], offset 8 (Q4); seeded",
         "activations": "f32 N(0,1), seeded",
-        "parallelism": f"columns sharded x{gpus}, NCCL all-gather at 4 points per layer + logits" if gpus > 1 else "single GPU",
+        "parallelism": (f"columns sharded x{gpus}, exchange at 4 points per layer + logits: " +
+                        ("slices pushed into every peer's buffer by the GEMV kernel (NVLink stores + arrival counters)"
+                         if exchange == "peer" else "NCCL all-gather")) if gpus > 1 else "single GPU",
         "l2": "no flush needed: each step streams its weights once, 4-37x the 126 MB L2",
         "launch": "one CUDA graph per token",
     }
@@ -211,6 +213,8 @@ def main():
     ap.add_argument("--model", choices=["qwen3-8b", "smollm2-135m"], default="qwen3-8b")
     ap.add_argument("--impl", choices=["mgq", "reference"], default="mgq")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
+                    help="multi-GPU exchange: slices pushed over NVLink by the GEMV kernels (default) or NCCL all-gather")
     ap.add_argument("--plan-kernel", action="store_true", help="run the token as one persistent plan kernel instead of one kernel per GEMV")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "mgq" else args.warmup
@@ -238,7 +242,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     chain = dc.DecodeGemvChain(shape, fmt, batch=args.batch, rank=rank, world=world, seed=0,
-                               use_plan=args.plan_kernel)
+                               use_plan=args.plan_kernel, exchange=args.exchange)
     captured = chain.capture()
 
     def barrier():
@@ -267,6 +271,8 @@ def main():
     ms_dev = timed(chain.step, args.steps, args.warmup)
     ms_e2e = timed(chain.step_host, args.steps, args.warmup)
     clocks = sampler.stop() if sampler else None
+    if chain.peer is not None and chain.peer.error():
+        raise SystemExit("a bounded wait of the peer exchange ran out (MGQ_ERR_TIMEOUT): results are invalid")
 
     bytes_rank = chain.bytes_per_step()
     total_bytes = bytes_rank * world
@@ -284,7 +290,7 @@ def main():
             "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(shape, fmt, args.batch, world),
+            "config": workload_config(shape, fmt, args.batch, world, args.exchange),
             "tokens_per_s": round(args.batch / (ms_step * 1e-3), 1),
             "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": chain.h2d_bytes(),
                     "d2h_bytes_per_step": chain.d2h_bytes(), "ms_per_step": round(ms_e2e / args.steps, 4),

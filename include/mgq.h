@@ -98,6 +98,38 @@ int mgq_buffer_download(const void *dev, void *host, size_t bytes, void *stream)
 int mgq_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
              uint32_t m, uint32_t k, uint32_t n, void *stream);
 
+/* ---- column-sharded GEMV with a fused all-gather over peer memory (no reference counterpart: the
+ * reference is single-device, src/runtime.rs:1513-1531).
+ *
+ * Each rank runs the unchanged GEMV on its column slice.  With `push_dev` set, the lane that
+ * finishes a column also stores it into every rank's copy of the gathered vector (plain peer
+ * stores over NVLink into memory the caller made peer-accessible, e.g. CUDA IPC or symmetric
+ * memory).  An element travels as one 8-byte {value, stamp} pair, stamp = *epoch + 1, written by a
+ * single 64-bit store, so data and validity arrive together and no fence, counter or atomic is
+ * needed.  With `wait_vec` set (the local gathered vector of length k that this GEMV consumes),
+ * every thread first polls -- with an iteration limit, after which *error is raised -- the stamps
+ * of the 32 elements of its block.  mgq_exchange_finish ends a token: it polls all `length` stamps
+ * of the last gathered vector and then increments *epoch.  Stamps only grow; nothing is reset
+ * between tokens, so a token can be replayed from a CUDA graph.  m = 1 only.
+ * x may be NULL when wait_vec is set: the GEMV then takes its activations from the gathered vector
+ * itself (the values it has just found valid), which is how a sharded model chains its layers.  A
+ * non-NULL x must be data of this GPU's own stream (it is read through the read-only cache). */
+#define MGQ_MAX_PEERS 8
+typedef struct mgq_exchange_elem { float value; uint32_t stamp; } mgq_exchange_elem;
+typedef struct mgq_exchange_push {            /* must live in device memory */
+    uint32_t world, rank;
+    uint32_t gather_cols;                     /* leading columns of this rank's y that every rank needs */
+    uint32_t reserved;
+    mgq_exchange_elem *dst[MGQ_MAX_PEERS];    /* rank p's gathered vector; this rank fills [rank*gather_cols, +gather_cols) */
+} mgq_exchange_push;
+
+int mgq_gemv_exchange(int fmt, const float *x, const void *w, const float *addend, float *y, uint32_t k, uint32_t n,
+                      const mgq_exchange_push *push_dev, const mgq_exchange_elem *wait_vec,
+                      const unsigned long long *epoch, unsigned int *error, void *stream);
+/* blocks_done: a zero-initialised word in local device memory (returns to zero). */
+int mgq_exchange_finish(const mgq_exchange_elem *last_vec, uint32_t length, unsigned long long *epoch,
+                        unsigned int *error, unsigned int *blocks_done, void *stream);
+
 /* c[m,n] = a[m,k] . dequant(w)[k,n] (+ addend[m,n]); a is f32 or bf16 row-major, c is f32.
  * Stands in for the MatMul / FusedMatMulAdd dispatches with a quantized weight_format
  * (src/compile.rs:1408-1419, 1511-1522; src/shaders/matmul.wgsl:28-109).

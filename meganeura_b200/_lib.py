@@ -60,6 +60,8 @@ SIGNATURES = {
     "mgq_buffer_download": (_int, [_vp, _vp, _sz, _vp]),
     "mgq_device_status": (_int, []),
     "mgq_gemv": (_int, [_int, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
+    "mgq_gemv_exchange": (_int, [_int, _vp, _vp, _vp, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
+    "mgq_exchange_finish": (_int, [_vp, _u32, _vp, _vp, _vp, _vp]),
     "mgq_gemm": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_matmul": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_matmul_host": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32]),
@@ -103,6 +105,12 @@ class PlanOp(ctypes.Structure):
     """mgq_plan_op"""
     _fields_ = [("fmt", ctypes.c_int), ("x", _vp), ("w", _vp), ("addend", _vp), ("y", _vp),
                 ("m", _u32), ("k", _u32), ("n", _u32), ("wait_for", _u32)]
+
+
+class ExchangePush(ctypes.Structure):
+    """mgq_exchange_push (built on the host, copied to device memory)"""
+    _fields_ = [("world", _u32), ("rank", _u32), ("gather_cols", _u32), ("reserved", _u32),
+                ("dst", ctypes.c_uint64 * 8)]
 
 
 def last_error() -> str:

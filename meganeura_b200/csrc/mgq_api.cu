@@ -86,6 +86,25 @@ int mgq_gemv(int fmt, const float *x, const void *w, const float *addend, float 
     return launch_gemv(fmt, x, w, addend, y, m, k, n, stream);
 }
 
+int mgq_gemv_exchange(int fmt, const float *x, const void *w, const float *addend, float *y, uint32_t k, uint32_t n,
+                      const mgq_exchange_push *push_dev, const mgq_exchange_elem *wait_vec,
+                      const unsigned long long *epoch, unsigned int *error, void *stream)
+{
+    if (!x && !wait_vec) return fail(MGQ_ERR_NULL, "x may only be null when the gathered vector is consumed (wait_vec)");
+    if (int rc = check_matmul_args(fmt, x ? static_cast<const void *>(x) : static_cast<const void *>(wait_vec), w, y, 1, k, n)) return rc;
+    if (!epoch || !error) return fail(MGQ_ERR_NULL, "exchange needs the epoch and error words");
+    if (reinterpret_cast<uintptr_t>(wait_vec) % 16 != 0) return fail(MGQ_ERR_ALIGN, "the gathered vector must be 16-byte aligned");
+    GemvExchange xc{push_dev, wait_vec, epoch, error};
+    return launch_gemv(fmt, x, w, addend, y, 1, k, n, stream, &xc);
+}
+
+int mgq_exchange_finish(const mgq_exchange_elem *last_vec, uint32_t length, unsigned long long *epoch,
+                        unsigned int *error, unsigned int *blocks_done, void *stream)
+{
+    if (!epoch || !error || !blocks_done) return fail(MGQ_ERR_NULL, "exchange needs the epoch, error and blocks_done words");
+    return launch_exchange_finish(last_vec, length, epoch, error, blocks_done, stream);
+}
+
 int mgq_gemm(int fmt, const void *a, int a_dtype, const void *w, const float *addend, float *c,
              uint32_t m, uint32_t k, uint32_t n, void *stream)
 {

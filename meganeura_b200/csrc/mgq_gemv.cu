@@ -96,11 +96,17 @@ __global__ void __launch_bounds__(TMAX) gemv_q4_kernel(const GemvParams p)
     for (int s = 0; s < STAGES - 1; s++) issue(s, true);                    // weights first: they depend on nothing
     grid_launch_dependents();
     grid_dependency_wait();                                                 // x, addend and y belong to earlier kernels
+    exchange_poll(p, b);                                                    // ... or to other GPUs
     MGQ_STAMP(p, 1);
 
     XBlock xb[MT];
 #pragma unroll
-    for (int r = 0; r < MT; r++) load_x<1>(p.x + (size_t)r * p.k, b, xb[r]);
+    for (int r = 0; r < MT; r++) {
+        // x is either a local vector (read-only path: the CTAs of an SM share one fetch) or, when the
+        // caller passed none, the gathered vector that was just polled (written by other GPUs: L2 only)
+        if (p.x) load_x<1, false>(p.x + (size_t)r * p.k, b, xb[r]);
+        else     load_x_gathered<1>(p.wait_vec, b, xb[r]);
+    }
     const ReduceSlot slot = make_slot<ROUND>(p);
 
     auto block_sum = [&](int idx, float (&out)[MT]) {
@@ -130,7 +136,8 @@ __global__ void __launch_bounds__(TMAX) gemv_q4_kernel(const GemvParams p)
             }
         }
         if (round == 0) MGQ_STAMP(p, 2);
-        reduce_store<MT, ROUND>(p, slot, s_red + (size_t)(round & 1) * MT * ROUND * T, part, g0 + g, g1);
+        reduce_store<MT, ROUND, true>(p, slot, s_red + (size_t)(round & 1) * MT * ROUND * T, part, g0 + g, g1,
+                                      p.push ? s_red + (size_t)2 * MT * ROUND * T : nullptr);
     }
     cp_async_wait<0>();
     MGQ_STAMP(p, 3);
@@ -189,11 +196,15 @@ __global__ void __launch_bounds__(TMAX) gemv_q8_kernel(const GemvParams p)
     for (int s = 0; s < STAGES - 1; s++) issue(s);
     grid_launch_dependents();
     grid_dependency_wait();
+    exchange_poll(p, b);
     MGQ_STAMP(p, 1);
 
     XBlock xb[MT];
 #pragma unroll
-    for (int r = 0; r < MT; r++) load_x<0>(p.x + (size_t)r * p.k, b, xb[r]);
+    for (int r = 0; r < MT; r++) {
+        if (p.x) load_x<0, false>(p.x + (size_t)r * p.k, b, xb[r]);
+        else     load_x_gathered<0>(p.wait_vec, b, xb[r]);
+    }
     const ReduceSlot slot = make_slot<ROUND>(p);
 
     auto block_sum = [&](int idx, float (&out)[MT]) {
@@ -224,7 +235,8 @@ __global__ void __launch_bounds__(TMAX) gemv_q8_kernel(const GemvParams p)
             }
         }
         if (round == 0) MGQ_STAMP(p, 2);
-        reduce_store<MT, ROUND>(p, slot, s_red + (size_t)(round & 1) * MT * ROUND * T, part, g0 + g, g1);
+        reduce_store<MT, ROUND, true>(p, slot, s_red + (size_t)(round & 1) * MT * ROUND * T, part, g0 + g, g1,
+                                      p.push ? s_red + (size_t)2 * MT * ROUND * T : nullptr);
     }
     cp_async_wait<0>();
     MGQ_STAMP(p, 3);
@@ -306,7 +318,7 @@ uint32_t columns_for(uint32_t threads, uint32_t bpc)
 size_t smem_bytes(int fmt, uint32_t threads, int c, int mt)
 {
     const size_t round = (size_t)kStages * c;
-    const size_t red = 2 * mt * round * threads * sizeof(float);
+    const size_t red = 2 * mt * round * threads * sizeof(float) + threads * sizeof(float);   // + one round of finished columns (exchange)
     if (fmt == MGQ_FMT_Q4) return round * threads * 20 + red;
     return (size_t)(threads / 32) * round * kQ8WarpStage + red;
 }
@@ -471,8 +483,48 @@ int set_gemv_option(const char *name, long value)
     return MGQ_OK;
 }
 
+// Ends a token on this GPU: waits (bounded) until every element of the last gathered vector carries
+// this token's stamp, then the block that finishes last advances the local token index.
+__global__ void exchange_finish_kernel(const float2 *last_vec, uint32_t length, unsigned long long *epoch,
+                                       unsigned int *error, unsigned int *blocks_done)
+{
+    const uint32_t stamp = dev::exchange_stamp(epoch);
+    if (last_vec) {
+        for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < length; i += gridDim.x * blockDim.x) {
+            for (uint32_t spins = 0;; spins++) {
+                uint32_t got;
+                asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(got) : "l"(&last_vec[i].y) : "memory");
+                if (got == stamp) break;
+                if (spins > dev::kExchangeSpinLimit) { atomicExch(error, 1u); break; }
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(blocks_done, 1u) == gridDim.x - 1) {
+            atomicExch(blocks_done, 0u);
+            *reinterpret_cast<volatile unsigned long long *>(epoch) = (unsigned long long)stamp;   // token + 1
+            __threadfence();
+        }
+    }
+}
+
+int launch_exchange_finish(const void *last_vec, uint32_t length, unsigned long long *epoch,
+                           unsigned int *error, unsigned int *blocks_done, void *stream_v)
+{
+    const uint32_t threads = 256;
+    uint32_t grid = last_vec ? (length + threads * 4 - 1) / (threads * 4) : 1;
+    if (grid > 148) grid = 148;
+    if (grid < 1) grid = 1;
+    exchange_finish_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream_v)>>>(
+        static_cast<const float2 *>(last_vec), length, epoch, error, blocks_done);
+    MGQ_CUDA(cudaGetLastError());
+    return MGQ_OK;
+}
+
 int launch_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
-                uint32_t m, uint32_t k, uint32_t n, void *stream_v)
+                uint32_t m, uint32_t k, uint32_t n, void *stream_v, const GemvExchange *xchg)
 {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const uint32_t bpc = k / 32;
@@ -480,10 +532,17 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
     p.k = k; p.n = n; p.bpc = bpc;
     p.num_blocks = (unsigned long long)bpc * n;
     p.w = static_cast<const uint8_t *>(w);
+    if (xchg) {
+        p.push = static_cast<const dev::ExchangePush *>(xchg->push_dev);
+        p.wait_vec = static_cast<const float2 *>(xchg->wait_vec);
+        p.epoch = xchg->epoch;
+        p.xerror = xchg->error;
+    }
 
     const bool streamable = bpc >= 8 && bpc <= 1024 && (p.num_blocks % 4 == 0) &&
                             (reinterpret_cast<uintptr_t>(x) % 16 == 0);
     if (!streamable) {
+        if (xchg) return fail(MGQ_ERR_SHAPE, "this shape has no exchanging GEMV kernel (K=%u N=%u)", k, n);
         p.x = x; p.addend = addend; p.y = y;
         const uint32_t warps = 8, grid = (n + warps - 1) / warps;
         if (fmt == MGQ_FMT_Q4) gemv_generic_kernel<MGQ_FMT_Q4><<<grid, warps * 32, 0, stream>>>(p, m);

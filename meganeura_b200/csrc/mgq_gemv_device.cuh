@@ -24,10 +24,67 @@ struct GemvParams {
     uint32_t red_shift;    // log2(lanes that finish one column sum)
     uint32_t red_chunk;    // partials summed by each finishing lane = ceil(bpc / lanes)
     unsigned long long num_blocks;
+    // multi-GPU exchange (all null / zero on a single GPU)
+    const struct ExchangePush *push;          // where the leading columns of y also go: every peer's gathered vector
+    const float2 *wait_vec;                   // local gathered {value, stamp} vector (length k) that must carry this token's stamps
+    const unsigned long long *epoch;          // local token index
+    unsigned int *xerror;                     // raised when the bounded wait runs out
 #ifdef MGQ_GEMV_TRACE
     unsigned long long *trace;   // [gridDim.x][4] globaltimer stamps: start, after dependency wait, first block done, end
 #endif
 };
+
+// Fused all-gather of a column-sharded GEMV.  Instead of a collective after the kernel, the lane
+// that finishes a column stores it straight into every rank's copy of the gathered vector (plain
+// peer stores over NVLink; remote data always lands in the consumer GPU's own memory).  Each
+// element travels as one 8-byte {value, stamp} pair written by a single 64-bit store, stamp = token
+// index + 1, so the data carries its own validity: a consumer polls the stamps of exactly the 32
+// elements it is about to use (with an iteration limit) and needs no fence, counter or atomic.
+constexpr int kMaxPeers = 8;
+struct ExchangePush {                          // one per exchanging GEMV, in device memory (mgq_exchange_push)
+    uint32_t world, rank;
+    uint32_t gather_cols;                      // leading columns of this rank's y that every rank needs
+    uint32_t reserved;
+    float2 *dst[kMaxPeers];                    // rank p's gathered {value, stamp} vector; this rank fills [rank*gather_cols, +gather_cols)
+};
+constexpr uint32_t kExchangeSpinLimit = 1u << 20;
+
+__device__ __forceinline__ uint32_t exchange_stamp(const unsigned long long *epoch)
+{
+    unsigned long long token;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(token) : "l"(epoch) : "memory");
+    return (uint32_t)token + 1u;
+}
+
+// Before block b of x is used: wait until all 32 of its elements carry this token's stamp.  Peer
+// stores land in this GPU's L2, so the poll uses L1-bypassing GPU-scope loads (system-scope loads
+// of this volume -- every thread of every CTA reads its 256 bytes -- were measured 8x slower); a
+// stale read only costs another iteration because every element carries its own stamp.
+__device__ __forceinline__ void exchange_poll(const GemvParams &p, uint32_t b)
+{
+    if (!p.wait_vec) return;
+    const uint32_t stamp = exchange_stamp(p.epoch);
+    const uint32_t lane = threadIdx.x & 31u;
+    // When a warp's 32 blocks are consecutive (K a multiple of 1024) the warp polls its 8 KB region
+    // together, lane l reading consecutive 16-byte pieces: fully coalesced, no sector read twice.
+    const bool together = (p.bpc & 31u) == 0;
+    const uint4 *src = together ? reinterpret_cast<const uint4 *>(p.wait_vec + 32u * (b - lane)) + lane
+                                : reinterpret_cast<const uint4 *>(p.wait_vec + 32u * b);
+    const uint32_t step = together ? 32u : 1u;
+    for (uint32_t spins = 0;; spins++) {
+        uint32_t ok = 1;
+#pragma unroll
+        for (uint32_t j = 0; j < 16; j++) {
+            uint4 v;
+            asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src + j * step) : "memory");
+            ok &= (v.y == stamp) & (v.w == stamp);
+        }
+        if (together) ok = __all_sync(0xffffffffu, ok);
+        if (ok) break;
+        if (spins > kExchangeSpinLimit) { atomicExch(p.xerror, 1u); break; }
+    }
+}
 
 #if defined(MGQ_GEMV_TRACE) || defined(MGQ_PLAN_TRACE)
 __device__ __forceinline__ unsigned long long now_ns()
@@ -104,17 +161,10 @@ struct XBlock {
 // ORDER 0 (Q8): word j holds elements 4j .. 4j+3.
 // ORDER 1 (Q4): word 2j holds elements 8j+{0,2,4,6} (low nibbles of nibble word j),
 //               word 2j+1 holds elements 8j+{1,3,5,7} (high nibbles).
-// COHERENT: read through L2 (the producer may be another CTA of the same persistent kernel).
-template <int ORDER, bool COHERENT = false>
-__device__ __forceinline__ void load_x(const float *xrow, uint32_t b, XBlock &xb)
+// Turns 32 activations (already in registers) into the three byte planes, scale and sum.
+template <int ORDER>
+__device__ __forceinline__ void prepare_x(const float (&v)[32], XBlock &xb)
 {
-    const float4 *xp = reinterpret_cast<const float4 *>(xrow + 32u * b);
-    float v[32];
-#pragma unroll
-    for (int j = 0; j < 8; j++) {
-        const float4 t = COHERENT ? __ldcg(xp + j) : __ldg(xp + j);
-        v[4 * j + 0] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
-    }
     float amax = 0.f, s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
@@ -145,6 +195,37 @@ __device__ __forceinline__ void load_x(const float *xrow, uint32_t b, XBlock &xb
         const uint32_t top = __byte_perm(__byte_perm(a, bb, 0x0062), __byte_perm(c, d, 0x0062), 0x5410);
         xb.p2[w] = (top + 0x40404040u) ^ 0x80808080u;                  // (u + 64) - 128 = u - 64 as int8; u <= 127: no carries
     }
+}
+
+// COHERENT: read through L2 (the producer may be another CTA of the same persistent kernel).
+template <int ORDER, bool COHERENT = false>
+__device__ __forceinline__ void load_x(const float *xrow, uint32_t b, XBlock &xb)
+{
+    const float4 *xp = reinterpret_cast<const float4 *>(xrow + 32u * b);
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const float4 t = COHERENT ? __ldcg(xp + j) : __ldg(xp + j);
+        v[4 * j + 0] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+    }
+    prepare_x<ORDER>(v, xb);
+}
+
+// Block b of x taken from a gathered {value, stamp} vector whose stamps have already been checked.
+template <int ORDER>
+__device__ __forceinline__ void load_x_gathered(const float2 *vec, uint32_t b, XBlock &xb)
+{
+    const uint4 *src = reinterpret_cast<const uint4 *>(vec + 32u * b);
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+        uint4 t;
+        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(t.x), "=r"(t.y), "=r"(t.z), "=r"(t.w) : "l"(src + j) : "memory");
+        v[2 * j] = __uint_as_float(t.x);
+        v[2 * j + 1] = __uint_as_float(t.z);
+    }
+    prepare_x<ORDER>(v, xb);
 }
 
 // Exact sum over one block of X[i] * code[i], returned in f32 (planes recombined with two FMAs).
@@ -212,7 +293,8 @@ __device__ __forceinline__ ReduceSlot make_slot(const GemvParams &p)
 
 template <int MT, int ROUND, bool COHERENT = false>
 __device__ __forceinline__ void reduce_store(const GemvParams &p, const ReduceSlot &slot, float *red,
-                                             const float (&part)[MT][ROUND], uint32_t it_base, uint32_t it_end)
+                                             const float (&part)[MT][ROUND], uint32_t it_base, uint32_t it_end,
+                                             float *push_stage = nullptr)
 {
     const uint32_t T = blockDim.x, t = threadIdx.x;
 #pragma unroll
@@ -238,11 +320,29 @@ __device__ __forceinline__ void reduce_store(const GemvParams &p, const ReduceSl
         if (slot.writer && it < it_end && col < p.n) {
             const size_t o = (size_t)r * p.n + col;
             const float add = p.addend ? (COHERENT ? __ldcg(p.addend + o) : p.addend[o]) : 0.f;
-            p.y[o] = p.addend ? s + add : s;
+            const float v = p.addend ? s + add : s;
+            p.y[o] = v;
+            if (push_stage && r == 0) push_stage[slot.iter * p.cpi + slot.cs] = v;     // column offset inside the round
+        }
+    }
+    if (push_stage) {
+        // The round's columns are consecutive: consecutive lanes send consecutive {value, stamp} pairs, so
+        // a peer receives a few full 128-byte writes instead of one 8-byte write per column.
+        __syncthreads();
+        const ExchangePush &px = *p.push;
+        const uint32_t first = it_base * p.cpi;
+        uint32_t ncols = min((uint32_t)ROUND, it_end - it_base) * p.cpi;
+        ncols = min(ncols, p.n - first);
+        if (first < px.gather_cols) {
+            ncols = min(ncols, px.gather_cols - first);
+            const uint32_t stamp = exchange_stamp(p.epoch);
+            for (uint32_t idx = t; idx < ncols * px.world; idx += T) {
+                const uint32_t q = idx / ncols, c = idx - q * ncols;
+                px.dst[q][(size_t)px.rank * px.gather_cols + first + c] = make_float2(push_stage[c], __uint_as_float(stamp));
+            }
         }
     }
 }
-
 
 }  // namespace dev
 }  // namespace mgq

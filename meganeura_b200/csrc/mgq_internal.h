@@ -16,9 +16,19 @@ int cuda_check(int cuda_err, const char *what, const char *file, int line);
 
 inline bool is_quant(int fmt) { return fmt == MGQ_FMT_Q4 || fmt == MGQ_FMT_Q8; }
 
+// Multi-GPU exchange arguments of one GEMV launch (device pointers; see mgq_gemv_exchange).
+struct GemvExchange {
+    const void *push_dev;                     // mgq_exchange_push in device memory, or null
+    const void *wait_vec;                     // gathered {value, stamp} vector this GEMV consumes, or null
+    const unsigned long long *epoch;
+    unsigned int *error;
+};
+
 // Launchers implemented in the .cu files (all pointers are device pointers).
 int launch_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
-                uint32_t m, uint32_t k, uint32_t n, void *stream);
+                uint32_t m, uint32_t k, uint32_t n, void *stream, const GemvExchange *xchg = nullptr);
+int launch_exchange_finish(const void *last_vec, uint32_t length, unsigned long long *epoch,
+                           unsigned int *error, unsigned int *blocks_done, void *stream);
 int set_gemv_option(const char *name, long value);
 int set_plan_option(const char *name, long value);
 int set_gemm_option(const char *name, long value);

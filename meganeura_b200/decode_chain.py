@@ -94,7 +94,8 @@ class DecodeGemvChain:
     """Device-resident column shards of every projection + the per-token launch sequence."""
 
     def __init__(self, shape: ModelShape, fmt: int = FMT_Q4, batch: int = 1, rank: int = 0, world: int = 1,
-                 layers: int | None = None, seed: int = 0, device=None, group=None, use_plan: bool | None = None):
+                 layers: int | None = None, seed: int = 0, device=None, group=None, use_plan: bool | None = None,
+                 exchange: str = "peer"):
         import torch
         if fmt not in (FMT_Q4, FMT_Q8):
             raise ValueError("fmt must be Q4 or Q8")
@@ -105,6 +106,12 @@ class DecodeGemvChain:
         self.launches_per_step = 0
         self.graph = None
         self.plan = None
+        # exchange between ranks: "peer" = slices pushed over NVLink by the GEMV itself (mgq_gemv_exchange),
+        # "nccl" = all_gather_into_tensor after each exchanging GEMV
+        self.exchange = exchange if (world > 1 or exchange == "peer-self") else "none"
+        if self.exchange == "peer-self":       # one rank pushing to itself: exercises the exchange code path on one GPU
+            self.exchange = "peer"
+        self.peer = None
         # use_plan=True runs the token as one persistent kernel (mgq_plan_*); the default is one
         # kernel per GEMV chained by programmatic dependent launch, which is currently faster
         self.use_plan = bool(use_plan) and world == 1 and batch == 1
@@ -120,6 +127,14 @@ class DecodeGemvChain:
                 self.ops_list.append(self._make_op(sp, seed * 100003 + layer * 16 + len(self.ops_list) % 16))
         self.head = self._make_op(head_spec(shape), seed * 100003 + 999983)
         self.ops_list.append(self.head)
+        if self.exchange == "peer":
+            if batch != 1:
+                raise ValueError("the peer exchange takes batch 1; use exchange='nccl'")
+            from .exchange import PeerExchange
+            self.peer = PeerExchange([op["gather_cols"] for op in self.ops_list], rank, world, group)
+            for i, op in enumerate(self.ops_list):
+                if op["gather_cols"]:
+                    op["full"] = self.peer.gathered(i)
         self.logits = self.head["full"] if self.head["full"] is not None else self.head["y"]
         self.logits_host = torch.empty_like(self.logits, device="cpu").pin_memory() if self.device.type == "cuda" else None
 
@@ -157,7 +172,7 @@ class DecodeGemvChain:
             addend = torch.randn((self.m, n_loc), generator=torch.Generator().manual_seed(seed + 17)).to(self.device)
         full = None
         gather_cols = 0
-        if world > 1 and sp.gather:
+        if (world > 1 or self.exchange == "peer") and sp.gather:
             gather_cols = widths[0]
             full = torch.zeros((world * self.m * gather_cols,), dtype=torch.float32, device=self.device)
         return {"spec": sp, "w": w, "y": y, "addend": addend, "full": full, "gather_cols": gather_cols, "n_loc": n_loc}
@@ -178,6 +193,8 @@ class DecodeGemvChain:
             self.plan.launch()
             self.launches_per_step = 1
             return 1
+        if self.exchange == "peer":
+            return self._launch_all_peer()
         count = 0
         for op in self.ops_list:
             sp = op["spec"]
@@ -190,6 +207,20 @@ class DecodeGemvChain:
                 dist.all_gather_into_tensor(op["full"], src.reshape(-1), group=self.group)
         self.launches_per_step = count
         return count
+
+    def _launch_all_peer(self):
+        """Every GEMV pushes its slice to all ranks; each one waits for the exchange before it."""
+        import torch
+        stream = torch.cuda.current_stream().cuda_stream
+        last_exchange = None
+        for i, op in enumerate(self.ops_list):
+            sp = op["spec"]
+            self.peer.gemv(self.fmt, self.x[sp.src], op["w"], op["addend"], op["y"], sp.k, op["n_loc"], i, last_exchange, stream)
+            if op["gather_cols"]:
+                last_exchange = i
+        self.peer.finish(last_exchange, stream)
+        self.launches_per_step = len(self.ops_list) + 1
+        return self.launches_per_step
 
     def capture(self):
         """Capture one token's launches into a CUDA graph (falls back to plain launches)."""

@@ -83,6 +83,8 @@ __device__ __forceinline__ void exchange_poll(const GemvParams &p, uint32_t b)
         if (together) ok = __all_sync(0xffffffffu, ok);
         if (ok) break;
         if (spins > kExchangeSpinLimit) { atomicExch(p.xerror, 1u); break; }
+        // once any thread of the step has given up, the step is lost: later waiters leave at once
+        if ((spins & 1023u) == 1023u && *reinterpret_cast<const volatile uint32_t *>(p.xerror) != 0u) break;
     }
 }
 

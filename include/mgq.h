@@ -57,8 +57,10 @@ const char *mgq_version(void);
  * (MEGANEURA_SERIAL_DISPATCH, src/runtime.rs:1703-1707).  0 means "automatic" for the tunables.
  *   "gemv.serial_dispatch"      1: every GEMV starts only after its predecessor has finished
  *                               (no programmatic dependent launch); also MGQ_SERIAL_DISPATCH=1
- *   "gemv.columns_per_thread"   1, 2 or 4 columns per thread and pipeline stage
+ *   "gemv.columns_per_thread"   1 or 2 columns per thread and pipeline stage
  *   "gemv.ctas_per_sm"          CTAs per SM a GEMV grid is sized for (default 3)
+ *   "gemv.lookahead_bytes"      most bytes of the following GEMV's weights that a GEMV asks L2 to
+ *                               fetch (mgq_gemv_lookahead); 0 = look-ahead off (the default)
  *   "plan.columns_per_thread"   1, 2 or 4 for plans created afterwards (default 2: two CTAs per SM)
  *   "gemm.force_tiled"          1: never use the tcgen05 kernel (CUDA-core tiled kernel only) */
 int mgq_set_option(const char *name, long value);
@@ -97,6 +99,18 @@ int mgq_buffer_download(const void *dev, void *host, size_t bytes, void *stream)
 #define MGQ_GEMV_MAX_M 16
 int mgq_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
              uint32_t m, uint32_t k, uint32_t n, void *stream);
+
+/* Look-ahead for chains of dependent GEMVs (no reference counterpart: the reference records its
+ * dispatches into one command encoder and leaves overlap to the driver, src/runtime.rs:2860-2878).
+ * Names the packed weights that the GEMV AFTER the next one will read.  The next mgq_gemv /
+ * mgq_gemv_exchange / mgq_matmul (m <= MGQ_GEMV_MAX_M) issued by the calling host thread then also
+ * asks L2 to start fetching up to "gemv.lookahead_bytes" of them, so HBM keeps streaming while
+ * the chain waits on its own dependencies.  Off unless that option is set: on B200 the decode
+ * chain is bound by per-kernel latency and instruction issue, and look-ahead measured within
+ * +-2 % of no look-ahead.  The hint is consumed by that one call.
+ * It only moves data into L2 earlier; results do not change.  next_w must be 16-byte aligned and
+ * next_bytes readable device memory; NULL clears a pending hint. */
+int mgq_gemv_lookahead(const void *next_w, size_t next_bytes);
 
 /* ---- column-sharded GEMV with a fused all-gather over peer memory (no reference counterpart: the
  * reference is single-device, src/runtime.rs:1513-1531).
@@ -142,6 +156,45 @@ int mgq_gemm(int fmt, const void *a, int a_dtype, const void *w, const float *ad
 /* Reports (and clears) a device-side timeout: every wait inside the tensor-core GEMM is bounded and
  * raises a device error word when it runs out instead of hanging.  Synchronises the device. */
 int mgq_device_status(void);
+
+/* ---- the operators between the GEMVs of a decode step (all pointers are device pointers, f32
+ * row-major; positions and token ids are u32 words in device memory, like the reference's
+ * kv_pos_buf / token_ids inputs, so that a whole step is a fixed launch sequence).
+ *
+ * mgq_embedding:        out[r, :] = table[ids[r], :]                 src/shaders/embedding.wgsl
+ * mgq_rms_norm:         out = x * rsqrt(mean(x^2) + eps) * weight     src/shaders/rms_norm.wgsl
+ * mgq_rope_dynamic:     HF half-split RoPE per head, position = row + *pos_offset
+ *                                                                    src/shaders/rope_dynamic.wgsl
+ * mgq_cache_write:      cache[*kv_pos, :] = src[0, :]                 src/shaders/cache_write.wgsl
+ * mgq_swiglu:           out = silu(gate) * up; gate/up are rows of `pitch` floats, so the
+ *                       concatenated [rows, 2*half_n] form passes gate = in, up = in + half_n,
+ *                       pitch = 2*half_n       src/shaders/swiglu_concat.wgsl, binary.wgsl (swiglu)
+ * mgq_cached_attention: one query token over cache rows 0..*kv_pos, grouped-query heads, scale
+ *                       1/sqrt(head_dim), softmax in f32; head_dim 64 or 128 (the reference's
+ *                       shader is fixed at 64), at most 8 query heads per KV head.  `workspace`
+ *                       is mgq_cached_attention_workspace(...) bytes of zero-initialised device
+ *                       memory owned by the caller (split-context partials and counters; it
+ *                       returns to its initial state).  Calls that share a workspace must be
+ *                       ordered on one stream.                       src/shaders/cached_attention.wgsl
+ * mgq_argmax:           greedy pick on the device (the reference picks on the host,
+ *                       bench/bench_meganeura.rs:255-273): *out_token = argmax(logits), lowest
+ *                       index on ties; history[*kv_pos] = token when history != NULL; when
+ *                       next_token != NULL the token is fed back (*next_token = token,
+ *                       *kv_pos += 1) so that steps can be replayed without a host round trip.
+ *                       `workspace`: mgq_argmax_workspace() bytes, zero-initialised. */
+int mgq_embedding(const uint32_t *ids, const float *table, float *out, uint32_t seq, uint32_t hidden, uint32_t vocab, void *stream);
+int mgq_rms_norm(const float *x, const float *weight, float *out, uint32_t rows, uint32_t cols, float eps, void *stream);
+int mgq_rope_dynamic(const float *x, float *out, const uint32_t *pos_offset, uint32_t seq, uint32_t dim, uint32_t head_dim,
+                     float theta, void *stream);
+int mgq_cache_write(const float *src, float *cache, const uint32_t *kv_pos, uint32_t dim, uint32_t max_seq, void *stream);
+int mgq_swiglu(const float *gate, const float *up, float *out, uint32_t rows, uint32_t half_n, uint32_t pitch, void *stream);
+size_t mgq_cached_attention_workspace(uint32_t num_kv_heads, uint32_t head_dim, uint32_t max_seq);
+int mgq_cached_attention(const float *q, const float *k_cache, const float *v_cache, const uint32_t *kv_pos, float *out,
+                         uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_dim, uint32_t max_seq, void *workspace,
+                         void *stream);
+size_t mgq_argmax_workspace(void);
+int mgq_argmax(const float *logits, uint32_t n, void *workspace, uint32_t *out_token, uint32_t *next_token, uint32_t *kv_pos,
+               uint32_t *history, uint32_t history_cap, void *stream);
 
 /* Routing wrapper: mgq_gemv when m <= MGQ_GEMV_MAX_M (f32 activations), else mgq_gemm. */
 int mgq_matmul(int fmt, const void *a, int a_dtype, const void *w, const float *addend, float *c,

@@ -60,6 +60,7 @@ SIGNATURES = {
     "mgq_buffer_download": (_int, [_vp, _vp, _sz, _vp]),
     "mgq_device_status": (_int, []),
     "mgq_gemv": (_int, [_int, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
+    "mgq_gemv_lookahead": (_int, [_vp, _sz]),
     "mgq_gemv_exchange": (_int, [_int, _vp, _vp, _vp, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
     "mgq_exchange_finish": (_int, [_vp, _u32, _vp, _vp, _vp, _vp]),
     "mgq_gemm": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),

@@ -86,6 +86,69 @@ int mgq_gemv(int fmt, const float *x, const void *w, const float *addend, float 
     return launch_gemv(fmt, x, w, addend, y, m, k, n, stream);
 }
 
+// ---- decode-step operators: argument checks, then the launchers of mgq_decode_ops.cu
+int mgq_embedding(const uint32_t *ids, const float *table, float *out, uint32_t seq, uint32_t hidden, uint32_t vocab, void *stream)
+{
+    if (!ids || !table || !out) return fail(MGQ_ERR_NULL, "embedding: null pointer");
+    if (seq == 0 || hidden == 0 || vocab == 0) return fail(MGQ_ERR_SHAPE, "embedding: empty shape");
+    return launch_embedding(ids, table, out, seq, hidden, vocab, stream);
+}
+
+int mgq_rms_norm(const float *x, const float *weight, float *out, uint32_t rows, uint32_t cols, float eps, void *stream)
+{
+    if (!x || !weight || !out) return fail(MGQ_ERR_NULL, "rms_norm: null pointer");
+    if (rows == 0 || cols == 0) return fail(MGQ_ERR_SHAPE, "rms_norm: empty shape");
+    return launch_rms_norm(x, weight, out, rows, cols, eps, stream);
+}
+
+int mgq_rope_dynamic(const float *x, float *out, const uint32_t *pos_offset, uint32_t seq, uint32_t dim, uint32_t head_dim,
+                     float theta, void *stream)
+{
+    if (!x || !out || !pos_offset) return fail(MGQ_ERR_NULL, "rope: null pointer");
+    if (seq == 0 || dim == 0 || head_dim == 0) return fail(MGQ_ERR_SHAPE, "rope: empty shape");
+    return launch_rope(x, out, pos_offset, seq, dim, head_dim, theta, stream);
+}
+
+int mgq_cache_write(const float *src, float *cache, const uint32_t *kv_pos, uint32_t dim, uint32_t max_seq, void *stream)
+{
+    if (!src || !cache || !kv_pos) return fail(MGQ_ERR_NULL, "cache_write: null pointer");
+    if (dim == 0 || max_seq == 0) return fail(MGQ_ERR_SHAPE, "cache_write: empty shape");
+    return launch_cache_write(src, cache, kv_pos, dim, max_seq, stream);
+}
+
+int mgq_swiglu(const float *gate, const float *up, float *out, uint32_t rows, uint32_t half_n, uint32_t pitch, void *stream)
+{
+    if (!gate || !up || !out) return fail(MGQ_ERR_NULL, "swiglu: null pointer");
+    if (rows == 0 || half_n == 0 || pitch < half_n) return fail(MGQ_ERR_SHAPE, "swiglu: bad shape");
+    return launch_swiglu(gate, up, out, rows, half_n, pitch, stream);
+}
+
+size_t mgq_cached_attention_workspace(uint32_t num_kv_heads, uint32_t head_dim, uint32_t max_seq)
+{
+    return attention_workspace_bytes(num_kv_heads, head_dim, max_seq);
+}
+
+int mgq_cached_attention(const float *q, const float *k_cache, const float *v_cache, const uint32_t *kv_pos, float *out,
+                         uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_dim, uint32_t max_seq, void *workspace,
+                         void *stream)
+{
+    if (!q || !k_cache || !v_cache || !kv_pos || !out) return fail(MGQ_ERR_NULL, "cached_attention: null pointer");
+    if (max_seq == 0) return fail(MGQ_ERR_SHAPE, "cached_attention: empty cache");
+    return launch_cached_attention(q, k_cache, v_cache, kv_pos, out, num_heads, num_kv_heads, head_dim, max_seq, workspace, stream);
+}
+
+size_t mgq_argmax_workspace(void) { return argmax_workspace_bytes(); }
+
+int mgq_argmax(const float *logits, uint32_t n, void *workspace, uint32_t *out_token, uint32_t *next_token, uint32_t *kv_pos,
+               uint32_t *history, uint32_t history_cap, void *stream)
+{
+    if (!logits || !out_token) return fail(MGQ_ERR_NULL, "argmax: null pointer");
+    if (n == 0) return fail(MGQ_ERR_SHAPE, "argmax: empty vector");
+    return launch_argmax(logits, n, workspace, out_token, next_token, kv_pos, history, history_cap, stream);
+}
+
+int mgq_gemv_lookahead(const void *next_w, size_t next_bytes) { return set_gemv_lookahead(next_w, next_bytes); }
+
 int mgq_gemv_exchange(int fmt, const float *x, const void *w, const float *addend, float *y, uint32_t k, uint32_t n,
                       const mgq_exchange_push *push_dev, const mgq_exchange_elem *wait_vec,
                       const unsigned long long *epoch, unsigned int *error, void *stream)

@@ -1,0 +1,403 @@
+// The operators that sit between the quantized GEMVs of a decode step, as plain CUDA kernels:
+// embedding lookup, RMSNorm, RoPE with a device-side position, KV-cache write, single-token cached
+// attention, SwiGLU, and a device-side greedy pick.  Semantics follow meganeura's shaders
+//   src/shaders/embedding.wgsl, rms_norm.wgsl, rope_dynamic.wgsl, cache_write.wgsl,
+//   cached_attention.wgsl, swiglu_concat.wgsl (forward), binary.wgsl (swiglu)
+// and their lowering in src/compile.rs (Op::Embedding, Op::RmsNorm, Op::RoPE with a dynamic offset,
+// Op::CacheWrite, Op::CachedAttention, Op::SwiGLU, Op::SwiGLUConcat).
+//
+// All of them are tiny next to the GEMVs (a few KB to a few MB per launch), so the design goal is
+// latency: every kernel is launched with programmatic stream serialization, does its index
+// arithmetic, then waits for its predecessor (griddepcontrol.wait) right before the first load.
+// The position / token inputs live in device memory (like the reference's kv_pos_buf), so a whole
+// decode step is a fixed launch sequence that can be replayed from a CUDA graph.
+#include <cuda_runtime.h>
+
+#include <cfloat>
+#include <cstdint>
+
+#include "mgq_internal.h"
+
+namespace mgq {
+namespace {
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+template <typename... Args>
+int launch(void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args)
+{
+    cudaLaunchConfig_t lc{};
+    lc.gridDim = grid;
+    lc.blockDim = block;
+    lc.dynamicSmemBytes = smem;
+    lc.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    MGQ_CUDA(cudaLaunchKernelEx(&lc, kernel, args...));
+    return MGQ_OK;
+}
+
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// ---------------------------------------------------------------- embedding (embedding.wgsl)
+__global__ void embedding_kernel(const uint32_t *ids, const float *table, float *out, uint32_t seq, uint32_t hidden,
+                                 uint32_t vocab)
+{
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;          // float4 index
+    const uint32_t per_row = hidden / 4;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (i >= seq * per_row) return;
+    const uint32_t row = i / per_row, col = i - row * per_row;
+    uint32_t tok = ids[row];
+    if (tok >= vocab) tok = vocab - 1;                                  // the reference would read out of bounds
+    reinterpret_cast<float4 *>(out)[i] = reinterpret_cast<const float4 *>(table)[(size_t)tok * per_row + col];
+}
+
+// ---------------------------------------------------------------- RMSNorm (rms_norm.wgsl)
+// One CTA per row: dst = src * rsqrt(mean(src^2) + eps) * weight.
+__global__ void __launch_bounds__(256) rms_norm_kernel(const float *src, const float *weight, float *dst, uint32_t cols, float eps)
+{
+    __shared__ float s_part[8];
+    const uint32_t row = blockIdx.x, t = threadIdx.x;
+    const float4 *x4 = reinterpret_cast<const float4 *>(src + (size_t)row * cols);
+    const float4 *w4 = reinterpret_cast<const float4 *>(weight);
+    float4 *y4 = reinterpret_cast<float4 *>(dst + (size_t)row * cols);
+    const uint32_t n4 = cols / 4;
+    pdl_launch_dependents();
+    pdl_wait();
+    float ss = 0.f;
+    for (uint32_t j = t; j < n4; j += 256) {
+        const float4 v = x4[j];
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = warp_sum(ss);
+    if ((t & 31u) == 0) s_part[t >> 5] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) total += s_part[i];
+    const float r = rsqrtf(total / (float)cols + eps);
+    for (uint32_t j = t; j < n4; j += 256) {
+        const float4 v = x4[j], w = w4[j];
+        y4[j] = make_float4(v.x * r * w.x, v.y * r * w.y, v.z * r * w.z, v.w * r * w.w);
+    }
+}
+
+// ---------------------------------------------------------------- RoPE, dynamic offset (rope_dynamic.wgsl)
+// HF half-split pairs inside each head; position = row + *pos_offset.
+__global__ void rope_kernel(const float *src, float *dst, const uint32_t *pos_offset, uint32_t seq, uint32_t dim,
+                            uint32_t head_dim, float theta)
+{
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t half_dim = dim / 2, half_head = head_dim / 2;
+    pdl_launch_dependents();
+    if (i >= seq * half_dim) { pdl_wait(); return; }
+    const uint32_t row = i / half_dim, pair_in_row = i - row * half_dim;
+    const uint32_t head = pair_in_row / half_head, pair_in_head = pair_in_row - head * half_head;
+    const float inv_freq = powf(theta, -2.0f * (float)pair_in_head / (float)head_dim);
+    pdl_wait();
+    const float angle = (float)(row + pos_offset[0]) * inv_freq;
+    float s, c;
+    sincosf(angle, &s, &c);
+    const uint32_t idx0 = row * dim + head * head_dim + pair_in_head, idx1 = idx0 + half_head;
+    const float v0 = src[idx0], v1 = src[idx1];
+    dst[idx0] = v0 * c - v1 * s;
+    dst[idx1] = v0 * s + v1 * c;
+}
+
+// ---------------------------------------------------------------- KV-cache write (cache_write.wgsl)
+__global__ void cache_write_kernel(const float *src, float *cache, const uint32_t *kv_pos, uint32_t dim, uint32_t max_seq)
+{
+    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t pos = kv_pos[0];
+    if (j < dim && pos < max_seq) cache[(size_t)pos * dim + j] = src[j];
+}
+
+// ---------------------------------------------------------------- SwiGLU (binary.wgsl swiglu, swiglu_concat.wgsl)
+// out[r, c] = silu(gate[r, c]) * up[r, c]; gate and up are rows of pitch `pitch` floats (for the
+// concatenated form both point into the same [rows, 2*half_n] matrix).
+__global__ void swiglu_kernel(const float *gate, const float *up, float *out, uint32_t rows, uint32_t half_n, uint32_t pitch)
+{
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (i >= rows * half_n) return;
+    const uint32_t row = i / half_n, col = i - row * half_n;
+    const float g = gate[(size_t)row * pitch + col], u = up[(size_t)row * pitch + col];
+    const float sig = 1.0f / (1.0f + expf(-g));
+    out[i] = g * sig * u;
+}
+
+// ---------------------------------------------------------------- cached attention (cached_attention.wgsl)
+// One query token against positions 0..kv_pos of the cache.  The reference runs one 64-thread
+// workgroup per query head over the whole context with an online softmax; here the context is cut
+// into chunks of kChunk positions and a CTA takes one chunk for ALL query heads of one KV head
+// (grouped-query attention reads each K/V row once, not once per query head).  Every CTA leaves an
+// unnormalised partial (max, sum, weighted V) in the workspace; the CTA of a KV head that finishes
+// last merges the partials -- the same online-softmax algebra, applied across chunks.
+constexpr int kChunk = 64;
+constexpr int kMaxGroup = 8;          // query heads per KV head
+
+template <int D>                      // head_dim: 64 or 128; blockDim.x == 128
+__global__ void __launch_bounds__(128) cached_attention_kernel(const float *q, const float *k_cache, const float *v_cache,
+                                                               const uint32_t *kv_pos, float *out, uint32_t num_heads,
+                                                               uint32_t num_kv_heads, uint32_t max_seq, float *workspace,
+                                                               unsigned int *counters)
+{
+    constexpr int LPP = D / 4;                    // lanes per position (each lane holds a float4 of the row)
+    constexpr int PPW = 32 / LPP;                 // positions per warp step
+    __shared__ float s_score[kMaxGroup][kChunk];
+    __shared__ float s_q[kMaxGroup][D];
+    __shared__ float s_acc[128 / D][kMaxGroup][D];
+    __shared__ bool s_last;
+    const uint32_t kvh = blockIdx.x, chunk = blockIdx.y, splits = gridDim.y;
+    const uint32_t t = threadIdx.x, lane = t & 31u, warp = t >> 5;
+    const uint32_t group = num_heads / num_kv_heads, kv_dim = num_kv_heads * D;
+    const float scale = rsqrtf((float)D);
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t kv_len = min(kv_pos[0] + 1u, max_seq);
+    const uint32_t p0 = chunk * kChunk, p1 = min(p0 + kChunk, kv_len);
+    float *part = workspace + ((size_t)kvh * splits + chunk) * kMaxGroup * (D + 2);      // [group][D + 2]: acc, max, sum
+
+    if (p0 < kv_len) {
+        for (uint32_t i = t; i < group * D; i += 128) s_q[i / D][i % D] = q[(size_t)kvh * group * D + i];
+        __syncthreads();
+        // scores: PPW positions per warp step, LPP lanes per position
+        const uint32_t sub = lane / LPP, li = lane % LPP;
+        for (uint32_t p = p0 + warp * PPW + sub; p < p0 + kChunk; p += 4 * PPW) {
+            float dot[kMaxGroup];
+#pragma unroll
+            for (int g = 0; g < kMaxGroup; g++) dot[g] = 0.f;
+            if (p < p1) {
+                const float4 kv = *reinterpret_cast<const float4 *>(k_cache + (size_t)p * kv_dim + kvh * D + li * 4);
+#pragma unroll
+                for (int g = 0; g < kMaxGroup; g++) {
+                    if (g < (int)group) {
+                        const float4 qv = *reinterpret_cast<const float4 *>(&s_q[g][li * 4]);
+                        dot[g] = kv.x * qv.x + kv.y * qv.y + kv.z * qv.z + kv.w * qv.w;
+                    }
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < kMaxGroup; g++) {
+                if (g < (int)group) {
+#pragma unroll
+                    for (int o = LPP / 2; o > 0; o >>= 1) dot[g] += __shfl_xor_sync(0xffffffffu, dot[g], o);
+                    if (li == 0) s_score[g][p - p0] = p < p1 ? dot[g] * scale : -FLT_MAX;
+                }
+            }
+        }
+        __syncthreads();
+        // per head: chunk maximum and exponentials (warp w takes heads w, w+4)
+        for (uint32_t g = warp; g < group; g += 4) {
+            float m = fmaxf(s_score[g][lane], s_score[g][lane + 32]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            const float e0 = p0 + lane < p1 ? expf(s_score[g][lane] - m) : 0.f;
+            const float e1 = p0 + lane + 32 < p1 ? expf(s_score[g][lane + 32] - m) : 0.f;
+            s_score[g][lane] = e0;
+            s_score[g][lane + 32] = e1;
+            const float l = warp_sum(e0 + e1);
+            if (lane == 0) { part[g * (D + 2) + D] = m; part[g * (D + 2) + D + 1] = l; }
+        }
+        __syncthreads();
+        // weighted V: thread <-> (position parity slice, dim); 128 / D slices
+        const uint32_t d = t % D, slice = t / D;
+        constexpr uint32_t SL = 128 / D;
+        float acc[kMaxGroup];
+#pragma unroll
+        for (int g = 0; g < kMaxGroup; g++) acc[g] = 0.f;
+        for (uint32_t p = p0 + slice; p < p1; p += SL) {
+            const float v = v_cache[(size_t)p * kv_dim + kvh * D + d];
+#pragma unroll
+            for (int g = 0; g < kMaxGroup; g++)
+                if (g < (int)group) acc[g] = fmaf(s_score[g][p - p0], v, acc[g]);
+        }
+#pragma unroll
+        for (int g = 0; g < kMaxGroup; g++)
+            if (g < (int)group) s_acc[slice][g][d] = acc[g];
+        __syncthreads();
+        if (slice == 0) {
+            for (uint32_t g = 0; g < group; g++) {
+                float a = s_acc[0][g][d];
+                if (SL > 1) a += s_acc[SL - 1][g][d];
+                part[g * (D + 2) + d] = a;
+            }
+        }
+    }
+    // the last CTA of this KV head merges
+    __threadfence();
+    __syncthreads();
+    if (t == 0) {
+        const unsigned int done = atomicAdd(&counters[kvh], 1u);
+        s_last = done == splits - 1;
+        if (s_last) counters[kvh] = 0;                       // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const uint32_t live = (kv_len + kChunk - 1) / kChunk;
+    const float *base = workspace + (size_t)kvh * splits * kMaxGroup * (D + 2);
+    for (uint32_t i = t; i < group * D; i += 128) {
+        const uint32_t g = i / D, d = i % D;
+        float m = -FLT_MAX;
+        for (uint32_t c = 0; c < live; c++) m = fmaxf(m, __ldcg(base + ((size_t)c * kMaxGroup + g) * (D + 2) + D));
+        float l = 0.f, a = 0.f;
+        for (uint32_t c = 0; c < live; c++) {
+            const float *pc = base + ((size_t)c * kMaxGroup + g) * (D + 2);
+            const float w = expf(__ldcg(pc + D) - m);
+            l = fmaf(__ldcg(pc + D + 1), w, l);
+            a = fmaf(__ldcg(pc + d), w, a);
+        }
+        out[(size_t)(kvh * group + g) * D + d] = a / (l == 0.f ? 1.f : l);
+    }
+}
+
+// ---------------------------------------------------------------- greedy pick
+// argmax over the logits (lowest index wins ties, like a sequential host scan); the CTA that
+// finishes last writes the winner to *out_token, appends it to the history and, when asked,
+// feeds it back: *next_token = winner, *kv_pos += 1.
+__global__ void __launch_bounds__(256) argmax_kernel(const float *logits, uint32_t n, float *part_val, uint32_t *part_idx,
+                                                     unsigned int *counter, uint32_t *out_token, uint32_t *next_token,
+                                                     uint32_t *kv_pos, uint32_t *history, uint32_t history_cap)
+{
+    __shared__ float s_val[8];
+    __shared__ uint32_t s_idx[8];
+    __shared__ bool s_last;
+    const uint32_t t = threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    float best = -FLT_MAX;
+    uint32_t best_i = 0xFFFFFFFFu;
+    for (uint32_t i = blockIdx.x * 256 + t; i < n; i += gridDim.x * 256) {
+        const float v = logits[i];
+        if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+    }
+    auto merge = [](float &bv, uint32_t &bi, float ov, uint32_t oi) {
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        merge(best, best_i, ov, oi);
+    }
+    if ((t & 31u) == 0) { s_val[t >> 5] = best; s_idx[t >> 5] = best_i; }
+    __syncthreads();
+    if (t == 0) {
+        for (int w = 1; w < 8; w++) merge(best, best_i, s_val[w], s_idx[w]);
+        part_val[blockIdx.x] = best;
+        part_idx[blockIdx.x] = best_i;
+        __threadfence();
+        const unsigned int done = atomicAdd(counter, 1u);
+        s_last = done == gridDim.x - 1;
+        if (s_last) *counter = 0;
+    }
+    __syncthreads();
+    if (!s_last || t != 0) return;
+    __threadfence();
+    best = -FLT_MAX;
+    best_i = 0xFFFFFFFFu;
+    for (uint32_t b = 0; b < gridDim.x; b++) merge(best, best_i, __ldcg(part_val + b), __ldcg(part_idx + b));
+    if (best_i == 0xFFFFFFFFu) best_i = 0;                   // every logit was NaN
+    *out_token = best_i;
+    if (history && kv_pos && kv_pos[0] < history_cap) history[kv_pos[0]] = best_i;
+    if (next_token) *next_token = best_i;
+    if (kv_pos && next_token) kv_pos[0] += 1;
+}
+
+}  // namespace
+
+int launch_embedding(const uint32_t *ids, const float *table, float *out, uint32_t seq, uint32_t hidden, uint32_t vocab, void *stream)
+{
+    if (hidden % 4 != 0) return fail(MGQ_ERR_SHAPE, "embedding width %u must be a multiple of 4", hidden);
+    const uint32_t total = seq * (hidden / 4);
+    return launch(embedding_kernel, dim3((total + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream), ids, table, out, seq,
+                  hidden, vocab);
+}
+
+int launch_rms_norm(const float *x, const float *weight, float *out, uint32_t rows, uint32_t cols, float eps, void *stream)
+{
+    if (cols % 4 != 0) return fail(MGQ_ERR_SHAPE, "rms_norm width %u must be a multiple of 4", cols);
+    return launch(rms_norm_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), x, weight, out, cols, eps);
+}
+
+int launch_rope(const float *x, float *out, const uint32_t *pos_offset, uint32_t seq, uint32_t dim, uint32_t head_dim, float theta,
+                void *stream)
+{
+    if (dim % 2 || head_dim % 2 || dim % head_dim) return fail(MGQ_ERR_SHAPE, "rope: dim %u / head_dim %u", dim, head_dim);
+    const uint32_t total = seq * (dim / 2);
+    return launch(rope_kernel, dim3((total + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream), x, out, pos_offset, seq, dim,
+                  head_dim, theta);
+}
+
+int launch_cache_write(const float *src, float *cache, const uint32_t *kv_pos, uint32_t dim, uint32_t max_seq, void *stream)
+{
+    return launch(cache_write_kernel, dim3((dim + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream), src, cache, kv_pos, dim,
+                  max_seq);
+}
+
+int launch_swiglu(const float *gate, const float *up, float *out, uint32_t rows, uint32_t half_n, uint32_t pitch, void *stream)
+{
+    const uint32_t total = rows * half_n;
+    return launch(swiglu_kernel, dim3((total + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream), gate, up, out, rows, half_n,
+                  pitch);
+}
+
+size_t attention_workspace_bytes(uint32_t num_kv_heads, uint32_t head_dim, uint32_t max_seq)
+{
+    const size_t splits = (max_seq + kChunk - 1) / kChunk;
+    return 256 + (size_t)num_kv_heads * splits * kMaxGroup * (head_dim + 2) * sizeof(float);   // 256 B of counters first
+}
+
+int launch_cached_attention(const float *q, const float *k_cache, const float *v_cache, const uint32_t *kv_pos, float *out,
+                            uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_dim, uint32_t max_seq, void *workspace,
+                            void *stream)
+{
+    if (num_kv_heads == 0 || num_heads % num_kv_heads != 0) return fail(MGQ_ERR_SHAPE, "attention: %u heads over %u KV heads", num_heads, num_kv_heads);
+    if (num_heads / num_kv_heads > (uint32_t)kMaxGroup) return fail(MGQ_ERR_SHAPE, "attention: at most %d query heads per KV head", kMaxGroup);
+    if (num_kv_heads > 64) return fail(MGQ_ERR_SHAPE, "attention: at most 64 KV heads");
+    if (!workspace) return fail(MGQ_ERR_NULL, "attention needs its workspace");
+    unsigned int *counters = static_cast<unsigned int *>(workspace);
+    float *partials = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + 256);
+    const dim3 grid(num_kv_heads, (max_seq + kChunk - 1) / kChunk);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (head_dim == 64)
+        return launch(cached_attention_kernel<64>, grid, dim3(128), 0, st, q, k_cache, v_cache, kv_pos, out, num_heads, num_kv_heads,
+                      max_seq, partials, counters);
+    if (head_dim == 128)
+        return launch(cached_attention_kernel<128>, grid, dim3(128), 0, st, q, k_cache, v_cache, kv_pos, out, num_heads, num_kv_heads,
+                      max_seq, partials, counters);
+    return fail(MGQ_ERR_SHAPE, "attention: head_dim %u (64 and 128 are built)", head_dim);
+}
+
+size_t argmax_workspace_bytes() { return 256 + 2 * 256 * sizeof(float); }
+
+int launch_argmax(const float *logits, uint32_t n, void *workspace, uint32_t *out_token, uint32_t *next_token, uint32_t *kv_pos,
+                  uint32_t *history, uint32_t history_cap, void *stream)
+{
+    if (!workspace) return fail(MGQ_ERR_NULL, "argmax needs its workspace");
+    unsigned int *counter = static_cast<unsigned int *>(workspace);
+    float *part_val = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + 256);
+    uint32_t *part_idx = reinterpret_cast<uint32_t *>(part_val + 256);
+    uint32_t grid = (n + 256 * 8 - 1) / (256 * 8);
+    if (grid > 256) grid = 256;
+    if (grid < 1) grid = 1;
+    return launch(argmax_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), logits, n, part_val, part_idx, counter,
+                  out_token, next_token, kv_pos, history, history_cap);
+}
+
+}  // namespace mgq

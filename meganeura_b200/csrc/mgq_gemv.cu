@@ -35,6 +35,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 #include <vector>
 
 #include "mgq_gemv_device.cuh"
@@ -50,53 +51,73 @@ using namespace dev;
 // A "group" is cpi consecutive columns: one block for each of the `active` threads.  A CTA owns
 // the groups [g0, g1); a pipeline stage holds C consecutive groups, so a thread works on C
 // columns with the same activations before it touches the ring again.
+//
+// TS is the launch bound and the stride of every shared-memory array (threads <= TS), so that all
+// shared-memory addressing folds into immediates.  Threads beyond `active` shadow the last active
+// thread: they fetch and compute like everybody else, and nothing ever reads what they produce.
+// A CTA runs "fast" rounds, in which every fetch and every block is known to be in range and the
+// code carries no predicates, and then at most a few "checked" rounds at the end of its range.
 constexpr int kStages = 4;
 
-template <int MT, int C, int TMAX>
-__global__ void __launch_bounds__(TMAX) gemv_q4_kernel(const GemvParams p)
+struct CtaRange {
+    uint32_t g0, g1, n_g;
+    uint32_t n_full;     // leading groups of the range in which every column of the group exists (CTA-uniform)
+};
+
+__device__ __forceinline__ CtaRange cta_range(const GemvParams &p)
+{
+    CtaRange r;
+    r.g0 = (uint32_t)((unsigned long long)blockIdx.x * p.total_iters / gridDim.x);
+    r.g1 = (uint32_t)((unsigned long long)(blockIdx.x + 1) * p.total_iters / gridDim.x);
+    r.n_g = r.g1 - r.g0;
+    const bool ragged_end = r.g1 == p.total_iters && r.n_g > 0 && p.total_iters * p.cpi != p.n;
+    r.n_full = ragged_end ? r.n_g - 1 : r.n_g;
+    return r;
+}
+
+template <int MT, int C, int TS>
+__global__ void __launch_bounds__(TS) gemv_q4_kernel(const GemvParams p)
 {
     constexpr int STAGES = kStages, ROUND = kStages * C;
     extern __shared__ __align__(16) uint8_t smem[];
-    const uint32_t T = blockDim.x, t = threadIdx.x;
-    uint4 *s_nib = reinterpret_cast<uint4 *>(smem) + t;                                  // [STAGES*C][T], own slot
-    uint32_t *s_hdr = reinterpret_cast<uint32_t *>(smem + (size_t)ROUND * T * 16) + t;   // [STAGES*C][T], own slot
-    float *s_red = reinterpret_cast<float *>(smem + (size_t)ROUND * T * 20);             // [2][MT][ROUND][T]
+    const uint32_t t = threadIdx.x;
+    uint4 *s_nib = reinterpret_cast<uint4 *>(smem) + t;                                  // [ROUND][TS], own slot
+    uint32_t *s_hdr = reinterpret_cast<uint32_t *>(smem + ROUND * TS * 16) + t;          // [ROUND][TS], own slot
+    float *s_red = reinterpret_cast<float *>(smem + ROUND * TS * 20);                    // [2][MT][ROUND][TS] (+ [TS])
     MGQ_STAMP(p, 0);
 
-    const uint32_t g0 = (uint32_t)((unsigned long long)blockIdx.x * p.total_iters / gridDim.x);
-    const uint32_t g1 = (uint32_t)((unsigned long long)(blockIdx.x + 1) * p.total_iters / gridDim.x);
-    const uint32_t n_g = g1 - g0;
-    const bool has_block = t < p.active;
-    const uint32_t b = t % p.bpc, csub = t / p.bpc;
-    // groups in which this thread has a column: all of them, except that the very last group of
-    // the matrix may hold fewer than cpi columns
-    uint32_t my_n = has_block ? n_g : 0u;
-    if (has_block && g1 == p.total_iters && n_g > 0 && (p.total_iters - 1) * p.cpi + csub >= p.n) my_n = n_g - 1;
+    const CtaRange cr = cta_range(p);
+    const uint32_t tt = t < p.active ? t : p.active - 1;
+    const uint32_t b = tt % p.bpc, csub = tt / p.bpc;
+    // groups in which this thread's column exists: all, except that the very last group of the
+    // matrix may hold fewer than cpi columns
+    const uint32_t my_n = (cr.n_full != cr.n_g && (p.total_iters - 1) * p.cpi + csub >= p.n) ? cr.n_g - 1 : cr.n_g;
 
-    const unsigned long long first = (unsigned long long)g0 * p.active + t;              // = col*bpc + b
-    const uint32_t *hdr_next = reinterpret_cast<const uint32_t *>(p.w) + first;
-    const uint4 *nib_next = reinterpret_cast<const uint4 *>(p.w + p.num_blocks * 4) + first;
+    const unsigned long long first = (unsigned long long)cr.g0 * p.active + tt;          // = col*bpc + b
+    const uint32_t *hdr_base = reinterpret_cast<const uint32_t *>(p.w) + first;
+    const uint4 *nib_base = reinterpret_cast<const uint4 *>(p.w + p.num_blocks * 4) + first;
     const uint32_t stride = p.active;
+    uint32_t off = 0;                                                                    // blocks from `first` to the next fetch
     uint32_t g_next = 0;                                                                 // next group to fetch
 
-    auto issue = [&](int stage, bool checked) {
+    auto issue = [&](int stage, auto checked) {
 #pragma unroll
         for (int j = 0; j < C; j++) {
-            if (!checked || g_next + j < my_n) {
-                cp_async16(s_nib + (stage * C + j) * T, nib_next);
-                cp_async4(s_hdr + (stage * C + j) * T, hdr_next);
+            if (!decltype(checked)::value || g_next + j < my_n) {
+                cp_async16(s_nib + (stage * C + j) * TS, nib_base + off);
+                cp_async4(s_hdr + (stage * C + j) * TS, hdr_base + off);
             }
-            nib_next += stride;
-            hdr_next += stride;
+            off += stride;
         }
-        g_next += C;
+        if (decltype(checked)::value) g_next += C;
         cp_async_commit();
     };
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; s++) issue(s, true);                    // weights first: they depend on nothing
+    for (int s = 0; s < STAGES - 1; s++) issue(s, std::true_type{});       // weights first: they depend on nothing
+    prefetch_ahead(p);
     grid_launch_dependents();
     grid_dependency_wait();                                                 // x, addend and y belong to earlier kernels
-    exchange_poll(p, b);                                                    // ... or to other GPUs
+    exchange_poll(p, t % p.bpc);                                            // ... or to other GPUs
     MGQ_STAMP(p, 1);
 
     XBlock xb[MT];
@@ -107,61 +128,62 @@ __global__ void __launch_bounds__(TMAX) gemv_q4_kernel(const GemvParams p)
         if (p.x) load_x<1, false>(p.x + (size_t)r * p.k, b, xb[r]);
         else     load_x_gathered<1>(p.wait_vec, b, xb[r]);
     }
-    const ReduceSlot slot = make_slot<ROUND>(p);
+    const ReduceSlot slot = make_slot<ROUND, TS>(p);
 
-    auto block_sum = [&](int idx, float (&out)[MT]) {
-        const uint4 q = s_nib[idx * T];
-        const uint32_t h = s_hdr[idx * T];
+    auto block_sum = [&](int idx, float (&part)[MT][ROUND]) {
+        const uint4 q = s_nib[idx * TS];
+        const uint32_t h = s_hdr[idx * TS];
         const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&h));       // (d, m), IEEE
 #pragma unroll
-        for (int r = 0; r < MT; r++) out[r] = fmaf(dm.x * xb[r].inv, dot_q4(q, xb[r]), dm.y * xb[r].sum);
+        for (int r = 0; r < MT; r++) part[r][idx] = fmaf(dm.x * xb[r].inv, dot_q4(q, xb[r]), dm.y * xb[r].sum);
     };
 
-    uint32_t round = 0;
-    for (uint32_t g = 0; g < n_g; g += ROUND, round++) {
+    auto do_round = [&](uint32_t g, uint32_t round, auto checked) {
         float part[MT][ROUND];
-        const bool all_in_range = g + 2 * ROUND - C <= my_n;   // this round and everything it prefetches
 #pragma unroll
         for (int u = 0; u < STAGES; u++) {
-            issue((u + STAGES - 1) % STAGES, !all_in_range);
+            issue((u + STAGES - 1) % STAGES, checked);
             cp_async_wait<STAGES - 1>();
 #pragma unroll
             for (int j = 0; j < C; j++) {
-                float out[MT];
+                // past the end of the range the slot holds stale bytes; what is computed from them
+                // belongs to no column, but skipping it saves the time
+                if (!decltype(checked)::value || g + u * C + j < cr.n_g) block_sum(u * C + j, part);
+                else {
 #pragma unroll
-                for (int r = 0; r < MT; r++) out[r] = 0.f;
-                if (all_in_range || g + u * C + j < my_n) block_sum(u * C + j, out);
-#pragma unroll
-                for (int r = 0; r < MT; r++) part[r][u * C + j] = out[r];
+                    for (int r = 0; r < MT; r++) part[r][u * C + j] = 0.f;
+                }
             }
         }
         if (round == 0) MGQ_STAMP(p, 2);
-        reduce_store<MT, ROUND, true>(p, slot, s_red + (size_t)(round & 1) * MT * ROUND * T, part, g0 + g, g1,
-                                      p.push ? s_red + (size_t)2 * MT * ROUND * T : nullptr);
-    }
+        reduce_store<MT, ROUND, true, TS>(p, slot, s_red + (round & 1) * MT * ROUND * TS, part, cr.g0 + g, cr.g1,
+                                          p.push ? s_red + 2 * MT * ROUND * TS : nullptr);
+    };
+
+    uint32_t g = 0, round = 0;
+    // fast rounds: the round itself and everything it prefetches (STAGES-1 stages ahead) is in range
+    for (; g + 2 * ROUND - C <= cr.n_full; g += ROUND, round++) do_round(g, round, std::false_type{});
+    g_next = g + (STAGES - 1) * C;
+    for (; g < cr.n_g; g += ROUND, round++) do_round(g, round, std::true_type{});
     cp_async_wait<0>();
     MGQ_STAMP(p, 3);
 }
 
 // ------------------------------------------------------------------------------------ Q8
 
-template <int MT, int C, int TMAX>
-__global__ void __launch_bounds__(TMAX) gemv_q8_kernel(const GemvParams p)
+template <int MT, int C, int TS>
+__global__ void __launch_bounds__(TS) gemv_q8_kernel(const GemvParams p)
 {
     constexpr int STAGES = kStages, ROUND = kStages * C;
     extern __shared__ __align__(16) uint8_t smem[];
-    const uint32_t T = blockDim.x, t = threadIdx.x, lane = t & 31u, warp = t >> 5, W = T >> 5;
-    uint8_t *s_w = smem + (size_t)warp * ROUND * kQ8WarpStage;                          // this warp's ring [STAGES*C][1152]
-    float *s_red = reinterpret_cast<float *>(smem + (size_t)W * ROUND * kQ8WarpStage);    // [2][MT][ROUND][T]
+    const uint32_t t = threadIdx.x, lane = t & 31u, warp = t >> 5;
+    uint8_t *s_w = smem + warp * (ROUND * kQ8WarpStage);                                 // this warp's ring [ROUND][1152]
+    float *s_red = reinterpret_cast<float *>(smem + (TS / 32) * ROUND * kQ8WarpStage);   // [2][MT][ROUND][TS] (+ [TS])
     MGQ_STAMP(p, 0);
 
-    const uint32_t g0 = (uint32_t)((unsigned long long)blockIdx.x * p.total_iters / gridDim.x);
-    const uint32_t g1 = (uint32_t)((unsigned long long)(blockIdx.x + 1) * p.total_iters / gridDim.x);
-    const uint32_t n_g = g1 - g0;
-    const bool has_block = t < p.active;
-    const uint32_t b = t % p.bpc, csub = t / p.bpc;
-    uint32_t my_n = has_block ? n_g : 0u;
-    if (has_block && g1 == p.total_iters && n_g > 0 && (p.total_iters - 1) * p.cpi + csub >= p.n) my_n = n_g - 1;
+    const CtaRange cr = cta_range(p);
+    const uint32_t tt = t < p.active ? t : p.active - 1;
+    const uint32_t b = tt % p.bpc;
 
     // A warp owns 32 consecutive blocks of each group: `full` of them in every group, and `last`
     // of them in the final group of the matrix (which may hold fewer columns).  active is a
@@ -170,33 +192,43 @@ __global__ void __launch_bounds__(TMAX) gemv_q8_kernel(const GemvParams p)
     const uint32_t full = p.active > w0 ? min(32u, p.active - w0) : 0u;
     const uint32_t last_live = (p.n - (p.total_iters - 1) * p.cpi) * p.bpc;
     const uint32_t last = last_live > w0 ? min(32u, last_live - w0) : 0u;
-    const uint32_t last_group = g1 == p.total_iters ? n_g - 1 : 0xFFFFFFFFu;             // index inside this CTA's range
-    const uint8_t *src_next = p.w + ((unsigned long long)g0 * p.active + w0) * 36ull + 16u * lane;
+    const uint32_t last_group = cr.g1 == p.total_iters ? cr.n_g - 1 : 0xFFFFFFFFu;       // index inside this CTA's range
+    const uint8_t *src_base = p.w + ((unsigned long long)cr.g0 * p.active + w0) * 36ull + 16u * lane;
     const uint32_t stride = p.active * 36u;
+    uint32_t off = 0;                                                                    // bytes from src_base to the next fetch
     uint32_t g_next = 0;
+    const bool whole_warp = full == 32u;                                                 // 1152 bytes per group: 72 pieces
 
-    auto issue = [&](int stage) {
+    auto issue = [&](int stage, auto checked) {
 #pragma unroll
         for (int j = 0; j < C; j++) {
-            const uint32_t gi = g_next + j;
-            if (gi < n_g) {
-                const uint32_t cnt = gi == last_group ? last : full;
-                const uint32_t pieces = (cnt * 36u + 15u) >> 4;
-                uint8_t *dst = s_w + (stage * C + j) * kQ8WarpStage + 16u * lane;
-                if (lane < pieces) cp_async16(dst, src_next);
-                if (lane + 32u < pieces) cp_async16(dst + 512, src_next + 512);
-                if (lane + 64u < pieces) cp_async16(dst + 1024, src_next + 1024);
+            uint8_t *dst = s_w + (stage * C + j) * kQ8WarpStage + 16u * lane;
+            const uint8_t *src = src_base + off;
+            if (!decltype(checked)::value && whole_warp) {
+                cp_async16(dst, src);
+                cp_async16(dst + 512, src + 512);
+                if (lane < 8u) cp_async16(dst + 1024, src + 1024);
+            } else {
+                const uint32_t gi = g_next + j;
+                if (!decltype(checked)::value || gi < cr.n_g) {
+                    const uint32_t cnt = (decltype(checked)::value && gi == last_group) ? last : full;
+                    const uint32_t pieces = (cnt * 36u + 15u) >> 4;
+                    if (lane < pieces) cp_async16(dst, src);
+                    if (lane + 32u < pieces) cp_async16(dst + 512, src + 512);
+                    if (lane + 64u < pieces) cp_async16(dst + 1024, src + 1024);
+                }
             }
-            src_next += stride;
+            off += stride;
         }
-        g_next += C;
+        if (decltype(checked)::value) g_next += C;
         cp_async_commit();
     };
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; s++) issue(s);
+    for (int s = 0; s < STAGES - 1; s++) issue(s, std::true_type{});
+    prefetch_ahead(p);
     grid_launch_dependents();
     grid_dependency_wait();
-    exchange_poll(p, b);
+    exchange_poll(p, t % p.bpc);
     MGQ_STAMP(p, 1);
 
     XBlock xb[MT];
@@ -205,39 +237,42 @@ __global__ void __launch_bounds__(TMAX) gemv_q8_kernel(const GemvParams p)
         if (p.x) load_x<0, false>(p.x + (size_t)r * p.k, b, xb[r]);
         else     load_x_gathered<0>(p.wait_vec, b, xb[r]);
     }
-    const ReduceSlot slot = make_slot<ROUND>(p);
+    const ReduceSlot slot = make_slot<ROUND, TS>(p);
 
-    auto block_sum = [&](int idx, float (&out)[MT]) {
+    auto block_sum = [&](int idx, float (&part)[MT][ROUND]) {
         const uint32_t *bp = reinterpret_cast<const uint32_t *>(s_w + idx * kQ8WarpStage + 36u * lane);
         const uint32_t sw = bp[0];
         const float scale = __half2float(__ushort_as_half((unsigned short)(sw & 0xFFFFu)));
 #pragma unroll
-        for (int r = 0; r < MT; r++) out[r] = scale * xb[r].inv * dot_q8(bp + 1, xb[r]);
+        for (int r = 0; r < MT; r++) part[r][idx] = scale * xb[r].inv * dot_q8(bp + 1, xb[r]);
     };
 
-    uint32_t round = 0;
-    for (uint32_t g = 0; g < n_g; g += ROUND, round++) {
+    auto do_round = [&](uint32_t g, uint32_t round, auto checked) {
         float part[MT][ROUND];
 #pragma unroll
         for (int u = 0; u < STAGES; u++) {
             __syncwarp();                                   // every lane is done reading the stage refilled next
-            issue((u + STAGES - 1) % STAGES);
+            issue((u + STAGES - 1) % STAGES, checked);
             cp_async_wait<STAGES - 1>();
             __syncwarp();                                   // the other lanes' copies for this stage are visible
 #pragma unroll
             for (int j = 0; j < C; j++) {
-                float out[MT];
+                if (!decltype(checked)::value || g + u * C + j < cr.n_g) block_sum(u * C + j, part);
+                else {
 #pragma unroll
-                for (int r = 0; r < MT; r++) out[r] = 0.f;
-                if (g + u * C + j < my_n) block_sum(u * C + j, out);
-#pragma unroll
-                for (int r = 0; r < MT; r++) part[r][u * C + j] = out[r];
+                    for (int r = 0; r < MT; r++) part[r][u * C + j] = 0.f;
+                }
             }
         }
         if (round == 0) MGQ_STAMP(p, 2);
-        reduce_store<MT, ROUND, true>(p, slot, s_red + (size_t)(round & 1) * MT * ROUND * T, part, g0 + g, g1,
-                                      p.push ? s_red + (size_t)2 * MT * ROUND * T : nullptr);
-    }
+        reduce_store<MT, ROUND, true, TS>(p, slot, s_red + (round & 1) * MT * ROUND * TS, part, cr.g0 + g, cr.g1,
+                                          p.push ? s_red + 2 * MT * ROUND * TS : nullptr);
+    };
+
+    uint32_t g = 0, round = 0;
+    for (; g + 2 * ROUND - C <= cr.n_full; g += ROUND, round++) do_round(g, round, std::false_type{});
+    g_next = g + (STAGES - 1) * C;
+    for (; g < cr.n_g; g += ROUND, round++) do_round(g, round, std::true_type{});
     cp_async_wait<0>();
     MGQ_STAMP(p, 3);
 }
@@ -300,11 +335,19 @@ struct Config {
 
 // Tunables (0 = automatic), settable through mgq_set_option.
 struct Tuning {
-    int cols_per_thread = 0;   // "gemv.columns_per_thread": 1, 2 or 4
+    int cols_per_thread = 0;   // "gemv.columns_per_thread": 1 or 2
     int ctas_per_sm = 0;       // "gemv.ctas_per_sm"
     int serial = -1;           // "gemv.serial_dispatch": 1 turns programmatic dependent launch off
+    long ahead_cap = 0;         // "gemv.lookahead_bytes": most bytes of the next GEMV's weights requested into L2 (0 = off)
 };
 Tuning g_tuning;
+
+// Set by mgq_gemv_lookahead, consumed by the next GEMV launched from the same host thread.
+struct Lookahead {
+    const uint8_t *w = nullptr;
+    size_t bytes = 0;
+};
+thread_local Lookahead t_lookahead;
 
 // Largest column count per group that fits `threads` and keeps cpi*bpc a multiple of 4
 // (so that a Q8 warp's 36-byte blocks always start on a 16-byte boundary).
@@ -315,12 +358,20 @@ uint32_t columns_for(uint32_t threads, uint32_t bpc)
     return cpi - cpi % need;
 }
 
+// Shared-memory stride class of a thread count: the kernels are instantiated for these bounds.
+uint32_t stride_class(uint32_t threads)
+{
+    for (uint32_t ts : {128u, 256u, 384u, 512u}) if (threads <= ts) return ts;
+    return 1024u;
+}
+
 size_t smem_bytes(int fmt, uint32_t threads, int c, int mt)
 {
+    const size_t ts = stride_class(threads);
     const size_t round = (size_t)kStages * c;
-    const size_t red = 2 * mt * round * threads * sizeof(float) + threads * sizeof(float);   // + one round of finished columns (exchange)
-    if (fmt == MGQ_FMT_Q4) return round * threads * 20 + red;
-    return (size_t)(threads / 32) * round * kQ8WarpStage + red;
+    const size_t red = 2 * mt * round * ts * sizeof(float) + ts * sizeof(float);   // + one round of finished columns (exchange)
+    if (fmt == MGQ_FMT_Q4) return round * ts * 20 + red;
+    return (ts / 32) * round * kQ8WarpStage + red;
 }
 
 // Thread count and summation order depend on K only, so that a column's result is the same for
@@ -372,14 +423,14 @@ using KernelFn = void (*)(const GemvParams);
 template <int MT, int C>
 KernelFn pick_by_threads(int fmt, uint32_t threads)
 {
-    if (fmt == MGQ_FMT_Q4) {
-        if (threads <= 256) return gemv_q4_kernel<MT, C, 256>;
-        if (threads <= 512) return gemv_q4_kernel<MT, C, 512>;
-        return nullptr;
+    const bool q4 = fmt == MGQ_FMT_Q4;
+    switch (stride_class(threads)) {
+        case 128: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 128> : (KernelFn)gemv_q8_kernel<MT, C, 128>;
+        case 256: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 256> : (KernelFn)gemv_q8_kernel<MT, C, 256>;
+        case 384: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 384> : (KernelFn)gemv_q8_kernel<MT, C, 384>;
+        case 512: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 512> : (KernelFn)gemv_q8_kernel<MT, C, 512>;
+        default: return nullptr;
     }
-    if (threads <= 256) return gemv_q8_kernel<MT, C, 256>;
-    if (threads <= 512) return gemv_q8_kernel<MT, C, 512>;
-    return nullptr;
 }
 
 KernelFn pick_kernel(int fmt, int mt, const Config &c)
@@ -388,15 +439,14 @@ KernelFn pick_kernel(int fmt, int mt, const Config &c)
         if (mt != 1 || c.cols_per_thread != 1) return nullptr;
         return fmt == MGQ_FMT_Q4 ? (KernelFn)gemv_q4_kernel<1, 1, 1024> : (KernelFn)gemv_q8_kernel<1, 1, 1024>;
     }
-    switch (c.cols_per_thread) {
-        case 4: return mt == 2 ? pick_by_threads<2, 4>(fmt, c.threads) : pick_by_threads<1, 4>(fmt, c.threads);
-        case 2: return mt == 2 ? pick_by_threads<2, 2>(fmt, c.threads) : pick_by_threads<1, 2>(fmt, c.threads);
-        default: return mt == 2 ? pick_by_threads<2, 1>(fmt, c.threads) : pick_by_threads<1, 1>(fmt, c.threads);
-    }
+    if (c.cols_per_thread == 2) return mt == 2 ? pick_by_threads<2, 2>(fmt, c.threads) : pick_by_threads<1, 2>(fmt, c.threads);
+    return mt == 2 ? pick_by_threads<2, 1>(fmt, c.threads) : pick_by_threads<1, 1>(fmt, c.threads);
 }
 
 struct DeviceInfo {
     int sms = 0;
+    size_t smem_per_sm = 0, smem_reserved = 0;     // shared memory of an SM, and what every resident CTA costs on top of its request
+    size_t smem_optin = 0;                         // largest dynamic request one CTA may make
     bool ok = false;
 };
 
@@ -410,6 +460,14 @@ int device_info(DeviceInfo &out)
     if (dev < 0 || dev >= 64) return fail(MGQ_ERR_CUDA, "device index %d out of range", dev);
     if (!cache[dev].ok) {
         MGQ_CUDA(cudaDeviceGetAttribute(&cache[dev].sms, cudaDevAttrMultiProcessorCount, dev));
+        int per_sm = 0, reserved = 0;
+        MGQ_CUDA(cudaDeviceGetAttribute(&per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev));
+        MGQ_CUDA(cudaDeviceGetAttribute(&reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev));
+        cache[dev].smem_per_sm = (size_t)per_sm;
+        cache[dev].smem_reserved = (size_t)reserved;
+        int optin = 0;
+        MGQ_CUDA(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        cache[dev].smem_optin = (size_t)optin;
         cache[dev].ok = true;
     }
     out = cache[dev];
@@ -467,16 +525,27 @@ unsigned long long *g_trace = nullptr;
 extern "C" void mgq_debug_set_trace(unsigned long long *dev_buffer) { g_trace = dev_buffer; }
 #endif
 
+int set_gemv_lookahead(const void *w, size_t bytes)
+{
+    if (w && reinterpret_cast<uintptr_t>(w) % 16 != 0) return fail(MGQ_ERR_ALIGN, "look-ahead weights must be 16-byte aligned");
+    t_lookahead.w = static_cast<const uint8_t *>(w);
+    t_lookahead.bytes = w ? bytes : 0;
+    return MGQ_OK;
+}
+
 int set_gemv_option(const char *name, long value)
 {
     if (!std::strcmp(name, "gemv.columns_per_thread")) {
-        if (value != 0 && value != 1 && value != 2 && value != 4) return fail(MGQ_ERR_SHAPE, "%s must be 0, 1, 2 or 4", name);
+        if (value != 0 && value != 1 && value != 2) return fail(MGQ_ERR_SHAPE, "%s must be 0, 1 or 2", name);
         g_tuning.cols_per_thread = (int)value;
     } else if (!std::strcmp(name, "gemv.ctas_per_sm")) {
         if (value < 0 || value > 32) return fail(MGQ_ERR_SHAPE, "%s out of range", name);
         g_tuning.ctas_per_sm = (int)value;
     } else if (!std::strcmp(name, "gemv.serial_dispatch")) {
         g_tuning.serial = value < 0 ? -1 : (value ? 1 : 0);
+    } else if (!std::strcmp(name, "gemv.lookahead_bytes")) {
+        if (value < 0 || value > (1l << 30)) return fail(MGQ_ERR_SHAPE, "%s out of range", name);
+        g_tuning.ahead_cap = value;
     } else {
         return fail(MGQ_ERR_NAME, "unknown option: %s", name);
     }
@@ -539,6 +608,8 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
         p.xerror = xchg->error;
     }
 
+    const Lookahead ahead = t_lookahead;
+    t_lookahead = Lookahead{};
     const bool streamable = bpc >= 8 && bpc <= 1024 && (p.num_blocks % 4 == 0) &&
                             (reinterpret_cast<uintptr_t>(x) % 16 == 0);
     if (!streamable) {
@@ -577,9 +648,28 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
         if (per_sm > occ) per_sm = occ;
         uint32_t grid = (uint32_t)di.sms * (uint32_t)per_sm;
         if (grid > stages_total) grid = stages_total;
+        // With programmatic dependent launch the CTAs of the next kernel take whatever room is left on
+        // an SM while this one still runs; the hardware packs them onto the first SMs that have room,
+        // which leaves the other SMs short of work, and co-resident CTAs that only wait were measured
+        // to cost more than their early prefetch gains (12 Qwen3-8B-shaped layers: 547 us with room
+        // for exactly per_sm CTAs, 643 us with room for 2*per_sm).  So the shared-memory request is
+        // padded until exactly per_sm CTAs fit: a successor's CTA starts when one of ours exits.
+        size_t launch_smem = smem;
+        if (overlap_allowed() && occ > per_sm) {
+            const size_t share = di.smem_per_sm / (size_t)per_sm;
+            if (share > di.smem_reserved + smem) launch_smem = (share - di.smem_reserved) & ~(size_t)127;
+            if (launch_smem > di.smem_optin) launch_smem = di.smem_optin;
+        }
         p.x = x + (size_t)r0 * k;
         p.addend = addend ? addend + (size_t)r0 * n : nullptr;
         p.y = y + (size_t)r0 * n;
+        p.ahead = nullptr;
+        p.ahead_per_cta = 0;
+        if (ahead.w && r0 + mt >= m && g_tuning.ahead_cap > 0) {          // the last launch of this call looks ahead
+            const size_t want = ahead.bytes < (size_t)g_tuning.ahead_cap ? ahead.bytes : (size_t)g_tuning.ahead_cap;
+            p.ahead = ahead.w;
+            p.ahead_per_cta = (uint32_t)(want / grid / 512u * 512u);
+        }
 #ifdef MGQ_GEMV_TRACE
         p.trace = g_trace;
         if (g_trace) g_trace += (size_t)4096 * 4;
@@ -587,7 +677,7 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
         cudaLaunchConfig_t lc{};
         lc.gridDim = dim3(grid, 1, 1);
         lc.blockDim = dim3(cfg.threads, 1, 1);
-        lc.dynamicSmemBytes = smem;
+        lc.dynamicSmemBytes = launch_smem;
         lc.stream = stream;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

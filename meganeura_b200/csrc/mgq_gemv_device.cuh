@@ -29,6 +29,9 @@ struct GemvParams {
     const float2 *wait_vec;                   // local gathered {value, stamp} vector (length k) that must carry this token's stamps
     const unsigned long long *epoch;          // local token index
     unsigned int *xerror;                     // raised when the bounded wait runs out
+    // look-ahead: packed weights of the GEMV that follows this one in the stream (may be null)
+    const uint8_t *ahead;
+    uint32_t ahead_per_cta;                   // bytes each CTA asks L2 to fetch, a multiple of 512
 #ifdef MGQ_GEMV_TRACE
     unsigned long long *trace;   // [gridDim.x][4] globaltimer stamps: start, after dependency wait, first block done, end
 #endif
@@ -125,6 +128,19 @@ __device__ __forceinline__ void cp_async_wait()
 // weights (immutable after upload) are fetched there.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+// A decode step is a chain of dependent GEMVs, and between two of them (dependency release,
+// activation load, reduction) HBM would sit idle.  So each CTA, right after queueing its own first
+// weight stages, asks L2 to start fetching a slice of the NEXT GEMV's packed weights: the request
+// holds no shared memory or registers, HBM keeps streaming through the gaps, and the next kernel
+// finds its weights in L2.  Weights are immutable, so this is legal before the dependency wait.
+__device__ __forceinline__ void prefetch_ahead(const GemvParams &p)
+{
+    if (p.ahead_per_cta == 0 || threadIdx.x >= 32) return;
+    const uint32_t chunk = p.ahead_per_cta >> 5;                                           // per lane, a multiple of 16
+    const uint8_t *src = p.ahead + (size_t)blockIdx.x * p.ahead_per_cta + (size_t)threadIdx.x * chunk;
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(src), "r"(chunk) : "memory");
+}
 
 // dp4a with mixed signedness (a: packed codes, b: packed activation bytes).
 __device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c)
@@ -274,10 +290,11 @@ struct ReduceSlot {
     bool vec;            // run is float4-readable
 };
 
-template <int ROUND>
+// STRIDE: floats between consecutive rows of the staging array (0: one row per thread of the CTA).
+template <int ROUND, int STRIDE = 0>
 __device__ __forceinline__ ReduceSlot make_slot(const GemvParams &p)
 {
-    const uint32_t T = blockDim.x, t = threadIdx.x;
+    const uint32_t T = STRIDE ? (uint32_t)STRIDE : blockDim.x, t = threadIdx.x;
     const uint32_t R = 1u << p.red_shift;
     const uint32_t slot = t >> p.red_shift, li = t & (R - 1);
     ReduceSlot s{};
@@ -293,12 +310,12 @@ __device__ __forceinline__ ReduceSlot make_slot(const GemvParams &p)
     return s;
 }
 
-template <int MT, int ROUND, bool COHERENT = false>
+template <int MT, int ROUND, bool COHERENT = false, int STRIDE = 0>
 __device__ __forceinline__ void reduce_store(const GemvParams &p, const ReduceSlot &slot, float *red,
                                              const float (&part)[MT][ROUND], uint32_t it_base, uint32_t it_end,
                                              float *push_stage = nullptr)
 {
-    const uint32_t T = blockDim.x, t = threadIdx.x;
+    const uint32_t T = STRIDE ? (uint32_t)STRIDE : blockDim.x, t = threadIdx.x;
 #pragma unroll
     for (int r = 0; r < MT; r++)
 #pragma unroll
@@ -316,7 +333,11 @@ __device__ __forceinline__ void reduce_store(const GemvParams &p, const ReduceSl
         } else {
             for (uint32_t j = 0; j < slot.cnt; j++) s += src[j];
         }
-        for (uint32_t o = (1u << p.red_shift) >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (p.red_shift > 4) s += __shfl_xor_sync(0xffffffffu, s, 16);
+        if (p.red_shift > 3) s += __shfl_xor_sync(0xffffffffu, s, 8);
+        if (p.red_shift > 2) s += __shfl_xor_sync(0xffffffffu, s, 4);
+        if (p.red_shift > 1) s += __shfl_xor_sync(0xffffffffu, s, 2);
+        if (p.red_shift > 0) s += __shfl_xor_sync(0xffffffffu, s, 1);
         const uint32_t it = it_base + slot.iter;
         const uint32_t col = it * p.cpi + slot.cs;
         if (slot.writer && it < it_end && col < p.n) {
@@ -338,7 +359,7 @@ __device__ __forceinline__ void reduce_store(const GemvParams &p, const ReduceSl
         if (first < px.gather_cols) {
             ncols = min(ncols, px.gather_cols - first);
             const uint32_t stamp = exchange_stamp(p.epoch);
-            for (uint32_t idx = t; idx < ncols * px.world; idx += T) {
+            for (uint32_t idx = t; idx < ncols * px.world; idx += blockDim.x) {
                 const uint32_t q = idx / ncols, c = idx - q * ncols;
                 px.dst[q][(size_t)px.rank * px.gather_cols + first + c] = make_float2(push_stage[c], __uint_as_float(stamp));
             }

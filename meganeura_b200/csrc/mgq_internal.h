@@ -30,6 +30,7 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
 int launch_exchange_finish(const void *last_vec, uint32_t length, unsigned long long *epoch,
                            unsigned int *error, unsigned int *blocks_done, void *stream);
 int set_gemv_option(const char *name, long value);
+int set_gemv_lookahead(const void *w, size_t bytes);
 int set_plan_option(const char *name, long value);
 int set_gemm_option(const char *name, long value);
 bool force_tiled();
@@ -41,6 +42,21 @@ bool gemm_tc_eligible(int a_dtype, uint32_t m, uint32_t k, uint32_t n, const voi
 int launch_gemm_tc(int fmt, const void *a, const void *w, const float *addend, float *c,
                    uint32_t m, uint32_t k, uint32_t n, void *stream);
 int tc_device_status();
+
+// Decode-step operators (mgq_decode_ops.cu).
+int launch_embedding(const uint32_t *ids, const float *table, float *out, uint32_t seq, uint32_t hidden, uint32_t vocab, void *stream);
+int launch_rms_norm(const float *x, const float *weight, float *out, uint32_t rows, uint32_t cols, float eps, void *stream);
+int launch_rope(const float *x, float *out, const uint32_t *pos_offset, uint32_t seq, uint32_t dim, uint32_t head_dim, float theta,
+                void *stream);
+int launch_cache_write(const float *src, float *cache, const uint32_t *kv_pos, uint32_t dim, uint32_t max_seq, void *stream);
+int launch_swiglu(const float *gate, const float *up, float *out, uint32_t rows, uint32_t half_n, uint32_t pitch, void *stream);
+size_t attention_workspace_bytes(uint32_t num_kv_heads, uint32_t head_dim, uint32_t max_seq);
+int launch_cached_attention(const float *q, const float *k_cache, const float *v_cache, const uint32_t *kv_pos, float *out,
+                            uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_dim, uint32_t max_seq, void *workspace,
+                            void *stream);
+size_t argmax_workspace_bytes();
+int launch_argmax(const float *logits, uint32_t n, void *workspace, uint32_t *out_token, uint32_t *next_token, uint32_t *kv_pos,
+                  uint32_t *history, uint32_t history_cap, void *stream);
 
 }  // namespace mgq
 

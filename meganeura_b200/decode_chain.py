@@ -112,6 +112,7 @@ class DecodeGemvChain:
         if self.exchange == "peer-self":       # one rank pushing to itself: exercises the exchange code path on one GPU
             self.exchange = "peer"
         self.peer = None
+        self.lookahead = True      # every GEMV asks L2 for its successor's weights (mgq_gemv_lookahead)
         # use_plan=True runs the token as one persistent kernel (mgq_plan_*); the default is one
         # kernel per GEMV chained by programmatic dependent launch, which is currently faster
         self.use_plan = bool(use_plan) and world == 1 and batch == 1
@@ -196,8 +197,10 @@ class DecodeGemvChain:
         if self.exchange == "peer":
             return self._launch_all_peer()
         count = 0
-        for op in self.ops_list:
+        for i, op in enumerate(self.ops_list):
             sp = op["spec"]
+            if self.lookahead and i + 1 < len(self.ops_list):
+                ops.lookahead(self.ops_list[i + 1]["w"])
             ops.matmul(self.fmt, self.x[sp.src], op["w"], sp.k, op["n_loc"], addend=op["addend"], out=op["y"], route="gemv")
             count += (self.m + 1) // 2 if self.m > 1 else 1
             if op["full"] is not None:
@@ -215,6 +218,8 @@ class DecodeGemvChain:
         last_exchange = None
         for i, op in enumerate(self.ops_list):
             sp = op["spec"]
+            if self.lookahead and i + 1 < len(self.ops_list):
+                ops.lookahead(self.ops_list[i + 1]["w"])
             self.peer.gemv(self.fmt, self.x[sp.src], op["w"], op["addend"], op["y"], sp.k, op["n_loc"], i, last_exchange, stream)
             if op["gather_cols"]:
                 last_exchange = i

@@ -15,6 +15,13 @@ def set_option(name: str, value: int) -> None:
     check(lib.mgq_set_option(name.encode(), int(value)))
 
 
+def lookahead(next_w) -> None:
+    """mgq_gemv_lookahead: the GEMV launched next also asks L2 to start fetching `next_w` (a device
+    uint8 tensor holding the packed weights of the GEMV after it)."""
+    check(lib.mgq_gemv_lookahead(next_w.data_ptr() if next_w is not None else None,
+                                 next_w.numel() * next_w.element_size() if next_w is not None else 0))
+
+
 def device_status() -> None:
     """Raises MgqError(MGQ_ERR_TIMEOUT) if a bounded device-side wait ran out (mgq_device_status)."""
     check(lib.mgq_device_status())

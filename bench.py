@@ -189,6 +189,45 @@ def run_reference(args, shape, fmt):
 
 # ------------------------------------------------------------------------------- GPU arm
 
+def decode_tokens_per_s(model: str, steps: int = 128, context: int = 2048):
+    """Whole-model greedy decode through Graph / build_inference_session / Session: every operator
+    of the step (embedding, norms, RoPE, cache writes, attention, SwiGLU, the quantized GEMVs and
+    the greedy pick) runs on the GPU from one captured CUDA graph per token; the host only launches.
+    KV caches are pre-filled to `context` positions; weights are the synthetic packed weights."""
+    from meganeura_b200 import decode_model as M
+    cfg = M.QWEN3_8B if model == "qwen3-8b" else M.SMOLLM2_135M
+    if cfg is M.SMOLLM2_135M:
+        context = 128
+    max_seq = context + steps + 8
+    t0 = time.perf_counter()
+    dec = M.DecodeSession(cfg, max_seq, seed=3, greedy_history=max_seq)
+    dec.fill_caches(context)
+    build_s = time.perf_counter() - t0
+    s = dec.session
+    dec.set_position(1, context)
+    s.step()                                     # warm-up outside the graph
+    s.wait()
+    s.capture()
+    dec.set_position(1, context)
+    for _ in range(3):
+        s.step()
+    s.wait()
+    dec.set_position(1, context)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        s.step()
+    s.wait()
+    tokens = s.read_tokens(context, steps)
+    dt = time.perf_counter() - t0
+    plan = s.plan().dispatches
+    kv_bytes = 2 * cfg.num_hidden_layers * cfg.kv_dim * 4 * (context + steps // 2)
+    return {"model": f"{cfg.name}-shaped, random packed weights", "tokens_per_s": round(steps / dt, 1),
+            "ms_per_token": round(dt / steps * 1e3, 4), "steps": steps, "kv_context": context, "batch": 1,
+            "launches_per_token": len(plan) + 1, "greedy_pick": "device", "timing": "host wall clock around launch + final token read",
+            "weight_plus_kv_gbs": round((M.packed_weight_bytes(cfg) + kv_bytes) / (dt / steps) / 1e9, 1),
+            "distinct_tokens": int(len(set(int(t) for t in tokens))), "build_s": round(build_s, 1)}
+
+
 def workload_config(shape, fmt, batch, gpus, exchange="peer"):
     return {
         "workload": f"{shape.name}-shaped decode token, all {'Q4' if fmt == 2 else 'Q8'} GEMVs "
@@ -213,6 +252,7 @@ def main():
     ap.add_argument("--model", choices=["qwen3-8b", "smollm2-135m"], default="qwen3-8b")
     ap.add_argument("--impl", choices=["mgq", "reference"], default="mgq")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode tokens/s measurement")
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                     help="multi-GPU exchange: slices pushed over NVLink by the GEMV kernels (default) or NCCL all-gather")
     ap.add_argument("--plan-kernel", action="store_true", help="run the token as one persistent plan kernel instead of one kernel per GEMV")
@@ -308,6 +348,9 @@ def main():
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(shape, fmt)
+        if world == 1 and not args.no_decode and args.batch == 1 and not args.plan_kernel:
+            chain.graph = None
+            line["decode"] = decode_tokens_per_s(args.model)
         print(json.dumps(line))
     if world > 1:
         # A captured graph that holds NCCL nodes must go before the communicator does (destroying the

@@ -62,7 +62,13 @@ const char *mgq_version(void);
  *   "gemv.lookahead_bytes"      most bytes of the following GEMV's weights that a GEMV asks L2 to
  *                               fetch (mgq_gemv_lookahead); 0 = look-ahead off (the default)
  *   "plan.columns_per_thread"   1, 2 or 4 for plans created afterwards (default 2: two CTAs per SM)
- *   "gemm.force_tiled"          1: never use the tcgen05 kernel (CUDA-core tiled kernel only) */
+ *   "gemm.force_tiled"          1: never use the tcgen05 kernel (CUDA-core tiled kernel only)
+ *   "session.horizontal_fusion" sessions built afterwards merge single-row matmuls that read the same
+ *                               activation into one GEMV over the concatenated weight: 0 never,
+ *                               1 gate|up under a SwiGLU only (the reference's rule,
+ *                               src/optimize.rs:776-879), 2 every such group, e.g. q|k|v (default)
+ *   "session.fuse_rope_cache"   1 (default): RoPE(q), RoPE(k), CacheWrite(k), CacheWrite(v) of a decode
+ *                               layer run as one launch; 0: four dispatches like the reference */
 int mgq_set_option(const char *name, long value);
 
 /* ---- format: TensorType::size_bytes for quantized dtypes (src/graph.rs:52-68) ---------- */
@@ -186,6 +192,12 @@ int mgq_embedding(const uint32_t *ids, const float *table, float *out, uint32_t 
 int mgq_rms_norm(const float *x, const float *weight, float *out, uint32_t rows, uint32_t cols, float eps, void *stream);
 int mgq_rope_dynamic(const float *x, float *out, const uint32_t *pos_offset, uint32_t seq, uint32_t dim, uint32_t head_dim,
                      float theta, void *stream);
+/* The four dispatches after a decode layer's q|k|v projection in one launch (no reference
+ * counterpart as a single shader): q_dst = rope(q_src), k_dst = rope(k_src),
+ * k_cache[*kv_pos] = k_dst, v_cache[*kv_pos] = v_src; q is [1, q_dim], k and v are [1, kv_dim]. */
+int mgq_rope_cache_write(const float *q_src, float *q_dst, const float *k_src, float *k_dst, const float *v_src, float *k_cache,
+                         float *v_cache, const uint32_t *kv_pos, uint32_t q_dim, uint32_t kv_dim, uint32_t head_dim, float theta,
+                         uint32_t max_seq, void *stream);
 int mgq_cache_write(const float *src, float *cache, const uint32_t *kv_pos, uint32_t dim, uint32_t max_seq, void *stream);
 int mgq_swiglu(const float *gate, const float *up, float *out, uint32_t rows, uint32_t half_n, uint32_t pitch, void *stream);
 size_t mgq_cached_attention_workspace(uint32_t num_kv_heads, uint32_t head_dim, uint32_t max_seq);
@@ -271,6 +283,14 @@ typedef struct mgq_session mgq_session;
 #define MGQ_SHADER_MATMUL_GEMV       2
 #define MGQ_SHADER_MATMUL_GEMV_ADD   3
 #define MGQ_SHADER_ADD               4
+#define MGQ_SHADER_EMBEDDING         5
+#define MGQ_SHADER_RMS_NORM          6
+#define MGQ_SHADER_ROPE_DYNAMIC      7
+#define MGQ_SHADER_CACHE_WRITE       8
+#define MGQ_SHADER_CACHED_ATTENTION  9
+#define MGQ_SHADER_SWIGLU            10
+#define MGQ_SHADER_SWIGLU_CONCAT     11
+#define MGQ_SHADER_ROPE_CACHE_WRITE  12   /* RoPEDynamic x2 + CacheWrite x2 merged (no reference entry) */
 
 mgq_graph *mgq_graph_new(void);
 void mgq_graph_free(mgq_graph *g);
@@ -281,6 +301,18 @@ int mgq_graph_parameter_q4(mgq_graph *g, const char *name, const size_t *shape, 
 int mgq_graph_parameter_q8(mgq_graph *g, const char *name, const size_t *shape, size_t rank);
 int mgq_graph_matmul(mgq_graph *g, int a, int b);
 int mgq_graph_add(mgq_graph *g, int a, int b);
+/* decode-step nodes: Graph::{input_u32, embedding, rms_norm, rope_dynamic_offset, cache_write,
+ * cached_attention, swiglu, swiglu_concat} (src/graph.rs:1003-1009, 1029-1040, 1062-1087, 1148-1170,
+ * 1659-1700), same argument checks; a cache is an f32 parameter [max_seq, kv_dim] written in place. */
+int mgq_graph_input_u32(mgq_graph *g, const char *name, const size_t *shape, size_t rank);
+int mgq_graph_embedding(mgq_graph *g, int indices, int table);
+int mgq_graph_rms_norm(mgq_graph *g, int x, int weight, float eps);
+int mgq_graph_rope_dynamic_offset(mgq_graph *g, int x, float theta, int offset_input, uint32_t head_dim);
+int mgq_graph_cache_write(mgq_graph *g, int new_kv, int cache, int kv_pos);
+int mgq_graph_cached_attention(mgq_graph *g, int q, int k_cache, int v_cache, int kv_pos, uint32_t num_heads,
+                               uint32_t num_kv_heads, uint32_t head_dim);
+int mgq_graph_swiglu(mgq_graph *g, int gate, int up);
+int mgq_graph_swiglu_concat(mgq_graph *g, int input);
 int mgq_graph_set_outputs(mgq_graph *g, const int *ids, size_t count);
 
 /* build_inference_session (src/train.rs:380-389): fuse, lower, allocate zero-filled buffers. */
@@ -291,7 +323,28 @@ int mgq_session_set_parameter(mgq_session *s, const char *name, const float *dat
 /* upload_param: raw bytes into the parameter buffer, no conversion (src/runtime.rs:2786-2791). */
 int mgq_session_upload_param(mgq_session *s, const char *name, const void *bytes, size_t nbytes);
 int mgq_session_set_input(mgq_session *s, const char *name, const float *data, size_t len);
+/* Session::save_checkpoint / load_checkpoint (src/runtime.rs:4205-4336), same file layout: a
+ * safetensors file with every parameter buffer -- packed Q4/Q8 bytes as they are -- stored as a flat
+ * F32 tensor of byte_len/4 elements under the parameter's name, metadata adam_step.  A file written
+ * by either side loads on the other when parameter names and shapes agree; loading skips
+ * re-quantization.  Parameters missing from the file keep their contents. */
+int mgq_session_save_checkpoint(mgq_session *s, const char *path);
+int mgq_session_load_checkpoint(mgq_session *s, const char *path);
+int mgq_session_set_input_u32(mgq_session *s, const char *name, const uint32_t *data, size_t len);
 int mgq_session_step(mgq_session *s);
+/* No reference counterpart (the reference re-records its command buffer every step,
+ * src/runtime.rs:2843-2881): captures the dispatch list once into a CUDA graph; later steps replay
+ * it.  Needs one ordinary step first.  Inputs and parameters may still be rewritten between steps
+ * (their buffers do not move). */
+int mgq_session_capture(mgq_session *s);
+/* No reference counterpart (the reference picks the next token on the host,
+ * bench/bench_meganeura.rs:255-273): after the dispatches of every step, pick argmax of output
+ * `output_index` on the device, store it at history[position], write it into the u32 input
+ * `token_input` and add one to the u32 input `pos_input`.  Call before mgq_session_capture.
+ * mgq_session_read_tokens copies history[first_pos, first_pos + count) to the host. */
+int mgq_session_enable_greedy(mgq_session *s, size_t output_index, const char *token_input, const char *pos_input,
+                              uint32_t history_cap);
+int mgq_session_read_tokens(mgq_session *s, uint32_t first_pos, uint32_t *out, size_t count);
 int mgq_session_wait(mgq_session *s);
 int mgq_session_read_output(mgq_session *s, float *out, size_t len);
 int mgq_session_read_output_by_index(mgq_session *s, size_t index, float *out, size_t len);

@@ -61,6 +61,16 @@ SIGNATURES = {
     "mgq_device_status": (_int, []),
     "mgq_gemv": (_int, [_int, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_gemv_lookahead": (_int, [_vp, _sz]),
+    "mgq_embedding": (_int, [_vp, _vp, _vp, _u32, _u32, _u32, _vp]),
+    "mgq_rms_norm": (_int, [_vp, _vp, _vp, _u32, _u32, ctypes.c_float, _vp]),
+    "mgq_rope_dynamic": (_int, [_vp, _vp, _vp, _u32, _u32, _u32, ctypes.c_float, _vp]),
+    "mgq_rope_cache_write": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, ctypes.c_float, _u32, _vp]),
+    "mgq_cache_write": (_int, [_vp, _vp, _vp, _u32, _u32, _vp]),
+    "mgq_swiglu": (_int, [_vp, _vp, _vp, _u32, _u32, _u32, _vp]),
+    "mgq_cached_attention_workspace": (_sz, [_u32, _u32, _u32]),
+    "mgq_cached_attention": (_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _vp]),
+    "mgq_argmax_workspace": (_sz, []),
+    "mgq_argmax": (_int, [_vp, _u32, _vp, _vp, _vp, _vp, _vp, _u32, _vp]),
     "mgq_gemv_exchange": (_int, [_int, _vp, _vp, _vp, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
     "mgq_exchange_finish": (_int, [_vp, _u32, _vp, _vp, _vp, _vp]),
     "mgq_gemm": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
@@ -80,13 +90,27 @@ SIGNATURES = {
     "mgq_graph_parameter_q8": (_int, [_vp, ctypes.c_char_p, _szp, _sz]),
     "mgq_graph_matmul": (_int, [_vp, _int, _int]),
     "mgq_graph_add": (_int, [_vp, _int, _int]),
+    "mgq_graph_input_u32": (_int, [_vp, ctypes.c_char_p, _szp, _sz]),
+    "mgq_graph_embedding": (_int, [_vp, _int, _int]),
+    "mgq_graph_rms_norm": (_int, [_vp, _int, _int, ctypes.c_float]),
+    "mgq_graph_rope_dynamic_offset": (_int, [_vp, _int, ctypes.c_float, _int, _u32]),
+    "mgq_graph_cache_write": (_int, [_vp, _int, _int, _int]),
+    "mgq_graph_cached_attention": (_int, [_vp, _int, _int, _int, _int, _u32, _u32, _u32]),
+    "mgq_graph_swiglu": (_int, [_vp, _int, _int]),
+    "mgq_graph_swiglu_concat": (_int, [_vp, _int]),
     "mgq_graph_set_outputs": (_int, [_vp, ctypes.POINTER(_int), _sz]),
     "mgq_build_inference_session": (_int, [_vp, ctypes.POINTER(_vp)]),
     "mgq_session_free": (None, [_vp]),
     "mgq_session_set_parameter": (_int, [_vp, ctypes.c_char_p, _vp, _sz]),
     "mgq_session_upload_param": (_int, [_vp, ctypes.c_char_p, _vp, _sz]),
     "mgq_session_set_input": (_int, [_vp, ctypes.c_char_p, _vp, _sz]),
+    "mgq_session_save_checkpoint": (_int, [_vp, ctypes.c_char_p]),
+    "mgq_session_load_checkpoint": (_int, [_vp, ctypes.c_char_p]),
+    "mgq_session_set_input_u32": (_int, [_vp, ctypes.c_char_p, _vp, _sz]),
     "mgq_session_step": (_int, [_vp]),
+    "mgq_session_capture": (_int, [_vp]),
+    "mgq_session_enable_greedy": (_int, [_vp, _sz, ctypes.c_char_p, ctypes.c_char_p, _u32]),
+    "mgq_session_read_tokens": (_int, [_vp, _u32, _vp, _sz]),
     "mgq_session_wait": (_int, [_vp]),
     "mgq_session_read_output": (_int, [_vp, _vp, _sz]),
     "mgq_session_read_output_by_index": (_int, [_vp, _sz, _vp, _sz]),

@@ -73,6 +73,7 @@ int mgq_set_option(const char *name, long value)
     if (!name) return fail(MGQ_ERR_NULL, "null option name");
     if (!std::strncmp(name, "plan.", 5)) return set_plan_option(name, value);
     if (!std::strncmp(name, "gemm.", 5)) return set_gemm_option(name, value);
+    if (!std::strncmp(name, "session.", 8)) return set_session_option(name, value);
     return set_gemv_option(name, value);
 }
 
@@ -107,6 +108,15 @@ int mgq_rope_dynamic(const float *x, float *out, const uint32_t *pos_offset, uin
     if (!x || !out || !pos_offset) return fail(MGQ_ERR_NULL, "rope: null pointer");
     if (seq == 0 || dim == 0 || head_dim == 0) return fail(MGQ_ERR_SHAPE, "rope: empty shape");
     return launch_rope(x, out, pos_offset, seq, dim, head_dim, theta, stream);
+}
+
+int mgq_rope_cache_write(const float *q_src, float *q_dst, const float *k_src, float *k_dst, const float *v_src, float *k_cache,
+                         float *v_cache, const uint32_t *kv_pos, uint32_t q_dim, uint32_t kv_dim, uint32_t head_dim, float theta,
+                         uint32_t max_seq, void *stream)
+{
+    if (!q_src || !q_dst || !k_src || !k_dst || !v_src || !k_cache || !v_cache || !kv_pos) return fail(MGQ_ERR_NULL, "rope_cache_write: null pointer");
+    if (q_dim == 0 || kv_dim == 0 || head_dim == 0 || max_seq == 0) return fail(MGQ_ERR_SHAPE, "rope_cache_write: empty shape");
+    return launch_rope_cache(q_src, q_dst, k_src, k_dst, v_src, k_cache, v_cache, kv_pos, q_dim, kv_dim, head_dim, theta, max_seq, stream);
 }
 
 int mgq_cache_write(const float *src, float *cache, const uint32_t *kv_pos, uint32_t dim, uint32_t max_seq, void *stream)

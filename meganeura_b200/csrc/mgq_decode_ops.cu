@@ -115,6 +115,44 @@ __global__ void rope_kernel(const float *src, float *dst, const uint32_t *pos_of
     dst[idx1] = v0 * s + v1 * c;
 }
 
+// ---------------------------------------------------------------- RoPE(q), RoPE(k) and both cache writes in one launch
+// The four dispatches that follow the q|k|v projection of a decode layer (rope_dynamic.wgsl twice,
+// cache_write.wgsl twice) touch a few KB; one launch instead of four saves three kernel boundaries
+// per layer.  Thread ranges: q pairs, then k pairs (rotated k also goes to its cache row), then v.
+__global__ void rope_cache_kernel(const float *q_src, float *q_dst, const float *k_src, float *k_dst, const float *v_src,
+                                  float *k_cache, float *v_cache, const uint32_t *pos_buf, uint32_t q_dim, uint32_t kv_dim,
+                                  uint32_t head_dim, float theta, uint32_t max_seq)
+{
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t half_head = head_dim / 2, q_pairs = q_dim / 2, k_pairs = kv_dim / 2;
+    pdl_launch_dependents();
+    if (i >= q_pairs + k_pairs + kv_dim) { pdl_wait(); return; }
+    const bool is_v = i >= q_pairs + k_pairs, is_k = !is_v && i >= q_pairs;
+    const uint32_t pair = is_k ? i - q_pairs : i;
+    const uint32_t head = pair / half_head, pair_in_head = pair - head * half_head;
+    const float inv_freq = is_v ? 0.f : powf(theta, -2.0f * (float)pair_in_head / (float)head_dim);
+    pdl_wait();
+    const uint32_t pos = pos_buf[0];
+    if (is_v) {
+        const uint32_t j = i - q_pairs - k_pairs;
+        if (pos < max_seq) v_cache[(size_t)pos * kv_dim + j] = v_src[j];
+        return;
+    }
+    float s, c;
+    sincosf((float)pos * inv_freq, &s, &c);
+    const uint32_t idx0 = head * head_dim + pair_in_head, idx1 = idx0 + half_head;
+    const float *src = is_k ? k_src : q_src;
+    float *dst = is_k ? k_dst : q_dst;
+    const float v0 = src[idx0], v1 = src[idx1];
+    const float r0 = v0 * c - v1 * s, r1 = v0 * s + v1 * c;
+    dst[idx0] = r0;
+    dst[idx1] = r1;
+    if (is_k && pos < max_seq) {
+        k_cache[(size_t)pos * kv_dim + idx0] = r0;
+        k_cache[(size_t)pos * kv_dim + idx1] = r1;
+    }
+}
+
 // ---------------------------------------------------------------- KV-cache write (cache_write.wgsl)
 __global__ void cache_write_kernel(const float *src, float *cache, const uint32_t *kv_pos, uint32_t dim, uint32_t max_seq)
 {
@@ -342,6 +380,16 @@ int launch_rope(const float *x, float *out, const uint32_t *pos_offset, uint32_t
     const uint32_t total = seq * (dim / 2);
     return launch(rope_kernel, dim3((total + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream), x, out, pos_offset, seq, dim,
                   head_dim, theta);
+}
+
+int launch_rope_cache(const float *q_src, float *q_dst, const float *k_src, float *k_dst, const float *v_src, float *k_cache,
+                      float *v_cache, const uint32_t *pos, uint32_t q_dim, uint32_t kv_dim, uint32_t head_dim, float theta,
+                      uint32_t max_seq, void *stream)
+{
+    if (q_dim % head_dim || kv_dim % head_dim || head_dim % 2) return fail(MGQ_ERR_SHAPE, "rope: dims %u / %u, head_dim %u", q_dim, kv_dim, head_dim);
+    const uint32_t total = q_dim / 2 + kv_dim / 2 + kv_dim;
+    return launch(rope_cache_kernel, dim3((total + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream), q_src, q_dst, k_src, k_dst,
+                  v_src, k_cache, v_cache, pos, q_dim, kv_dim, head_dim, theta, max_seq);
 }
 
 int launch_cache_write(const float *src, float *cache, const uint32_t *kv_pos, uint32_t dim, uint32_t max_seq, void *stream)

@@ -33,6 +33,7 @@ int set_gemv_option(const char *name, long value);
 int set_gemv_lookahead(const void *w, size_t bytes);
 int set_plan_option(const char *name, long value);
 int set_gemm_option(const char *name, long value);
+int set_session_option(const char *name, long value);
 bool force_tiled();
 int launch_gemm(int fmt, const void *a, int a_dtype, const void *w, const float *addend, float *c,
                 uint32_t m, uint32_t k, uint32_t n, void *stream);
@@ -48,6 +49,9 @@ int launch_embedding(const uint32_t *ids, const float *table, float *out, uint32
 int launch_rms_norm(const float *x, const float *weight, float *out, uint32_t rows, uint32_t cols, float eps, void *stream);
 int launch_rope(const float *x, float *out, const uint32_t *pos_offset, uint32_t seq, uint32_t dim, uint32_t head_dim, float theta,
                 void *stream);
+int launch_rope_cache(const float *q_src, float *q_dst, const float *k_src, float *k_dst, const float *v_src, float *k_cache,
+                      float *v_cache, const uint32_t *pos, uint32_t q_dim, uint32_t kv_dim, uint32_t head_dim, float theta,
+                      uint32_t max_seq, void *stream);
 int launch_cache_write(const float *src, float *cache, const uint32_t *kv_pos, uint32_t dim, uint32_t max_seq, void *stream);
 int launch_swiglu(const float *gate, const float *up, float *out, uint32_t rows, uint32_t half_n, uint32_t pitch, void *stream);
 size_t attention_workspace_bytes(uint32_t num_kv_heads, uint32_t head_dim, uint32_t max_seq);

@@ -1,0 +1,173 @@
+"""Single-token decode graphs of the two model shapes the benchmarks name, built through the
+Graph mirror exactly like meganeura builds them (src/models/smollm2.rs:315-421 build_decode_graph;
+examples/qwen3.rs:243-310 uses the same layer without q/k-norm), with the projections declared as
+quantized parameters.
+
+    token_ids, kv_pos (u32 inputs) -> embedding -> N x [rms_norm, q/k/v matmul, rope(q), rope(k),
+    cache_write(k), cache_write(v), cached_attention, o matmul + residual, rms_norm, gate/up matmul,
+    swiglu, down matmul + residual] -> rms_norm -> lm_head matmul
+
+The session fuses o/down with their residual adds, q|k|v and gate|up into single GEMVs.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, replace
+
+import numpy as np
+
+from . import synth
+from ._lib import FMT_Q4, FMT_Q8
+from .graph import Graph, Session, build_inference_session
+
+
+@dataclass(frozen=True)
+class DecoderConfig:
+    name: str
+    vocab_size: int
+    hidden_size: int
+    num_hidden_layers: int
+    num_attention_heads: int
+    num_key_value_heads: int
+    head_dim: int
+    intermediate_size: int
+    rms_norm_eps: float
+    rope_theta: float
+    attn_fmt: int
+    mlp_fmt: int
+    head_fmt: int
+
+    @property
+    def kv_dim(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    @property
+    def q_dim(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+
+# src/models/smollm2.rs:35-47; MLP Q4, attention and an untied lm_head Q8
+SMOLLM2_135M = DecoderConfig("smollm2-135m", 49152, 576, 30, 9, 3, 64, 1536, 1e-5, 1e4, FMT_Q8, FMT_Q4, FMT_Q8)
+# examples/qwen3.rs:91-105 (8B variant); every projection and the lm_head Q4
+QWEN3_8B = DecoderConfig("qwen3-8b", 151936, 4096, 36, 32, 8, 128, 12288, 1e-6, 1e6, FMT_Q4, FMT_Q4, FMT_Q4)
+
+
+def small(cfg: DecoderConfig, layers: int, vocab: int) -> DecoderConfig:
+    """The same layer shape with fewer layers and a smaller vocabulary (for tests)."""
+    return replace(cfg, name=f"{cfg.name}-{layers}l", num_hidden_layers=layers, vocab_size=vocab)
+
+
+def _qparam(g: Graph, fmt: int, name: str, shape):
+    return g.parameter_q4(name, shape) if fmt == FMT_Q4 else g.parameter_q8(name, shape)
+
+
+def build_decode_graph(g: Graph, cfg: DecoderConfig, max_seq_len: int):
+    """Returns (logits, k_cache_params, v_cache_params), like the reference's build_decode_graph."""
+    hidden, kv_dim, ffn = cfg.hidden_size, cfg.kv_dim, cfg.intermediate_size
+    token_ids = g.input_u32("token_ids", [1])
+    kv_pos = g.input_u32("kv_pos", [1])
+    embed = g.parameter("model.embed_tokens.weight", [cfg.vocab_size, hidden])
+    x = g.embedding(token_ids, embed)
+    k_caches, v_caches = [], []
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}"
+        h = g.rms_norm(x, g.parameter(f"{p}.input_layernorm.weight", [hidden]), cfg.rms_norm_eps)
+        wq = _qparam(g, cfg.attn_fmt, f"{p}.self_attn.q_proj.weight", [hidden, cfg.q_dim])
+        wk = _qparam(g, cfg.attn_fmt, f"{p}.self_attn.k_proj.weight", [hidden, kv_dim])
+        wv = _qparam(g, cfg.attn_fmt, f"{p}.self_attn.v_proj.weight", [hidden, kv_dim])
+        q, k, v = g.matmul(h, wq), g.matmul(h, wk), g.matmul(h, wv)
+        q = g.rope_dynamic_offset(q, cfg.rope_theta, kv_pos, cfg.head_dim)
+        k = g.rope_dynamic_offset(k, cfg.rope_theta, kv_pos, cfg.head_dim)
+        k_cache = g.parameter(f"kv_cache.layer.{i}.k", [max_seq_len, kv_dim])
+        v_cache = g.parameter(f"kv_cache.layer.{i}.v", [max_seq_len, kv_dim])
+        k_caches.append(k_cache)
+        v_caches.append(v_cache)
+        g.cache_write(k, k_cache, kv_pos)
+        g.cache_write(v, v_cache, kv_pos)
+        attn = g.cached_attention(q, k_cache, v_cache, kv_pos, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
+        wo = _qparam(g, cfg.attn_fmt, f"{p}.self_attn.o_proj.weight", [cfg.q_dim, hidden])
+        x = g.add(x, g.matmul(attn, wo))
+        h = g.rms_norm(x, g.parameter(f"{p}.post_attention_layernorm.weight", [hidden]), cfg.rms_norm_eps)
+        w_gate = _qparam(g, cfg.mlp_fmt, f"{p}.mlp.gate_proj.weight", [hidden, ffn])
+        w_up = _qparam(g, cfg.mlp_fmt, f"{p}.mlp.up_proj.weight", [hidden, ffn])
+        w_down = _qparam(g, cfg.mlp_fmt, f"{p}.mlp.down_proj.weight", [ffn, hidden])
+        ffn_out = g.swiglu(g.matmul(h, w_gate), g.matmul(h, w_up))
+        x = g.add(x, g.matmul(ffn_out, w_down))
+    x = g.rms_norm(x, g.parameter("model.norm.weight", [hidden]), cfg.rms_norm_eps)
+    logits = g.matmul(x, _qparam(g, cfg.head_fmt, "lm_head.weight", [hidden, cfg.vocab_size]))
+    return logits, k_caches, v_caches
+
+
+def quantized_weights(cfg: DecoderConfig):
+    """(name, fmt, k, n) of every quantized projection, in graph order."""
+    out = []
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}"
+        out += [(f"{p}.self_attn.q_proj.weight", cfg.attn_fmt, cfg.hidden_size, cfg.q_dim),
+                (f"{p}.self_attn.k_proj.weight", cfg.attn_fmt, cfg.hidden_size, cfg.kv_dim),
+                (f"{p}.self_attn.v_proj.weight", cfg.attn_fmt, cfg.hidden_size, cfg.kv_dim),
+                (f"{p}.self_attn.o_proj.weight", cfg.attn_fmt, cfg.q_dim, cfg.hidden_size),
+                (f"{p}.mlp.gate_proj.weight", cfg.mlp_fmt, cfg.hidden_size, cfg.intermediate_size),
+                (f"{p}.mlp.up_proj.weight", cfg.mlp_fmt, cfg.hidden_size, cfg.intermediate_size),
+                (f"{p}.mlp.down_proj.weight", cfg.mlp_fmt, cfg.intermediate_size, cfg.hidden_size)]
+    out.append(("lm_head.weight", cfg.head_fmt, cfg.hidden_size, cfg.vocab_size))
+    return out
+
+
+def norm_weights(cfg: DecoderConfig):
+    names = []
+    for i in range(cfg.num_hidden_layers):
+        names += [f"model.layers.{i}.input_layernorm.weight", f"model.layers.{i}.post_attention_layernorm.weight"]
+    return names + ["model.norm.weight"]
+
+
+def packed_weight_bytes(cfg: DecoderConfig) -> int:
+    from .ops import packed_bytes
+    return sum(packed_bytes(fmt, k, n) for _, fmt, k, n in quantized_weights(cfg))
+
+
+class DecodeSession:
+    """A decode session with synthetic weights: packed codes and scales as the benchmark
+    configurations describe them (synth.py), norm weights 1, a seeded N(0,1) embedding table."""
+
+    def __init__(self, cfg: DecoderConfig, max_seq_len: int, seed: int = 0, greedy_history: int = 0):
+        self.cfg, self.max_seq_len = cfg, max_seq_len
+        g = Graph()
+        logits, self.k_caches, self.v_caches = build_decode_graph(g, cfg, max_seq_len)
+        g.set_outputs([logits])
+        self.session: Session = build_inference_session(g)
+        s = self.session
+        rng = np.random.Generator(np.random.PCG64(seed))
+        table = rng.standard_normal((cfg.vocab_size, cfg.hidden_size), dtype=np.float32)
+        s.set_parameter("model.embed_tokens.weight", table)
+        ones = np.ones(cfg.hidden_size, dtype=np.float32)
+        for name in norm_weights(cfg):
+            s.set_parameter(name, ones)
+        cache = {}
+        for name, fmt, k, n in quantized_weights(cfg):
+            key = (fmt, k, n)
+            if key not in cache:                     # one seeded tile per shape keeps start-up in seconds
+                base, n0, reps = synth.synth_weights_tiled(fmt, k, n, seed * 1009 + len(cache))
+                cache[key] = synth.tile_columns(fmt, base, k, n0, reps)
+            s.upload_param(name, cache[key])
+        if greedy_history:
+            s.enable_greedy(0, "token_ids", "kv_pos", greedy_history)
+
+    def fill_caches(self, upto: int, seed: int = 1, scale: float = 0.1) -> None:
+        """Pretend `upto` tokens were already decoded: cache rows [0, upto) get N(0,1)*scale."""
+        rng = np.random.Generator(np.random.PCG64(seed))
+        for i in range(self.cfg.num_hidden_layers):
+            for kind in ("k", "v"):
+                rows = np.zeros((self.max_seq_len, self.cfg.kv_dim), dtype=np.float32)
+                rows[:upto] = rng.standard_normal((upto, self.cfg.kv_dim), dtype=np.float32) * scale
+                self.session.set_parameter(f"kv_cache.layer.{i}.{kind}", rows)
+
+    def set_position(self, token: int, pos: int) -> None:
+        self.session.set_input_u32("token_ids", [token])
+        self.session.set_input_u32("kv_pos", [pos])
+
+    def step(self) -> None:
+        self.session.step()
+
+    def logits(self) -> np.ndarray:
+        self.session.wait()
+        return self.session.read_output(self.cfg.vocab_size)

@@ -22,6 +22,14 @@ class ShaderEntry(IntEnum):
     MatMulGemv = 2
     MatMulGemvAdd = 3
     Add = 4
+    Embedding = 5
+    RmsNorm = 6
+    RoPEDynamic = 7
+    CacheWrite = 8
+    CachedAttention = 9
+    SwiGLU = 10
+    SwiGLUConcat = 11
+    RoPECacheWrite = 12
 
 
 class WeightFormat(IntEnum):
@@ -83,6 +91,31 @@ class Graph:
     def add(self, a: int, b: int) -> int:
         return _node(lib.mgq_graph_add(self._h, a, b))
 
+    def input_u32(self, name: str, shape) -> int:
+        return _node(lib.mgq_graph_input_u32(self._h, name.encode(), *_shape(shape)))
+
+    def embedding(self, indices: int, table: int) -> int:
+        return _node(lib.mgq_graph_embedding(self._h, indices, table))
+
+    def rms_norm(self, x: int, weight: int, eps: float) -> int:
+        return _node(lib.mgq_graph_rms_norm(self._h, x, weight, eps))
+
+    def rope_dynamic_offset(self, x: int, theta: float, offset_input: int, head_dim: int) -> int:
+        return _node(lib.mgq_graph_rope_dynamic_offset(self._h, x, theta, offset_input, head_dim))
+
+    def cache_write(self, new_kv: int, cache: int, kv_pos: int) -> int:
+        return _node(lib.mgq_graph_cache_write(self._h, new_kv, cache, kv_pos))
+
+    def cached_attention(self, q: int, k_cache: int, v_cache: int, kv_pos: int, num_heads: int, num_kv_heads: int,
+                         head_dim: int) -> int:
+        return _node(lib.mgq_graph_cached_attention(self._h, q, k_cache, v_cache, kv_pos, num_heads, num_kv_heads, head_dim))
+
+    def swiglu(self, gate: int, up: int) -> int:
+        return _node(lib.mgq_graph_swiglu(self._h, gate, up))
+
+    def swiglu_concat(self, x: int) -> int:
+        return _node(lib.mgq_graph_swiglu_concat(self._h, x))
+
     def set_outputs(self, ids) -> None:
         arr = (ctypes.c_int * len(ids))(*ids)
         check(lib.mgq_graph_set_outputs(self._h, arr, len(ids)))
@@ -109,8 +142,31 @@ class Session:
         data = np.ascontiguousarray(data, dtype=np.float32).reshape(-1)
         check(lib.mgq_session_set_input(self._h, name.encode(), data.ctypes.data, data.size))
 
+    def save_checkpoint(self, path) -> None:
+        check(lib.mgq_session_save_checkpoint(self._h, str(path).encode()))
+
+    def load_checkpoint(self, path) -> None:
+        check(lib.mgq_session_load_checkpoint(self._h, str(path).encode()))
+
+    def set_input_u32(self, name: str, data) -> None:
+        data = np.ascontiguousarray(data, dtype=np.uint32).reshape(-1)
+        check(lib.mgq_session_set_input_u32(self._h, name.encode(), data.ctypes.data, data.size))
+
     def step(self) -> None:
         check(lib.mgq_session_step(self._h))
+
+    def capture(self) -> None:
+        """Capture the dispatch list into a CUDA graph (after at least one ordinary step)."""
+        check(lib.mgq_session_capture(self._h))
+
+    def enable_greedy(self, output_index: int, token_input: str, pos_input: str, history_cap: int) -> None:
+        """Pick the next token on the device after every step and feed it (and position + 1) back."""
+        check(lib.mgq_session_enable_greedy(self._h, output_index, token_input.encode(), pos_input.encode(), history_cap))
+
+    def read_tokens(self, first_pos: int, count: int) -> np.ndarray:
+        out = np.empty(count, dtype=np.uint32)
+        check(lib.mgq_session_read_tokens(self._h, first_pos, out.ctypes.data, count))
+        return out
 
     def wait(self) -> None:
         check(lib.mgq_session_wait(self._h))

@@ -67,6 +67,10 @@ const char *mgq_version(void);
  *                               activation into one GEMV over the concatenated weight: 0 never,
  *                               1 gate|up under a SwiGLU only (the reference's rule,
  *                               src/optimize.rs:776-879), 2 every such group, e.g. q|k|v (default)
+ *   "session.fuse_input"        1: a single-row RmsNorm / SwiGLU consumed only by the next GEMV is
+ *                               computed inside that GEMV (mgq_gemv_rms_norm / _swiglu); 0 (default):
+ *                               separate launches, measured faster (2.95 vs 3.17 ms per token on the
+ *                               Qwen3-8B shape: the transform lengthens every CTA's start-up)
  *   "session.fuse_rope_cache"   1 (default): RoPE(q), RoPE(k), CacheWrite(k), CacheWrite(v) of a decode
  *                               layer run as one launch; 0: four dispatches like the reference */
 int mgq_set_option(const char *name, long value);
@@ -105,6 +109,18 @@ int mgq_buffer_download(const void *dev, void *host, size_t bytes, void *stream)
 #define MGQ_GEMV_MAX_M 16
 int mgq_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
              uint32_t m, uint32_t k, uint32_t n, void *stream);
+
+/* GEMVs that compute their activations while loading them (no reference counterpart: the reference
+ * runs SwiGLU / RmsNorm as dispatches of their own, src/compile.rs:1814-1830 and Op::RmsNorm):
+ *   mgq_gemv_swiglu:    y = (silu(gate) * up) . dequant(w) (+ addend)        gate, up: [m, k]
+ *   mgq_gemv_rms_norm:  y = (x * rsqrt(mean(x^2) + eps) * norm_weight) . dequant(w) (+ addend)
+ * Same results as the separate operator followed by mgq_gemv up to f32 summation order.  m <= 2,
+ * and only shapes the streaming kernels take: mgq_gemv_fusable(x, k, n) != 0 (256 <= k <= 32768, k*n/32 a multiple of 4, x 16-byte aligned); otherwise MGQ_ERR_SHAPE. */
+int mgq_gemv_swiglu(int fmt, const float *gate, const float *up, const void *w, const float *addend, float *y,
+                    uint32_t m, uint32_t k, uint32_t n, void *stream);
+int mgq_gemv_rms_norm(int fmt, const float *x, const float *norm_weight, float eps, const void *w, const float *addend, float *y,
+                      uint32_t m, uint32_t k, uint32_t n, void *stream);
+int mgq_gemv_fusable(const void *x, uint32_t k, uint32_t n);
 
 /* Look-ahead for chains of dependent GEMVs (no reference counterpart: the reference records its
  * dispatches into one command encoder and leaves overlap to the driver, src/runtime.rs:2860-2878).

@@ -64,21 +64,38 @@ __global__ void embedding_kernel(const uint32_t *ids, const float *table, float 
 }
 
 // ---------------------------------------------------------------- RMSNorm (rms_norm.wgsl)
-// One CTA per row: dst = src * rsqrt(mean(src^2) + eps) * weight.
+// One CTA per row: dst = src * rsqrt(mean(src^2) + eps) * weight.  The weight vector is a constant
+// of the model, so it is fetched before the wait on the predecessor; a row of up to 16384 floats
+// stays in registers between the two passes, so the kernel costs one global round trip after the wait.
 __global__ void __launch_bounds__(256) rms_norm_kernel(const float *src, const float *weight, float *dst, uint32_t cols, float eps)
 {
+    constexpr int kHold = 16;                       // float4 values a thread keeps
     __shared__ float s_part[8];
     const uint32_t row = blockIdx.x, t = threadIdx.x;
     const float4 *x4 = reinterpret_cast<const float4 *>(src + (size_t)row * cols);
     const float4 *w4 = reinterpret_cast<const float4 *>(weight);
     float4 *y4 = reinterpret_cast<float4 *>(dst + (size_t)row * cols);
     const uint32_t n4 = cols / 4;
+    const bool held = n4 <= 256u * kHold;
+    float4 w[kHold], v[kHold];
     pdl_launch_dependents();
+    if (held) {
+#pragma unroll
+        for (int i = 0; i < kHold; i++) w[i] = t + 256u * i < n4 ? __ldg(w4 + t + 256u * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     pdl_wait();
     float ss = 0.f;
-    for (uint32_t j = t; j < n4; j += 256) {
-        const float4 v = x4[j];
-        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    if (held) {
+#pragma unroll
+        for (int i = 0; i < kHold; i++) {
+            v[i] = t + 256u * i < n4 ? x4[t + 256u * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+        }
+    } else {
+        for (uint32_t j = t; j < n4; j += 256) {
+            const float4 q = x4[j];
+            ss += q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w;
+        }
     }
     ss = warp_sum(ss);
     if ((t & 31u) == 0) s_part[t >> 5] = ss;
@@ -87,9 +104,15 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float *src, const f
 #pragma unroll
     for (int i = 0; i < 8; i++) total += s_part[i];
     const float r = rsqrtf(total / (float)cols + eps);
-    for (uint32_t j = t; j < n4; j += 256) {
-        const float4 v = x4[j], w = w4[j];
-        y4[j] = make_float4(v.x * r * w.x, v.y * r * w.y, v.z * r * w.z, v.w * r * w.w);
+    if (held) {
+#pragma unroll
+        for (int i = 0; i < kHold; i++)
+            if (t + 256u * i < n4) y4[t + 256u * i] = make_float4(v[i].x * r * w[i].x, v[i].y * r * w[i].y, v[i].z * r * w[i].z, v[i].w * r * w[i].w);
+    } else {
+        for (uint32_t j = t; j < n4; j += 256) {
+            const float4 q = x4[j], u = w4[j];
+            y4[j] = make_float4(q.x * r * u.x, q.y * r * u.y, q.z * r * u.z, q.w * r * u.w);
+        }
     }
 }
 
@@ -188,6 +211,82 @@ __global__ void swiglu_kernel(const float *gate, const float *up, float *out, ui
 constexpr int kChunk = 64;
 constexpr int kMaxGroup = 8;          // query heads per KV head
 
+// The last CTA of a KV head merges the chunk partials: out[g, d] = sum_c w_c acc_c[g, d] / sum_c w_c l_c
+// with w_c = exp(m_c - max_c m_c).  Every global round trip costs ~1 us here (the partials sit in
+// L2, written by other SMs), so the loads are arranged to need few of them: the first batch of
+// accumulator loads is issued before the maxima and sums are even known, and each thread keeps
+// NOUT x BATCH independent loads in flight (thread t owns outputs t + 128 j).
+template <int D, int NOUT, int BATCH>
+__device__ __forceinline__ void merge_partials(const float *base, uint32_t live, uint32_t group, float *s_w, float *out)
+{
+    __shared__ float s_inv[kMaxGroup];
+    constexpr size_t cstride = (size_t)kMaxGroup * (D + 2);
+    const uint32_t t = threadIdx.x, lane = t & 31u, warp = t >> 5, total = group * D;
+    float acc[NOUT], v[NOUT][BATCH];
+    auto fetch = [&](uint32_t c0) {
+#pragma unroll
+        for (int j = 0; j < NOUT; j++) {
+            const uint32_t i = t + 128u * j;
+            const float *col = base + (size_t)(i / D) * (D + 2) + i % D;
+#pragma unroll
+            for (int u = 0; u < BATCH; u++) v[j][u] = (i < total && c0 + u < live) ? __ldcg(col + (c0 + u) * cstride) : 0.f;
+        }
+    };
+#pragma unroll
+    for (int j = 0; j < NOUT; j++) acc[j] = 0.f;
+    fetch(0);
+    // chunk weights into shared memory ([group][kChunk]; at most kChunk chunks, checked at launch)
+    for (uint32_t g = warp; g < group; g += 4) {
+        float mc[2], lc[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint32_t c = lane + 32u * h;
+            const float *pc = base + ((size_t)c * kMaxGroup + g) * (D + 2);
+            mc[h] = c < live ? __ldcg(pc + D) : -FLT_MAX;
+            lc[h] = c < live ? __ldcg(pc + D + 1) : 0.f;
+        }
+        float m = fmaxf(mc[0], mc[1]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float l = 0.f;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const float w = lane + 32u * h < live ? expf(mc[h] - m) : 0.f;
+            s_w[g * kChunk + lane + 32u * h] = w;
+            l = fmaf(lc[h], w, l);
+        }
+        l = warp_sum(l);
+        if (lane == 0) s_inv[g] = 1.0f / (l == 0.f ? 1.f : l);
+    }
+    __syncthreads();
+    for (uint32_t c0 = 0; c0 < live; c0 += BATCH) {
+        if (c0) fetch(c0);
+#pragma unroll
+        for (int j = 0; j < NOUT; j++) {
+            const uint32_t g = min((t + 128u * j) / D, (uint32_t)kMaxGroup - 1u);
+#pragma unroll
+            for (int u = 0; u < BATCH; u++) acc[j] = fmaf(v[j][u], c0 + u < live ? s_w[g * kChunk + c0 + u] : 0.f, acc[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NOUT; j++) {
+        const uint32_t i = t + 128u * j;
+        if (i < total) out[i] = acc[j] * s_inv[i / D];
+    }
+}
+
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem)
+{
+    const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// Dynamic shared memory: the chunk's K rows, then its V rows ([kChunk][D] floats each).  Both tiles
+// are requested with cp.async up front, so a CTA has its whole 64 KB (D = 128) in flight at once
+// instead of paying a memory round trip per position.
 template <int D>                      // head_dim: 64 or 128; blockDim.x == 128
 __global__ void __launch_bounds__(128) cached_attention_kernel(const float *q, const float *k_cache, const float *v_cache,
                                                                const uint32_t *kv_pos, float *out, uint32_t num_heads,
@@ -196,6 +295,8 @@ __global__ void __launch_bounds__(128) cached_attention_kernel(const float *q, c
 {
     constexpr int LPP = D / 4;                    // lanes per position (each lane holds a float4 of the row)
     constexpr int PPW = 32 / LPP;                 // positions per warp step
+    extern __shared__ __align__(16) float s_tiles[];
+    float *s_k = s_tiles, *s_v = s_tiles + kChunk * D;
     __shared__ float s_score[kMaxGroup][kChunk];
     __shared__ float s_q[kMaxGroup][D];
     __shared__ float s_acc[128 / D][kMaxGroup][D];
@@ -211,16 +312,28 @@ __global__ void __launch_bounds__(128) cached_attention_kernel(const float *q, c
     float *part = workspace + ((size_t)kvh * splits + chunk) * kMaxGroup * (D + 2);      // [group][D + 2]: acc, max, sum
 
     if (p0 < kv_len) {
+        const uint32_t rows = p1 - p0;
+        for (uint32_t i = t; i < rows * LPP; i += 128) {
+            const uint32_t r = i / LPP, c = i % LPP;
+            cp_async16(s_k + r * D + c * 4, k_cache + (size_t)(p0 + r) * kv_dim + kvh * D + c * 4);
+        }
+        cp_async_commit();
+        for (uint32_t i = t; i < rows * LPP; i += 128) {
+            const uint32_t r = i / LPP, c = i % LPP;
+            cp_async16(s_v + r * D + c * 4, v_cache + (size_t)(p0 + r) * kv_dim + kvh * D + c * 4);
+        }
+        cp_async_commit();
         for (uint32_t i = t; i < group * D; i += 128) s_q[i / D][i % D] = q[(size_t)kvh * group * D + i];
+        cp_async_wait<1>();
         __syncthreads();
         // scores: PPW positions per warp step, LPP lanes per position
         const uint32_t sub = lane / LPP, li = lane % LPP;
-        for (uint32_t p = p0 + warp * PPW + sub; p < p0 + kChunk; p += 4 * PPW) {
+        for (uint32_t r = warp * PPW + sub; r < (uint32_t)kChunk; r += 4 * PPW) {
             float dot[kMaxGroup];
 #pragma unroll
             for (int g = 0; g < kMaxGroup; g++) dot[g] = 0.f;
-            if (p < p1) {
-                const float4 kv = *reinterpret_cast<const float4 *>(k_cache + (size_t)p * kv_dim + kvh * D + li * 4);
+            if (r < rows) {
+                const float4 kv = *reinterpret_cast<const float4 *>(s_k + r * D + li * 4);
 #pragma unroll
                 for (int g = 0; g < kMaxGroup; g++) {
                     if (g < (int)group) {
@@ -234,7 +347,7 @@ __global__ void __launch_bounds__(128) cached_attention_kernel(const float *q, c
                 if (g < (int)group) {
 #pragma unroll
                     for (int o = LPP / 2; o > 0; o >>= 1) dot[g] += __shfl_xor_sync(0xffffffffu, dot[g], o);
-                    if (li == 0) s_score[g][p - p0] = p < p1 ? dot[g] * scale : -FLT_MAX;
+                    if (li == 0) s_score[g][r] = r < rows ? dot[g] * scale : -FLT_MAX;
                 }
             }
         }
@@ -244,25 +357,26 @@ __global__ void __launch_bounds__(128) cached_attention_kernel(const float *q, c
             float m = fmaxf(s_score[g][lane], s_score[g][lane + 32]);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            const float e0 = p0 + lane < p1 ? expf(s_score[g][lane] - m) : 0.f;
-            const float e1 = p0 + lane + 32 < p1 ? expf(s_score[g][lane + 32] - m) : 0.f;
+            const float e0 = lane < rows ? expf(s_score[g][lane] - m) : 0.f;
+            const float e1 = lane + 32 < rows ? expf(s_score[g][lane + 32] - m) : 0.f;
             s_score[g][lane] = e0;
             s_score[g][lane + 32] = e1;
             const float l = warp_sum(e0 + e1);
             if (lane == 0) { part[g * (D + 2) + D] = m; part[g * (D + 2) + D + 1] = l; }
         }
+        cp_async_wait<0>();
         __syncthreads();
-        // weighted V: thread <-> (position parity slice, dim); 128 / D slices
+        // weighted V: thread <-> (position slice, dim); 128 / D slices
         const uint32_t d = t % D, slice = t / D;
         constexpr uint32_t SL = 128 / D;
         float acc[kMaxGroup];
 #pragma unroll
         for (int g = 0; g < kMaxGroup; g++) acc[g] = 0.f;
-        for (uint32_t p = p0 + slice; p < p1; p += SL) {
-            const float v = v_cache[(size_t)p * kv_dim + kvh * D + d];
+        for (uint32_t r = slice; r < rows; r += SL) {
+            const float v = s_v[r * D + d];
 #pragma unroll
             for (int g = 0; g < kMaxGroup; g++)
-                if (g < (int)group) acc[g] = fmaf(s_score[g][p - p0], v, acc[g]);
+                if (g < (int)group) acc[g] = fmaf(s_score[g][r], v, acc[g]);
         }
 #pragma unroll
         for (int g = 0; g < kMaxGroup; g++)
@@ -289,19 +403,8 @@ __global__ void __launch_bounds__(128) cached_attention_kernel(const float *q, c
     __threadfence();
     const uint32_t live = (kv_len + kChunk - 1) / kChunk;
     const float *base = workspace + (size_t)kvh * splits * kMaxGroup * (D + 2);
-    for (uint32_t i = t; i < group * D; i += 128) {
-        const uint32_t g = i / D, d = i % D;
-        float m = -FLT_MAX;
-        for (uint32_t c = 0; c < live; c++) m = fmaxf(m, __ldcg(base + ((size_t)c * kMaxGroup + g) * (D + 2) + D));
-        float l = 0.f, a = 0.f;
-        for (uint32_t c = 0; c < live; c++) {
-            const float *pc = base + ((size_t)c * kMaxGroup + g) * (D + 2);
-            const float w = expf(__ldcg(pc + D) - m);
-            l = fmaf(__ldcg(pc + D + 1), w, l);
-            a = fmaf(__ldcg(pc + d), w, a);
-        }
-        out[(size_t)(kvh * group + g) * D + d] = a / (l == 0.f ? 1.f : l);
-    }
+    if (group * D <= 4 * 128) merge_partials<D, 4, 16>(base, live, group, &s_score[0][0], out + (size_t)kvh * group * D);
+    else                      merge_partials<D, kMaxGroup, 8>(base, live, group, &s_score[0][0], out + (size_t)kvh * group * D);
 }
 
 // ---------------------------------------------------------------- greedy pick
@@ -345,11 +448,18 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *logits, uint32
         if (s_last) *counter = 0;
     }
     __syncthreads();
-    if (!s_last || t != 0) return;
+    if (!s_last || t >= 32) return;
     __threadfence();
     best = -FLT_MAX;
     best_i = 0xFFFFFFFFu;
-    for (uint32_t b = 0; b < gridDim.x; b++) merge(best, best_i, __ldcg(part_val + b), __ldcg(part_idx + b));
+    for (uint32_t b = t; b < gridDim.x; b += 32) merge(best, best_i, __ldcg(part_val + b), __ldcg(part_idx + b));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        merge(best, best_i, ov, oi);
+    }
+    if (t != 0) return;
     if (best_i == 0xFFFFFFFFu) best_i = 0;                   // every logit was NaN
     *out_token = best_i;
     if (history && kv_pos && kv_pos[0] < history_cap) history[kv_pos[0]] = best_i;
@@ -418,17 +528,27 @@ int launch_cached_attention(const float *q, const float *k_cache, const float *v
     if (num_kv_heads == 0 || num_heads % num_kv_heads != 0) return fail(MGQ_ERR_SHAPE, "attention: %u heads over %u KV heads", num_heads, num_kv_heads);
     if (num_heads / num_kv_heads > (uint32_t)kMaxGroup) return fail(MGQ_ERR_SHAPE, "attention: at most %d query heads per KV head", kMaxGroup);
     if (num_kv_heads > 64) return fail(MGQ_ERR_SHAPE, "attention: at most 64 KV heads");
+    if (max_seq > (uint32_t)(kChunk * kChunk)) return fail(MGQ_ERR_SHAPE, "attention: cache of %u rows (at most %d)", max_seq, kChunk * kChunk);
     if (!workspace) return fail(MGQ_ERR_NULL, "attention needs its workspace");
     unsigned int *counters = static_cast<unsigned int *>(workspace);
     float *partials = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + 256);
     const dim3 grid(num_kv_heads, (max_seq + kChunk - 1) / kChunk);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t tiles = (size_t)2 * kChunk * head_dim * sizeof(float);
     if (head_dim == 64)
-        return launch(cached_attention_kernel<64>, grid, dim3(128), 0, st, q, k_cache, v_cache, kv_pos, out, num_heads, num_kv_heads,
+        return launch(cached_attention_kernel<64>, grid, dim3(128), tiles, st, q, k_cache, v_cache, kv_pos, out, num_heads, num_kv_heads,
                       max_seq, partials, counters);
-    if (head_dim == 128)
-        return launch(cached_attention_kernel<128>, grid, dim3(128), 0, st, q, k_cache, v_cache, kv_pos, out, num_heads, num_kv_heads,
+    if (head_dim == 128) {
+        static bool opted_in[64] = {};
+        int dev = 0;
+        MGQ_CUDA(cudaGetDevice(&dev));
+        if (dev >= 0 && dev < 64 && !opted_in[dev]) {                  // 64 KB of dynamic shared memory needs the opt-in, once per device
+            MGQ_CUDA(cudaFuncSetAttribute(cached_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tiles));
+            opted_in[dev] = true;
+        }
+        return launch(cached_attention_kernel<128>, grid, dim3(128), tiles, st, q, k_cache, v_cache, kv_pos, out, num_heads, num_kv_heads,
                       max_seq, partials, counters);
+    }
     return fail(MGQ_ERR_SHAPE, "attention: head_dim %u (64 and 128 are built)", head_dim);
 }
 

@@ -75,7 +75,7 @@ __device__ __forceinline__ CtaRange cta_range(const GemvParams &p)
     return r;
 }
 
-template <int MT, int C, int TS>
+template <int MT, int C, int TS, bool XF = false>      // XF: activations go through a fused transform (GemvParams::xform)
 __global__ void __launch_bounds__(TS) gemv_q4_kernel(const GemvParams p)
 {
     constexpr int STAGES = kStages, ROUND = kStages * C;
@@ -125,8 +125,9 @@ __global__ void __launch_bounds__(TS) gemv_q4_kernel(const GemvParams p)
     for (int r = 0; r < MT; r++) {
         // x is either a local vector (read-only path: the CTAs of an SM share one fetch) or, when the
         // caller passed none, the gathered vector that was just polled (written by other GPUs: L2 only)
-        if (p.x) load_x<1, false>(p.x + (size_t)r * p.k, b, xb[r]);
-        else     load_x_gathered<1>(p.wait_vec, b, xb[r]);
+        if (XF)       load_x_fused<1>(p, r, b, t < p.bpc, s_red, xb[r]);
+        else if (p.x) load_x<1, false>(p.x + (size_t)r * p.k, b, xb[r]);
+        else          load_x_gathered<1>(p.wait_vec, b, xb[r]);
     }
     const ReduceSlot slot = make_slot<ROUND, TS>(p);
 
@@ -171,7 +172,7 @@ __global__ void __launch_bounds__(TS) gemv_q4_kernel(const GemvParams p)
 
 // ------------------------------------------------------------------------------------ Q8
 
-template <int MT, int C, int TS>
+template <int MT, int C, int TS, bool XF = false>
 __global__ void __launch_bounds__(TS) gemv_q8_kernel(const GemvParams p)
 {
     constexpr int STAGES = kStages, ROUND = kStages * C;
@@ -234,8 +235,9 @@ __global__ void __launch_bounds__(TS) gemv_q8_kernel(const GemvParams p)
     XBlock xb[MT];
 #pragma unroll
     for (int r = 0; r < MT; r++) {
-        if (p.x) load_x<0, false>(p.x + (size_t)r * p.k, b, xb[r]);
-        else     load_x_gathered<0>(p.wait_vec, b, xb[r]);
+        if (XF)       load_x_fused<0>(p, r, b, t < p.bpc, s_red, xb[r]);
+        else if (p.x) load_x<0, false>(p.x + (size_t)r * p.k, b, xb[r]);
+        else          load_x_gathered<0>(p.wait_vec, b, xb[r]);
     }
     const ReduceSlot slot = make_slot<ROUND, TS>(p);
 
@@ -420,27 +422,32 @@ Config choose_config(int fmt, uint32_t bpc, uint32_t n, int mt, int sms)
 
 using KernelFn = void (*)(const GemvParams);
 
-template <int MT, int C>
+template <int MT, int C, bool XF>
 KernelFn pick_by_threads(int fmt, uint32_t threads)
 {
     const bool q4 = fmt == MGQ_FMT_Q4;
     switch (stride_class(threads)) {
-        case 128: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 128> : (KernelFn)gemv_q8_kernel<MT, C, 128>;
-        case 256: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 256> : (KernelFn)gemv_q8_kernel<MT, C, 256>;
-        case 384: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 384> : (KernelFn)gemv_q8_kernel<MT, C, 384>;
-        case 512: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 512> : (KernelFn)gemv_q8_kernel<MT, C, 512>;
+        case 128: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 128, XF> : (KernelFn)gemv_q8_kernel<MT, C, 128, XF>;
+        case 256: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 256, XF> : (KernelFn)gemv_q8_kernel<MT, C, 256, XF>;
+        case 384: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 384, XF> : (KernelFn)gemv_q8_kernel<MT, C, 384, XF>;
+        case 512: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 512, XF> : (KernelFn)gemv_q8_kernel<MT, C, 512, XF>;
         default: return nullptr;
     }
 }
 
-KernelFn pick_kernel(int fmt, int mt, const Config &c)
+// Kernels with a fused input transform exist for single rows only (mt == 1).
+KernelFn pick_kernel(int fmt, int mt, const Config &c, bool xf)
 {
     if (c.threads > 512) {
-        if (mt != 1 || c.cols_per_thread != 1) return nullptr;
+        if (mt != 1 || c.cols_per_thread != 1 || xf) return nullptr;
         return fmt == MGQ_FMT_Q4 ? (KernelFn)gemv_q4_kernel<1, 1, 1024> : (KernelFn)gemv_q8_kernel<1, 1, 1024>;
     }
-    if (c.cols_per_thread == 2) return mt == 2 ? pick_by_threads<2, 2>(fmt, c.threads) : pick_by_threads<1, 2>(fmt, c.threads);
-    return mt == 2 ? pick_by_threads<2, 1>(fmt, c.threads) : pick_by_threads<1, 1>(fmt, c.threads);
+    if (xf) {
+        if (mt != 1) return nullptr;
+        return c.cols_per_thread == 2 ? pick_by_threads<1, 2, true>(fmt, c.threads) : pick_by_threads<1, 1, true>(fmt, c.threads);
+    }
+    if (c.cols_per_thread == 2) return mt == 2 ? pick_by_threads<2, 2, false>(fmt, c.threads) : pick_by_threads<1, 2, false>(fmt, c.threads);
+    return mt == 2 ? pick_by_threads<2, 1, false>(fmt, c.threads) : pick_by_threads<1, 1, false>(fmt, c.threads);
 }
 
 struct DeviceInfo {
@@ -592,8 +599,14 @@ int launch_exchange_finish(const void *last_vec, uint32_t length, unsigned long 
     return MGQ_OK;
 }
 
+bool gemv_streamable(const void *x, uint32_t k, uint32_t n)
+{
+    const uint32_t bpc = k / 32;
+    return bpc >= 8 && bpc <= 1024 && (((unsigned long long)bpc * n) % 4 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0);
+}
+
 int launch_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
-                uint32_t m, uint32_t k, uint32_t n, void *stream_v, const GemvExchange *xchg)
+                uint32_t m, uint32_t k, uint32_t n, void *stream_v, const GemvExchange *xchg, const GemvInput *xin)
 {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const uint32_t bpc = k / 32;
@@ -610,10 +623,16 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
 
     const Lookahead ahead = t_lookahead;
     t_lookahead = Lookahead{};
-    const bool streamable = bpc >= 8 && bpc <= 1024 && (p.num_blocks % 4 == 0) &&
-                            (reinterpret_cast<uintptr_t>(x) % 16 == 0);
+    if (xin && xin->xform != 0) {
+        if (reinterpret_cast<uintptr_t>(xin->x2) % 16 != 0) return fail(MGQ_ERR_ALIGN, "the second activation operand must be 16-byte aligned");
+        p.x2 = xin->x2;
+        p.xform = (uint32_t)xin->xform;
+        p.eps = xin->eps;
+    }
+    const bool streamable = gemv_streamable(x, k, n);
     if (!streamable) {
         if (xchg) return fail(MGQ_ERR_SHAPE, "this shape has no exchanging GEMV kernel (K=%u N=%u)", k, n);
+        if (p.xform) return fail(MGQ_ERR_SHAPE, "this shape has no GEMV kernel with a fused input transform (K=%u N=%u)", k, n);
         p.x = x; p.addend = addend; p.y = y;
         const uint32_t warps = 8, grid = (n + warps - 1) / warps;
         if (fmt == MGQ_FMT_Q4) gemv_generic_kernel<MGQ_FMT_Q4><<<grid, warps * 32, 0, stream>>>(p, m);
@@ -627,15 +646,15 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
 
     // Rows are processed two at a time (their activations live in registers); more rows re-read W.
     for (uint32_t r0 = 0; r0 < m;) {
-        const int mt = (m - r0 >= 2 && bpc <= 512) ? 2 : 1;
+        const int mt = (m - r0 >= 2 && bpc <= 512 && !p.xform) ? 2 : 1;
         const Config cfg = choose_config(fmt, bpc, n, mt, di.sms);
         p.cpi = cfg.cpi;
         p.active = cfg.cpi * bpc;
         p.red_shift = cfg.red_shift;
         p.red_chunk = cfg.red_chunk;
         p.total_iters = (n + cfg.cpi - 1) / cfg.cpi;
-        KernelFn fn = pick_kernel(fmt, mt, cfg);
-        if (!fn) return fail(MGQ_ERR_SHAPE, "no GEMV kernel for K=%u", k);
+        KernelFn fn = pick_kernel(fmt, mt, cfg, p.xform != 0);
+        if (!fn) return fail(MGQ_ERR_SHAPE, "no GEMV kernel for K=%u%s", k, p.xform ? " with a fused input transform" : "");
         const size_t smem = smem_bytes(fmt, cfg.threads, (int)cfg.cols_per_thread, mt);
         int occ = 0;
         if (int rc = kernel_occupancy(fn, cfg.threads, smem, occ)) return rc;
@@ -661,6 +680,7 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
             if (launch_smem > di.smem_optin) launch_smem = di.smem_optin;
         }
         p.x = x + (size_t)r0 * k;
+        if (p.xform == kXformSwiglu) p.x2 = xin->x2 + (size_t)r0 * k;          // up has rows like gate; a norm weight has one
         p.addend = addend ? addend + (size_t)r0 * n : nullptr;
         p.y = y + (size_t)r0 * n;
         p.ahead = nullptr;

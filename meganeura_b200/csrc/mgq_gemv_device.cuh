@@ -29,6 +29,10 @@ struct GemvParams {
     const float2 *wait_vec;                   // local gathered {value, stamp} vector (length k) that must carry this token's stamps
     const unsigned long long *epoch;          // local token index
     unsigned int *xerror;                     // raised when the bounded wait runs out
+    // activation transform fused into the load (kXform*): x2 is `up` (SwiGLU) or the norm weight (RMSNorm)
+    const float *x2;
+    uint32_t xform;
+    float eps;
     // look-ahead: packed weights of the GEMV that follows this one in the stream (may be null)
     const uint8_t *ahead;
     uint32_t ahead_per_cta;                   // bytes each CTA asks L2 to fetch, a multiple of 512
@@ -225,6 +229,57 @@ __device__ __forceinline__ void load_x(const float *xrow, uint32_t b, XBlock &xb
     for (int j = 0; j < 8; j++) {
         const float4 t = COHERENT ? __ldcg(xp + j) : __ldg(xp + j);
         v[4 * j + 0] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+    }
+    prepare_x<ORDER>(v, xb);
+}
+
+// What a decode graph computes right before a GEMV can be computed while the GEMV loads its
+// activations instead of in a launch of its own (every thread redoes it for its 32 elements):
+//   kXformSwiglu   x = silu(gate) * up                          (gate = p.x, up = p.x2)
+//   kXformRmsNorm  x = x * rsqrt(mean(x^2) + eps) * weight      (weight = p.x2; the mean runs over the
+//                  whole row, so the CTA adds up the squares of one thread per block: one barrier)
+constexpr uint32_t kXformNone = 0, kXformSwiglu = 1, kXformRmsNorm = 2;
+
+template <int ORDER>
+__device__ __forceinline__ void load_x_fused(const GemvParams &p, uint32_t row, uint32_t b, bool first_copy, float *scratch, XBlock &xb)
+{
+    const float4 *xp = reinterpret_cast<const float4 *>(p.x + (size_t)row * p.k + 32u * b);
+    const float4 *wp = reinterpret_cast<const float4 *>(p.x2 + (p.xform == kXformSwiglu ? (size_t)row * p.k : 0) + 32u * b);
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const float4 t = __ldg(xp + j);
+        v[4 * j + 0] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+    }
+    float r = 1.f;
+    if (p.xform == kXformRmsNorm) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; i++) ss = fmaf(v[i], v[i], ss);
+        if (!first_copy) ss = 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if ((threadIdx.x & 31u) == 0) scratch[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float total = 0.f;
+        for (uint32_t i = 0; i < (blockDim.x + 31u) / 32u; i++) total += scratch[i];
+        __syncthreads();                                      // scratch is reused (next row, then the reduction)
+        r = rsqrtf(total / (float)p.k + p.eps);
+    }
+    // the second operand is consumed in two halves of 16 so that it never occupies 32 registers
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        float w[16];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float4 u = __ldg(wp + 4 * h + j);
+            w[4 * j + 0] = u.x; w[4 * j + 1] = u.y; w[4 * j + 2] = u.z; w[4 * j + 3] = u.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const float x = v[16 * h + i];
+            v[16 * h + i] = p.xform == kXformSwiglu ? x * (1.0f / (1.0f + expf(-x))) * w[i] : x * r * w[i];
+        }
     }
     prepare_x<ORDER>(v, xb);
 }

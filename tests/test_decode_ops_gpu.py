@@ -8,6 +8,7 @@ from oracle import decode_oracle as D
 from gpu_util import to_dev
 
 pytestmark = pytest.mark.gpu
+O_FMT_Q4, O_FMT_Q8 = 2, 3
 
 
 def _stream():
@@ -28,11 +29,12 @@ def test_embedding_rows():
     table = rng.standard_normal((300, 576)).astype(np.float32)
     ids = np.array([0, 299, 17, 17], dtype=np.uint32)
     out = torch.zeros((4, 576), dtype=torch.float32, device="cuda")
-    check(lib.mgq_embedding(to_dev(ids).data_ptr(), to_dev(table).data_ptr(), out.data_ptr(), 4, 576, 300, _stream()))
+    ids_d, table_d = to_dev(ids), to_dev(table)                       # device inputs must outlive the launch
+    check(lib.mgq_embedding(ids_d.data_ptr(), table_d.data_ptr(), out.data_ptr(), 4, 576, 300, _stream()))
     assert np.array_equal(out.cpu().numpy(), D.embedding(ids, table))
 
 
-@pytest.mark.parametrize("rows,cols,eps", [(1, 576, 1e-5), (1, 4096, 1e-6), (3, 1536, 1e-5), (1, 12288, 1e-6)])
+@pytest.mark.parametrize("rows,cols,eps", [(1, 576, 1e-5), (1, 4096, 1e-6), (3, 1536, 1e-5), (1, 12288, 1e-6), (2, 20480, 1e-6)])
 def test_rms_norm(rows, cols, eps):
     import torch
     from meganeura_b200._lib import check, lib
@@ -40,7 +42,8 @@ def test_rms_norm(rows, cols, eps):
     x = (rng.standard_normal((rows, cols)) * 3).astype(np.float32)
     w = rng.standard_normal(cols).astype(np.float32)
     out = torch.zeros((rows, cols), dtype=torch.float32, device="cuda")
-    check(lib.mgq_rms_norm(to_dev(x).data_ptr(), to_dev(w).data_ptr(), out.data_ptr(), rows, cols, eps, _stream()))
+    xd, wd = to_dev(x), to_dev(w)
+    check(lib.mgq_rms_norm(xd.data_ptr(), wd.data_ptr(), out.data_ptr(), rows, cols, eps, _stream()))
     _close(out.cpu().numpy(), D.rms_norm(x, w, eps))
 
 
@@ -51,8 +54,8 @@ def test_rope_dynamic(dim, head_dim, theta, pos):
     rng = np.random.Generator(np.random.PCG64(3))
     x = rng.standard_normal((1, dim)).astype(np.float32)
     out = torch.zeros((1, dim), dtype=torch.float32, device="cuda")
-    check(lib.mgq_rope_dynamic(to_dev(x).data_ptr(), out.data_ptr(), to_dev(np.array([pos], dtype=np.uint32)).data_ptr(),
-                               1, dim, head_dim, theta, _stream()))
+    xd, posd = to_dev(x), to_dev(np.array([pos], dtype=np.uint32))
+    check(lib.mgq_rope_dynamic(xd.data_ptr(), out.data_ptr(), posd.data_ptr(), 1, dim, head_dim, theta, _stream()))
     # angles reach thousands of radians; f32 angle rounding (2^-13 at 2047) bounds the agreement
     _close(out.cpu().numpy(), D.rope(x, theta, pos, head_dim), tol=2e-4 if pos > 100 else 1e-5)
 
@@ -62,12 +65,13 @@ def test_cache_write_touches_one_row():
     from meganeura_b200._lib import check, lib
     cache = torch.full((8, 192), 7.0, dtype=torch.float32, device="cuda")
     src = to_dev(np.arange(192, dtype=np.float32).reshape(1, 192))
-    check(lib.mgq_cache_write(src.data_ptr(), cache.data_ptr(), to_dev(np.array([5], dtype=np.uint32)).data_ptr(), 192, 8, _stream()))
+    pos5, pos8 = to_dev(np.array([5], dtype=np.uint32)), to_dev(np.array([8], dtype=np.uint32))
+    check(lib.mgq_cache_write(src.data_ptr(), cache.data_ptr(), pos5.data_ptr(), 192, 8, _stream()))
     host = cache.cpu().numpy()
     assert np.array_equal(host[5], np.arange(192, dtype=np.float32))
     assert (np.delete(host, 5, axis=0) == 7.0).all()
     # a position past the end of the cache writes nothing
-    check(lib.mgq_cache_write(src.data_ptr(), cache.data_ptr(), to_dev(np.array([8], dtype=np.uint32)).data_ptr(), 192, 8, _stream()))
+    check(lib.mgq_cache_write(src.data_ptr(), cache.data_ptr(), pos8.data_ptr(), 192, 8, _stream()))
     assert np.array_equal(cache.cpu().numpy(), host)
 
 
@@ -144,3 +148,27 @@ def test_argmax_lowest_index_wins_and_feedback():
     # without feedback nothing but the token is written
     check(lib.mgq_argmax(ld.data_ptr(), 1000, ws.data_ptr(), tok.data_ptr(), None, None, None, 0, _stream()))
     assert int(tok.item()) == int(np.argmax(logits[:1000])) and int(pos.cpu().numpy()[0]) == 5
+
+
+@pytest.mark.parametrize("fmt", [O_FMT_Q4, O_FMT_Q8])
+@pytest.mark.parametrize("k,n", [(576, 960), (4096, 1024), (1536, 576), (12288, 512)])
+def test_gemv_with_fused_rms_norm_and_swiglu(fmt, k, n):
+    """mgq_gemv_rms_norm / mgq_gemv_swiglu against the oracle operator followed by the f64 oracle GEMV."""
+    import torch
+    from oracle import oracle as O
+    from meganeura_b200._lib import check, lib
+    rng = np.random.Generator(np.random.PCG64(k + n))
+    packed = O.synth_weights(fmt, k, n, seed=k)
+    wd = to_dev(packed)
+    x = (rng.standard_normal((1, k)) * 2).astype(np.float32)
+    nw = (1 + 0.2 * rng.standard_normal(k)).astype(np.float32)
+    up = rng.standard_normal((1, k)).astype(np.float32)
+    addend = rng.standard_normal((1, n)).astype(np.float32)
+    y = torch.zeros((1, n), dtype=torch.float32, device="cuda")
+    xd, nwd, upd, addd = to_dev(x), to_dev(nw), to_dev(up), to_dev(addend)
+    check(lib.mgq_gemv_rms_norm(fmt, xd.data_ptr(), nwd.data_ptr(), 1e-5, wd.data_ptr(), None, y.data_ptr(), 1, k, n, _stream()))
+    want = O.matmul_f64_np(fmt, D.rms_norm(x, nw, 1e-5), packed, k, n)
+    assert O.rel_l2(y.cpu().numpy(), want) <= 1e-4
+    check(lib.mgq_gemv_swiglu(fmt, xd.data_ptr(), upd.data_ptr(), wd.data_ptr(), addd.data_ptr(), y.data_ptr(), 1, k, n, _stream()))
+    want = O.matmul_f64_np(fmt, D.swiglu(x, up), packed, k, n, addend=addend)
+    assert O.rel_l2(y.cpu().numpy(), want) <= 1e-4

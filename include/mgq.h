@@ -59,6 +59,8 @@ const char *mgq_version(void);
  *                               (no programmatic dependent launch); also MGQ_SERIAL_DISPATCH=1
  *   "gemv.columns_per_thread"   1 or 2 columns per thread and pipeline stage
  *   "gemv.ctas_per_sm"          CTAs per SM a GEMV grid is sized for (default 3)
+ *   "gemv.batch_mma"            1 (default): 3..16 rows run on the integer tensor-core kernel that reads
+ *                               the weights once per 8 rows; 0: two rows at a time on the streaming kernels
  *   "gemv.lookahead_bytes"      most bytes of the following GEMV's weights that a GEMV asks L2 to
  *                               fetch (mgq_gemv_lookahead); 0 = look-ahead off (the default)
  *   "plan.columns_per_thread"   1, 2 or 4 for plans created afterwards (default 2: two CTAs per SM)

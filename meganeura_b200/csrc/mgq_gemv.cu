@@ -340,6 +340,7 @@ struct Tuning {
     int cols_per_thread = 0;   // "gemv.columns_per_thread": 1 or 2
     int ctas_per_sm = 0;       // "gemv.ctas_per_sm"
     int serial = -1;           // "gemv.serial_dispatch": 1 turns programmatic dependent launch off
+    int batch_mma = 1;          // "gemv.batch_mma": 3..16 rows run on the mma kernel (0: pairs of rows on the streaming kernels)
     long ahead_cap = 0;         // "gemv.lookahead_bytes": most bytes of the next GEMV's weights requested into L2 (0 = off)
 };
 Tuning g_tuning;
@@ -550,6 +551,8 @@ int set_gemv_option(const char *name, long value)
         g_tuning.ctas_per_sm = (int)value;
     } else if (!std::strcmp(name, "gemv.serial_dispatch")) {
         g_tuning.serial = value < 0 ? -1 : (value ? 1 : 0);
+    } else if (!std::strcmp(name, "gemv.batch_mma")) {
+        g_tuning.batch_mma = value ? 1 : 0;
     } else if (!std::strcmp(name, "gemv.lookahead_bytes")) {
         if (value < 0 || value > (1l << 30)) return fail(MGQ_ERR_SHAPE, "%s out of range", name);
         g_tuning.ahead_cap = value;
@@ -623,6 +626,8 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
 
     const Lookahead ahead = t_lookahead;
     t_lookahead = Lookahead{};
+    if (!xchg && !(xin && xin->xform) && g_tuning.batch_mma && gemv_mma_eligible(m, k, n, x, w))
+        return launch_gemv_mma(fmt, x, w, addend, y, m, k, n, stream_v);
     if (xin && xin->xform != 0) {
         if (reinterpret_cast<uintptr_t>(xin->x2) % 16 != 0) return fail(MGQ_ERR_ALIGN, "the second activation operand must be 16-byte aligned");
         p.x2 = xin->x2;

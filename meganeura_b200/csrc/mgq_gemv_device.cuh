@@ -184,7 +184,9 @@ struct XBlock {
 // ORDER 1 (Q4): word 2j holds elements 8j+{0,2,4,6} (low nibbles of nibble word j),
 //               word 2j+1 holds elements 8j+{1,3,5,7} (high nibbles).
 // Turns 32 activations (already in registers) into the three byte planes, scale and sum.
-template <int ORDER>
+// SIGNED_DIGITS: all three planes are signed bytes, X = p2*65536 + p1*256 + p0 with every digit in
+// [-128, 127] (what an int8 tensor-core operand wants); otherwise planes 0 and 1 are unsigned.
+template <int ORDER, bool SIGNED_DIGITS = false>
 __device__ __forceinline__ void prepare_x(const float (&v)[32], XBlock &xb)
 {
     float amax = 0.f, s0 = 0.f, s1 = 0.f;
@@ -205,15 +207,16 @@ __device__ __forceinline__ void prepare_x(const float (&v)[32], XBlock &xb)
     // float's bit pattern are the planes, the top one offset by 64.
     uint32_t bits[32];
 #pragma unroll
-    for (int i = 0; i < 32; i++) bits[i] = __float_as_uint(fmaf(v[i], scale, 12582912.f));
+    // (signed digits: adding 128 to the two low bytes, with carries, makes byte - 128 the balanced digit)
+    for (int i = 0; i < 32; i++) bits[i] = __float_as_uint(fmaf(v[i], scale, 12582912.f)) + (SIGNED_DIGITS ? 0x8080u : 0u);
 #pragma unroll
     for (int w = 0; w < 8; w++) {
         int e0, e1, e2, e3;
         if (ORDER == 0) { e0 = 4 * w; e1 = e0 + 1; e2 = e0 + 2; e3 = e0 + 3; }
         else            { e0 = 8 * (w >> 1) + (w & 1); e1 = e0 + 2; e2 = e0 + 4; e3 = e0 + 6; }
         const uint32_t a = bits[e0], bb = bits[e1], c = bits[e2], d = bits[e3];
-        xb.p0[w] = __byte_perm(__byte_perm(a, bb, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
-        xb.p1[w] = __byte_perm(__byte_perm(a, bb, 0x0051), __byte_perm(c, d, 0x0051), 0x5410);
+        xb.p0[w] = __byte_perm(__byte_perm(a, bb, 0x0040), __byte_perm(c, d, 0x0040), 0x5410) ^ (SIGNED_DIGITS ? 0x80808080u : 0u);
+        xb.p1[w] = __byte_perm(__byte_perm(a, bb, 0x0051), __byte_perm(c, d, 0x0051), 0x5410) ^ (SIGNED_DIGITS ? 0x80808080u : 0u);
         const uint32_t top = __byte_perm(__byte_perm(a, bb, 0x0062), __byte_perm(c, d, 0x0062), 0x5410);
         xb.p2[w] = (top + 0x40404040u) ^ 0x80808080u;                  // (u + 64) - 128 = u - 64 as int8; u <= 127: no carries
     }

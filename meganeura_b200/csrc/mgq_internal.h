@@ -35,6 +35,10 @@ struct GemvInput {
 int launch_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
                 uint32_t m, uint32_t k, uint32_t n, void *stream, const GemvExchange *xchg = nullptr,
                 const GemvInput *xin = nullptr);
+// Tensor-core (mma, int8 digit planes) GEMV for 3..16 rows (mgq_gemv_mma.cu).
+bool gemv_mma_eligible(uint32_t m, uint32_t k, uint32_t n, const void *x, const void *w);
+int launch_gemv_mma(int fmt, const float *x, const void *w, const float *addend, float *y,
+                    uint32_t m, uint32_t k, uint32_t n, void *stream);
 bool gemv_streamable(const void *x, uint32_t k, uint32_t n);   // the streaming kernels take this shape (else the generic kernel runs)
 int launch_exchange_finish(const void *last_vec, uint32_t length, unsigned long long *epoch,
                            unsigned int *error, unsigned int *blocks_done, void *stream);

@@ -287,7 +287,7 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // Dynamic shared memory: the chunk's K rows, then its V rows ([kChunk][D] floats each).  Both tiles
 // are requested with cp.async up front, so a CTA has its whole 64 KB (D = 128) in flight at once
 // instead of paying a memory round trip per position.
-template <int D>                      // head_dim: 64 or 128; blockDim.x == 128
+template <int D, int G2>              // head_dim: 64 or 128; G2: query heads per KV head rounded up to 4 or 8; blockDim.x == 128
 __global__ void __launch_bounds__(128) cached_attention_kernel(const float *q, const float *k_cache, const float *v_cache,
                                                                const uint32_t *kv_pos, float *out, uint32_t num_heads,
                                                                uint32_t num_kv_heads, uint32_t max_seq, float *workspace,
@@ -326,30 +326,42 @@ __global__ void __launch_bounds__(128) cached_attention_kernel(const float *q, c
         for (uint32_t i = t; i < group * D; i += 128) s_q[i / D][i % D] = q[(size_t)kvh * group * D + i];
         cp_async_wait<1>();
         __syncthreads();
-        // scores: PPW positions per warp step, LPP lanes per position
+        // scores: PPW positions per warp step, LPP lanes per position.  The query slices stay in
+        // registers; the G2 partial dot products of a row are reduced together: every exchange with
+        // the lane `off` away halves the number of heads a lane is still responsible for, so a row
+        // costs G2 - 1 + log2(LPP / G2) shuffles instead of one full reduction per head.
         const uint32_t sub = lane / LPP, li = lane % LPP;
-        for (uint32_t r = warp * PPW + sub; r < (uint32_t)kChunk; r += 4 * PPW) {
-            float dot[kMaxGroup];
+        float4 qreg[G2];
 #pragma unroll
-            for (int g = 0; g < kMaxGroup; g++) dot[g] = 0.f;
+        for (int h = 0; h < G2; h++)
+            qreg[h] = h < (int)group ? *reinterpret_cast<const float4 *>(&s_q[h][li * 4]) : make_float4(0.f, 0.f, 0.f, 0.f);
+        // the head this lane ends up with: one bit per halving step, taken from the lane's position
+        uint32_t my_head = 0;
+#pragma unroll
+        for (int keep = G2 / 2, off = LPP / 2; keep >= 1; keep >>= 1, off >>= 1) my_head = my_head * 2u + ((li & off) ? 1u : 0u);
+        for (uint32_t r = warp * PPW + sub; r < (uint32_t)kChunk; r += 4 * PPW) {
+            float v[G2];
             if (r < rows) {
                 const float4 kv = *reinterpret_cast<const float4 *>(s_k + r * D + li * 4);
 #pragma unroll
-                for (int g = 0; g < kMaxGroup; g++) {
-                    if (g < (int)group) {
-                        const float4 qv = *reinterpret_cast<const float4 *>(&s_q[g][li * 4]);
-                        dot[g] = kv.x * qv.x + kv.y * qv.y + kv.z * qv.z + kv.w * qv.w;
-                    }
+                for (int h = 0; h < G2; h++) v[h] = kv.x * qreg[h].x + kv.y * qreg[h].y + kv.z * qreg[h].z + kv.w * qreg[h].w;
+            } else {
+#pragma unroll
+                for (int h = 0; h < G2; h++) v[h] = 0.f;
+            }
+#pragma unroll
+            for (int keep = G2 / 2, off = LPP / 2; keep >= 1; keep >>= 1, off >>= 1) {
+                const bool upper = (li & off) != 0;
+#pragma unroll
+                for (int i = 0; i < keep; i++) {
+                    const float send = upper ? v[i] : v[i + keep];
+                    const float mine = upper ? v[i + keep] : v[i];
+                    v[i] = mine + __shfl_xor_sync(0xffffffffu, send, off);
                 }
             }
 #pragma unroll
-            for (int g = 0; g < kMaxGroup; g++) {
-                if (g < (int)group) {
-#pragma unroll
-                    for (int o = LPP / 2; o > 0; o >>= 1) dot[g] += __shfl_xor_sync(0xffffffffu, dot[g], o);
-                    if (li == 0) s_score[g][r] = r < rows ? dot[g] * scale : -FLT_MAX;
-                }
-            }
+            for (int off = LPP / (2 * G2); off > 0; off >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
+            if ((li & (LPP / G2 - 1)) == 0 && my_head < group) s_score[my_head][r] = r < rows ? v[0] * scale : -FLT_MAX;
         }
         __syncthreads();
         // per head: chunk maximum and exponentials (warp w takes heads w, w+4)
@@ -535,19 +547,21 @@ int launch_cached_attention(const float *q, const float *k_cache, const float *v
     const dim3 grid(num_kv_heads, (max_seq + kChunk - 1) / kChunk);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t tiles = (size_t)2 * kChunk * head_dim * sizeof(float);
+    const bool small_group = num_heads / num_kv_heads <= 4;
     if (head_dim == 64)
-        return launch(cached_attention_kernel<64>, grid, dim3(128), tiles, st, q, k_cache, v_cache, kv_pos, out, num_heads, num_kv_heads,
-                      max_seq, partials, counters);
+        return launch(small_group ? cached_attention_kernel<64, 4> : cached_attention_kernel<64, 8>, grid, dim3(128), tiles, st, q, k_cache,
+                      v_cache, kv_pos, out, num_heads, num_kv_heads, max_seq, partials, counters);
     if (head_dim == 128) {
         static bool opted_in[64] = {};
         int dev = 0;
         MGQ_CUDA(cudaGetDevice(&dev));
         if (dev >= 0 && dev < 64 && !opted_in[dev]) {                  // 64 KB of dynamic shared memory needs the opt-in, once per device
-            MGQ_CUDA(cudaFuncSetAttribute(cached_attention_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tiles));
+            MGQ_CUDA(cudaFuncSetAttribute(cached_attention_kernel<128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tiles));
+            MGQ_CUDA(cudaFuncSetAttribute(cached_attention_kernel<128, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tiles));
             opted_in[dev] = true;
         }
-        return launch(cached_attention_kernel<128>, grid, dim3(128), tiles, st, q, k_cache, v_cache, kv_pos, out, num_heads, num_kv_heads,
-                      max_seq, partials, counters);
+        return launch(small_group ? cached_attention_kernel<128, 4> : cached_attention_kernel<128, 8>, grid, dim3(128), tiles, st, q, k_cache,
+                      v_cache, kv_pos, out, num_heads, num_kv_heads, max_seq, partials, counters);
     }
     return fail(MGQ_ERR_SHAPE, "attention: head_dim %u (64 and 128 are built)", head_dim);
 }

@@ -199,7 +199,6 @@ __global__ void __launch_bounds__(kWarps * 32) gemv_mma_kernel(const MmaParams p
     __syncthreads();
 
     // ---- main loop: a tile at a time; one stage = 16 columns x 4 blocks
-    constexpr int kMagic = 0x4B400000;                      // as float: 12582912 + integer
     uint32_t item = 0;
     for (uint32_t j = 0; j < my_tiles; j++) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f};                // (col g, row 2t), (col g, row 2t+1), (col g+8, row 2t), (col g+8, row 2t+1)
@@ -239,26 +238,41 @@ __global__ void __launch_bounds__(kWarps * 32) gemv_mma_kernel(const MmaParams p
                         hd0 = make_float2(__half2float(__ushort_as_half((unsigned short)(r0[0] & 0xFFFFu))), 0.f);
                         hd1 = make_float2(__half2float(__ushort_as_half((unsigned short)(r1[0] & 0xFFFFu))), 0.f);
                     }
-                    int c0[4] = {kMagic, kMagic, kMagic, kMagic}, c1[4] = {kMagic, kMagic, kMagic, kMagic},
-                        c2[4] = {kMagic, kMagic, kMagic, kMagic};
                     const uint2 b0 = *reinterpret_cast<const uint2 *>(s_planes + (bl * 3u + 0u) * 64u + lane * 2u);
                     const uint2 b1 = *reinterpret_cast<const uint2 *>(s_planes + (bl * 3u + 1u) * 64u + lane * 2u);
                     const uint2 b2 = *reinterpret_cast<const uint2 *>(s_planes + (bl * 3u + 2u) * 64u + lane * 2u);
-                    if (FMT == MGQ_FMT_Q4) {
-                        mma_u8s8(c0, a, b0.x, b0.y); mma_u8s8(c1, a, b1.x, b1.y); mma_u8s8(c2, a, b2.x, b2.y);
-                    } else {
-                        mma_s8s8(c0, a, b0.x, b0.y); mma_s8s8(c1, a, b1.x, b1.y); mma_s8s8(c2, a, b2.x, b2.y);
-                    }
                     // (2^(E-21), sum) of batch rows 2t and 2t+1 for this block
                     const float4 sc = *reinterpret_cast<const float4 *>(s_scale + (bl * 8u + 2u * tq) * 2u);
+                    float dot[4];
+                    if (FMT == MGQ_FMT_Q4) {
+                        // |sum of nibble * X| <= 32 * 15 * 2^22 < 2^31: the three digits share ONE integer
+                        // accumulator, shifted by a byte between the MMAs (top digit first)
+                        int c[4] = {0, 0, 0, 0};
+                        mma_u8s8(c, a, b2.x, b2.y);
+#pragma unroll
+                        for (int i = 0; i < 4; i++) c[i] *= 256;
+                        mma_u8s8(c, a, b1.x, b1.y);
+#pragma unroll
+                        for (int i = 0; i < 4; i++) c[i] *= 256;
+                        mma_u8s8(c, a, b0.x, b0.y);
+#pragma unroll
+                        for (int i = 0; i < 4; i++) dot[i] = (float)c[i];
+                    } else {
+                        // int8 codes: the two upper digits fit one accumulator (32 * 128 * (64 * 256 + 128) < 2^27)
+                        int ch[4] = {0, 0, 0, 0}, cl[4] = {0, 0, 0, 0};
+                        mma_s8s8(ch, a, b2.x, b2.y);
+                        mma_s8s8(cl, a, b0.x, b0.y);
+#pragma unroll
+                        for (int i = 0; i < 4; i++) ch[i] *= 256;
+                        mma_s8s8(ch, a, b1.x, b1.y);
+#pragma unroll
+                        for (int i = 0; i < 4; i++) dot[i] = fmaf((float)ch[i], 256.f, (float)cl[i]);
+                    }
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
-                        const float f0 = __int_as_float(c0[i]) - 12582912.f, f1 = __int_as_float(c1[i]) - 12582912.f,
-                                    f2 = __int_as_float(c2[i]) - 12582912.f;
-                        const float dot = fmaf(f2, 65536.f, fmaf(f1, 256.f, f0));
                         const float2 hd = i < 2 ? hd0 : hd1;
                         const float inv = (i & 1) ? sc.z : sc.x, sm = (i & 1) ? sc.w : sc.y;
-                        acc[i] = FMT == MGQ_FMT_Q4 ? fmaf(hd.x * inv, dot, fmaf(hd.y, sm, acc[i])) : fmaf(hd.x * inv, dot, acc[i]);
+                        acc[i] = FMT == MGQ_FMT_Q4 ? fmaf(hd.x * inv, dot[i], fmaf(hd.y, sm, acc[i])) : fmaf(hd.x * inv, dot[i], acc[i]);
                     }
                 }
             }

@@ -3,6 +3,7 @@
     python -m meganeura_b200.kernel_cases gemv q4 4096x151936 [--launches 3] [--rows 1]
     python -m meganeura_b200.kernel_cases gemm q8 512x4096x14336 [--launches 3]
     python -m meganeura_b200.kernel_cases sweep q4            # the SmolLM2-135M decode shapes
+    python -m meganeura_b200.kernel_cases decode qwen3-8b --layers 4 --steps 4 [--context 2048]
 
 `gemv` rotates through enough distinct weight copies to exceed L2 several times over and replays
 the launches from a CUDA graph, so the printed GB/s is a streaming (cold-cache) figure; with
@@ -85,15 +86,44 @@ def gemm_case(fmt, m, k, n, launches=0):
     return tf
 
 
+def decode_case(model, layers, steps, context):
+    """A few whole decode steps of a shortened model through the session (plain launches, no graph):
+    what a profiler capture of the decode-step operators wants."""
+    import time
+    from dataclasses import replace
+    from . import decode_model as M
+    cfg = replace(M.QWEN3_8B if model == "qwen3-8b" else M.SMOLLM2_135M, num_hidden_layers=layers)
+    dec = M.DecodeSession(cfg, context + steps + 8, seed=3, greedy_history=context + steps + 8)
+    dec.fill_caches(context)
+    dec.set_position(1, context)
+    dec.step()
+    dec.session.wait()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        dec.step()
+    dec.session.wait()
+    print(f"decode {cfg.name}, {layers} layers, context {context}: {(time.perf_counter() - t0) / steps * 1e3:.3f} ms/token "
+          f"({len(dec.session.plan().dispatches) + 1} launches, no graph)")
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kind", choices=["gemv", "gemm", "sweep"])
-    ap.add_argument("fmt", choices=["q4", "q8"])
+    ap.add_argument("kind", choices=["gemv", "gemm", "sweep", "decode"])
+    ap.add_argument("fmt", help="q4 | q8, or the model for `decode` (qwen3-8b | smollm2-135m)")
     ap.add_argument("shape", nargs="?", default="")
     ap.add_argument("--launches", type=int, default=0)
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--peak-gbs", type=float, default=None)
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--context", type=int, default=2048)
     args = ap.parse_args()
+    if args.kind == "decode":
+        if args.fmt not in ("qwen3-8b", "smollm2-135m"):
+            ap.error("decode takes qwen3-8b or smollm2-135m")
+        return decode_case(args.fmt, args.layers, args.steps, args.context)
+    if args.fmt not in ("q4", "q8"):
+        ap.error("format must be q4 or q8")
     fmt = FMT_Q4 if args.fmt == "q4" else FMT_Q8
     warm = torch.randn(8192, 8192, device="cuda")          # bring the clocks up
     for _ in range(10):

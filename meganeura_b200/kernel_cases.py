@@ -26,10 +26,12 @@ def _weights(fmt, k, n, seed=1):
     return synth.tile_columns(fmt, torch.from_numpy(base).cuda(), k, n0, reps)
 
 
-def gemv_case(fmt, k, n, rows=1, launches=0, peak_gbs=None):
+def gemv_case(fmt, k, n, rows=1, launches=0, peak_gbs=None, hot=False):
+    """hot=True keeps ONE weight copy (L2-resident for small shapes); the default rotates copies so
+    that every launch streams from HBM."""
     w = _weights(fmt, k, n)
     nbytes = w.numel()
-    copies = 1 if launches else max(2, min(64, int(600e6 // nbytes) + 1))
+    copies = 1 if (launches or hot) else max(2, min(64, int(600e6 // nbytes) + 1))
     ws = [w] + [w.clone() for _ in range(copies - 1)]
     x = torch.randn((rows, k), device="cuda")
     y = torch.empty((rows, n), device="cuda")
@@ -59,7 +61,7 @@ def gemv_case(fmt, k, n, rows=1, launches=0, peak_gbs=None):
     gbs = alg / us / 1e3
     tail = f" ({gbs / peak_gbs * 100:.1f}% of {peak_gbs:.0f})" if peak_gbs else ""
     print(f"gemv {'Q4' if fmt == FMT_Q4 else 'Q8'} m={rows} {k}x{n}: {nbytes / 1e6:.2f} MB packed, {us:.2f} us/launch, "
-          f"{gbs:.1f} GB/s{tail}  [{copies} weight copies, {per_graph} launches per graph]")
+          f"{gbs:.1f} GB/s{tail}  [{'hot: ' if hot else ''}{copies} weight cop{'y' if copies == 1 else 'ies'}, {per_graph} launches per graph]")
     return gbs
 
 
@@ -114,6 +116,7 @@ def main():
     ap.add_argument("--launches", type=int, default=0)
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--peak-gbs", type=float, default=None)
+    ap.add_argument("--hot", action="store_true", help="one weight copy: the L2-resident regime for small shapes")
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--context", type=int, default=2048)
@@ -132,10 +135,10 @@ def main():
     del warm
     if args.kind == "sweep":
         for k, n in SMOLLM2_SHAPES:
-            gemv_case(fmt, k, n, peak_gbs=args.peak_gbs)
+            gemv_case(fmt, k, n, peak_gbs=args.peak_gbs, hot=args.hot)
     elif args.kind == "gemv":
         k, n = (int(v) for v in args.shape.split("x"))
-        gemv_case(fmt, k, n, rows=args.rows, launches=args.launches, peak_gbs=args.peak_gbs)
+        gemv_case(fmt, k, n, rows=args.rows, launches=args.launches, peak_gbs=args.peak_gbs, hot=args.hot)
     else:
         m, k, n = (int(v) for v in args.shape.split("x"))
         gemm_case(fmt, m, k, n, launches=args.launches)

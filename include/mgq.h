@@ -112,6 +112,13 @@ int mgq_buffer_download(const void *dev, void *host, size_t bytes, void *stream)
 int mgq_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
              uint32_t m, uint32_t k, uint32_t n, void *stream);
 
+/* GEMV over f16 weights (WeightFormat::F16): y = x . W (+ addend), W row-major [k, n] binary16 as
+ * the reference stores parameter_f16 weights, f32 accumulation -- the reference's f16 variant of
+ * matmul_gemv.wgsl (src/codegen.rs:1065-1101).  1 <= m <= MGQ_GEMV_MAX_M, n % 8 == 0, W 16-byte
+ * aligned.  mgq_convert_f16 is the host conversion (round to nearest even, like half::f16::from_f32). */
+int mgq_gemv_f16(const float *x, const void *w_f16, const float *addend, float *y, uint32_t m, uint32_t k, uint32_t n, void *stream);
+int mgq_convert_f16(const float *src, size_t len, uint16_t *dst);
+
 /* GEMVs that compute their activations while loading them (no reference counterpart: the reference
  * runs SwiGLU / RmsNorm as dispatches of their own, src/compile.rs:1814-1830 and Op::RmsNorm):
  *   mgq_gemv_swiglu:    y = (silu(gate) * up) . dequant(w) (+ addend)        gate, up: [m, k]
@@ -317,6 +324,9 @@ int mgq_graph_input(mgq_graph *g, const char *name, const size_t *shape, size_t 
 int mgq_graph_parameter(mgq_graph *g, const char *name, const size_t *shape, size_t rank);
 int mgq_graph_parameter_q4(mgq_graph *g, const char *name, const size_t *shape, size_t rank);
 int mgq_graph_parameter_q8(mgq_graph *g, const char *name, const size_t *shape, size_t rank);
+/* Graph::parameter_f16 (src/graph.rs:739-748): a [K, N] weight kept as row-major binary16; usable as the
+ * right operand of a matmul with at most MGQ_GEMV_MAX_M rows and N % 8 == 0. */
+int mgq_graph_parameter_f16(mgq_graph *g, const char *name, const size_t *shape, size_t rank);
 int mgq_graph_matmul(mgq_graph *g, int a, int b);
 int mgq_graph_add(mgq_graph *g, int a, int b);
 /* decode-step nodes: Graph::{input_u32, embedding, rms_norm, rope_dynamic_offset, cache_write,

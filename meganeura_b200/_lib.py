@@ -60,6 +60,9 @@ SIGNATURES = {
     "mgq_buffer_download": (_int, [_vp, _vp, _sz, _vp]),
     "mgq_device_status": (_int, []),
     "mgq_gemv": (_int, [_int, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
+    "mgq_gemv_f16": (_int, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
+    "mgq_convert_f16": (_int, [_vp, _sz, _vp]),
+    "mgq_graph_parameter_f16": (_int, [_vp, ctypes.c_char_p, _szp, _sz]),
     "mgq_gemv_swiglu": (_int, [_int, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_gemv_rms_norm": (_int, [_int, _vp, _vp, ctypes.c_float, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_gemv_fusable": (_int, [_vp, _u32, _u32]),

@@ -159,6 +159,14 @@ int mgq_argmax(const float *logits, uint32_t n, void *workspace, uint32_t *out_t
 
 int mgq_gemv_lookahead(const void *next_w, size_t next_bytes) { return set_gemv_lookahead(next_w, next_bytes); }
 
+int mgq_gemv_f16(const float *x, const void *w_f16, const float *addend, float *y, uint32_t m, uint32_t k, uint32_t n, void *stream)
+{
+    if (!x || !w_f16 || !y) return fail(MGQ_ERR_NULL, "null operand pointer");
+    if (m == 0 || k == 0 || n == 0) return fail(MGQ_ERR_SHAPE, "empty matmul %ux%ux%u", m, k, n);
+    if (m > MGQ_GEMV_MAX_M) return fail(MGQ_ERR_SHAPE, "gemv takes at most %d rows, got %u", MGQ_GEMV_MAX_M, m);
+    return launch_gemv_f16(x, w_f16, addend, y, m, k, n, stream);
+}
+
 int mgq_gemv_swiglu(int fmt, const float *gate, const float *up, const void *w, const float *addend, float *y,
                     uint32_t m, uint32_t k, uint32_t n, void *stream)
 {

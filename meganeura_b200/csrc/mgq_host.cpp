@@ -219,3 +219,12 @@ int mgq_shard_columns(int fmt, const uint8_t *packed, size_t k, size_t n, size_t
 }
 
 }  // extern "C"
+
+// f32 -> binary16 with the `half` crate's rounding (IEEE round to nearest even), what the reference
+// stores for parameter_f16 weights (src/runtime.rs:2335).
+extern "C" int mgq_convert_f16(const float *src, size_t len, uint16_t *dst)
+{
+    if (!src || !dst) return mgq::fail(MGQ_ERR_NULL, "null pointer");
+    for (size_t i = 0; i < len; i++) dst[i] = f16_from_f32(src[i]);
+    return MGQ_OK;
+}

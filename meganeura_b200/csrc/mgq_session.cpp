@@ -169,6 +169,13 @@ struct mgq_session {
 
 using mgq::fail;
 
+// Bytes of a node's buffer: packed blocks for Q4/Q8, 2 per element for f16 weights, else 4.
+static size_t node_bytes(const Node &nd)
+{
+    if (mgq::is_quant(nd.dtype)) return mgq_packed_bytes(nd.dtype, nd.shape[0], nd.shape[1]);
+    return nd.elements() * (nd.dtype == MGQ_FMT_F16 ? 2 : 4);
+}
+
 static int add_leaf(mgq_graph *g, Op op, const char *name, const size_t *shape, size_t rank, int dtype)
 {
     if (!g || !name || !shape) return -fail(MGQ_ERR_NULL, "null argument");
@@ -206,6 +213,8 @@ int mgq_graph_parameter_q4(mgq_graph *g, const char *name, const size_t *shape, 
 { return add_leaf(g, Op::Parameter, name, shape, rank, MGQ_FMT_Q4); }
 int mgq_graph_parameter_q8(mgq_graph *g, const char *name, const size_t *shape, size_t rank)
 { return add_leaf(g, Op::Parameter, name, shape, rank, MGQ_FMT_Q8); }
+int mgq_graph_parameter_f16(mgq_graph *g, const char *name, const size_t *shape, size_t rank)
+{ return add_leaf(g, Op::Parameter, name, shape, rank, MGQ_FMT_F16); }
 
 int mgq_graph_matmul(mgq_graph *g, int a, int b)
 {
@@ -478,7 +487,7 @@ void merge_input_transforms(mgq_session *s)
         const Dispatch &p = ds[i];
         Dispatch &d = ds[i + 1];
         if (d.shader != MGQ_SHADER_MATMUL_GEMV && d.shader != MGQ_SHADER_MATMUL_GEMV_ADD) continue;
-        if (d.xform || d.params[0] != 1 || d.in[0] != p.out) continue;
+        if (d.xform || d.params[0] != 1 || d.in[0] != p.out || !mgq::is_quant(d.weight_format)) continue;
         int xform = 0;
         if (p.shader == MGQ_SHADER_RMS_NORM && p.params[0] == 1) xform = 2;
         if ((p.shader == MGQ_SHADER_SWIGLU || p.shader == MGQ_SHADER_SWIGLU_CONCAT) && p.in[1] >= 0 && p.params[0] == p.params[1]) xform = 1;
@@ -541,7 +550,7 @@ int mgq_build_inference_session(const mgq_graph *g, mgq_session **out)
             continue;
         }
         Buffer buf;
-        buf.bytes = mgq::is_quant(nd.dtype) ? mgq_packed_bytes(nd.dtype, nd.shape[0], nd.shape[1]) : nd.elements() * 4;
+        buf.bytes = node_bytes(nd);
         s->node_buffer[id] = (int)s->buffers.size();
         s->buffers.push_back(buf);
     }
@@ -568,12 +577,17 @@ int mgq_build_inference_session(const mgq_graph *g, mgq_session **out)
             case Op::MatMul:
             case Op::FusedMatMulAdd: {
                 const Node &na = s->nodes[nd.inputs[0]], &nb = s->nodes[nd.inputs[1]];
-                if (nb.op != Op::Parameter || !mgq::is_quant(nb.dtype)) {
+                const bool f16w = nb.op == Op::Parameter && nb.dtype == MGQ_FMT_F16;
+                if (nb.op != Op::Parameter || !(mgq::is_quant(nb.dtype) || f16w)) {
                     mgq_session_free(s);
-                    return fail(MGQ_ERR_FORMAT, "matmul weight must be a parameter_q4 / parameter_q8 node (f32/f16 weights are outside this library)");
+                    return fail(MGQ_ERR_FORMAT, "matmul weight must be a parameter_q4 / parameter_q8 / parameter_f16 node (f32 weights are outside this library)");
                 }
                 const bool fused = nd.op == Op::FusedMatMulAdd;
                 const uint32_t m = (uint32_t)na.shape[0], k = (uint32_t)na.shape[1], n = (uint32_t)nb.shape[1];
+                if (f16w && (m > MGQ_GEMV_MAX_M || n % 8 != 0)) {
+                    mgq_session_free(s);
+                    return fail(MGQ_ERR_SHAPE, "f16 weights: at most %d rows and N %% 8 == 0 (got %ux%ux%u)", MGQ_GEMV_MAX_M, m, k, n);
+                }
                 if (m == 1 && n % 4 == 0) {
                     d.shader = fused ? MGQ_SHADER_MATMUL_GEMV_ADD : MGQ_SHADER_MATMUL_GEMV;
                     d.workgroups[0] = n / 4;
@@ -719,7 +733,7 @@ static int download_param(mgq_session *s, int id, std::vector<uint8_t> &out)
 {
     const Node &nd = s->nodes[id];
     if (!mgq::is_quant(nd.dtype)) {
-        out.resize(nd.elements() * 4);
+        out.resize(node_bytes(nd));
         return mgq_buffer_download(s->ptr(id), out.data(), out.size(), s->stream);
     }
     out.resize(mgq_packed_bytes(nd.dtype, nd.shape[0], nd.shape[1]));
@@ -759,7 +773,7 @@ int mgq_session_save_checkpoint(mgq_session *s, const char *path)
     size_t offset = 0;
     for (const auto &kv : params) {
         const Node &nd = s->nodes[kv.second];
-        const size_t bytes = mgq::is_quant(nd.dtype) ? mgq_packed_bytes(nd.dtype, nd.shape[0], nd.shape[1]) : nd.elements() * 4;
+        const size_t bytes = node_bytes(nd);
         std::string key;
         for (char c : kv.first) { if (c == '"' || c == '\\') key += '\\'; key += c; }
         char item[160];
@@ -811,7 +825,7 @@ int mgq_session_load_checkpoint(mgq_session *s, const char *path)
         if (off == std::string::npos || off > end) { std::fclose(f); return fail(MGQ_ERR_FORMAT, "%s: entry of '%s' has no data_offsets", path, nd.name.c_str()); }
         unsigned long long b = 0, e = 0;
         if (std::sscanf(header.c_str() + off + 16, "%llu,%llu", &b, &e) != 2 || e < b) { std::fclose(f); return fail(MGQ_ERR_FORMAT, "%s: bad offsets for '%s'", path, nd.name.c_str()); }
-        const size_t want = mgq::is_quant(nd.dtype) ? mgq_packed_bytes(nd.dtype, nd.shape[0], nd.shape[1]) : nd.elements() * 4;
+        const size_t want = node_bytes(nd);
         if (e - b != want) { std::fclose(f); return fail(MGQ_ERR_SIZE, "%s: '%s' holds %llu bytes, the session needs %zu", path, nd.name.c_str(), e - b, want); }
         bytes.resize(want);
         if (std::fseek(f, (long)(8 + hlen + b), SEEK_SET) != 0 || std::fread(bytes.data(), 1, want, f) != want) { std::fclose(f); return fail(MGQ_ERR_FORMAT, "%s: truncated data for '%s'", path, nd.name.c_str()); }
@@ -831,6 +845,11 @@ int mgq_session_set_parameter(mgq_session *s, const char *name, const float *dat
     if (id < 0) return fail(MGQ_ERR_NAME, "unknown parameter: %s", name);
     const Node &nd = s->nodes[id];
     if (len != nd.elements()) return fail(MGQ_ERR_SIZE, "parameter '%s' has %zu elements, got %zu", name, nd.elements(), len);
+    if (nd.dtype == MGQ_FMT_F16) {                       // the reference converts with half::f16::from_f32 (src/runtime.rs:2335)
+        s->staging.resize(len * 2);
+        if (int rc = mgq_convert_f16(data, len, reinterpret_cast<uint16_t *>(s->staging.data()))) return rc;
+        return mgq_buffer_upload(s->ptr(id), s->staging.data(), len * 2, s->stream);
+    }
     if (!mgq::is_quant(nd.dtype)) return mgq_buffer_upload(s->ptr(id), data, len * 4, s->stream);
     s->staging.resize(mgq_packed_bytes(nd.dtype, nd.shape[0], nd.shape[1]));
     const int rc = nd.dtype == MGQ_FMT_Q4 ? mgq_quantize_q4(data, nd.shape[0], nd.shape[1], s->staging.data())
@@ -846,7 +865,7 @@ int mgq_session_upload_param(mgq_session *s, const char *name, const void *bytes
     if (id < 0) return fail(MGQ_ERR_NAME, "unknown parameter: %s", name);
     const Node &nd = s->nodes[id];
     if (mgq::is_quant(nd.dtype)) return upload_packed(s, id, static_cast<const uint8_t *>(bytes), nbytes);
-    if (nbytes != nd.elements() * 4) return fail(MGQ_ERR_SIZE, "parameter '%s' buffer is %zu bytes, got %zu", name, nd.elements() * 4, nbytes);
+    if (nbytes != node_bytes(nd)) return fail(MGQ_ERR_SIZE, "parameter '%s' buffer is %zu bytes, got %zu", name, node_bytes(nd), nbytes);
     return mgq_buffer_upload(s->ptr(id), bytes, nbytes, s->stream);
 }
 
@@ -896,6 +915,8 @@ static int run_dispatch(mgq_session *s, const Dispatch &d)
             return mgq_swiglu(f(0), f(0) + d.params[1], outp, d.params[0] / d.params[1], d.params[1], d.params[2], s->stream);
         default: {
             const float *addend = d.in[2] >= 0 ? f(2) : nullptr;
+            if (d.weight_format == MGQ_FMT_F16)
+                return mgq_gemv_f16(f(0), s->ptr(d.in[1]), addend, outp, d.params[0], d.params[1], d.params[2], s->stream);
             if (d.xform == 1)
                 return mgq_gemv_swiglu(d.weight_format, f(0), f(3), s->ptr(d.in[1]), addend, outp, d.params[0], d.params[1], d.params[2], s->stream);
             if (d.xform == 2)

@@ -85,6 +85,9 @@ class Graph:
     def parameter_q8(self, name: str, shape) -> int:
         return _node(lib.mgq_graph_parameter_q8(self._h, name.encode(), *_shape(shape)))
 
+    def parameter_f16(self, name: str, shape) -> int:
+        return _node(lib.mgq_graph_parameter_f16(self._h, name.encode(), *_shape(shape)))
+
     def matmul(self, a: int, b: int) -> int:
         return _node(lib.mgq_graph_matmul(self._h, a, b))
 

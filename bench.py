@@ -310,6 +310,12 @@ def main():
         sampler.start()
     ms_dev = timed(chain.step, args.steps, args.warmup)
     ms_e2e = timed(chain.step_host, args.steps, args.warmup)
+    # nvidia-smi delivers a sample every 100 ms and the timed regions last tens of milliseconds: keep
+    # replaying the same step for ~0.6 s more (same count on every rank) so that the clock record
+    # holds several samples under this load
+    for _ in range(max(1, min(2000, int(0.6 / max(1e-6, ms_dev / args.steps * 1e-3))))):
+        chain.step()
+    torch.cuda.synchronize()
     clocks = sampler.stop() if sampler else None
     if chain.peer is not None and chain.peer.error():
         raise SystemExit("a bounded wait of the peer exchange ran out (MGQ_ERR_TIMEOUT): results are invalid")

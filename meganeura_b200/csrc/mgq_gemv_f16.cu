@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(kF16Threads) gemv_f16_kernel(const float *x, c
     if (live) {
         const uint4 *wp = reinterpret_cast<const uint4 *>(w + (size_t)slice * n + col0);
         const size_t step = (size_t)SLICES * n / 8;                     // uint4 elements between this thread's rows
-#pragma unroll 4
+#pragma unroll 8
         for (uint32_t kk = slice; kk < k; kk += SLICES, wp += step) {
             const uint4 q = __ldg(wp);
             const __half2 *h = reinterpret_cast<const __half2 *>(&q);
@@ -88,12 +88,13 @@ int launch_gemv_f16(const float *x, const void *w, const float *addend, float *y
     MGQ_CUDA(cudaGetDevice(&dev));
     MGQ_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    // wide tiles (64 columns, 128-byte row segments) when there are enough of them to fill the GPU
-    const bool wide = (n + 63) / 64 >= 2u * (uint32_t)sms;
+    // 64-column tiles (128-byte row segments) when there are enough of them to give every SM a couple
+    // of CTAs, else 32-column tiles (256-column tiles measured slower: 514 vs 396 us on 4096x151936)
+    const int lanes = (n + 63) / 64 >= 2u * (uint32_t)sms ? 8 : 4;
     for (uint32_t r0 = 0; r0 < m; r0 += kF16Rows) {
         const uint32_t rows = m - r0 < (uint32_t)kF16Rows ? m - r0 : (uint32_t)kF16Rows;
         cudaLaunchConfig_t lc{};
-        lc.gridDim = dim3(wide ? (n + 63) / 64 : (n + 31) / 32, 1, 1);
+        lc.gridDim = dim3((n + lanes * 8 - 1) / (lanes * 8), 1, 1);
         lc.blockDim = dim3(kF16Threads, 1, 1);
         lc.stream = stream;
         cudaLaunchAttribute attr[1];
@@ -105,8 +106,8 @@ int launch_gemv_f16(const float *x, const void *w, const float *addend, float *y
         const float *ar = addend ? addend + (size_t)r0 * n : nullptr;
         float *yr = y + (size_t)r0 * n;
         const __half *wh = static_cast<const __half *>(w);
-        if (wide) MGQ_CUDA(cudaLaunchKernelEx(&lc, gemv_f16_kernel<8>, xr, wh, ar, yr, rows, k, n));
-        else      MGQ_CUDA(cudaLaunchKernelEx(&lc, gemv_f16_kernel<4>, xr, wh, ar, yr, rows, k, n));
+        if (lanes == 8) MGQ_CUDA(cudaLaunchKernelEx(&lc, gemv_f16_kernel<8>, xr, wh, ar, yr, rows, k, n));
+        else            MGQ_CUDA(cudaLaunchKernelEx(&lc, gemv_f16_kernel<4>, xr, wh, ar, yr, rows, k, n));
     }
     return MGQ_OK;
 }

@@ -10,7 +10,7 @@ from gpu_util import to_dev
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("m,k,n", [(1, 576, 1536), (1, 4096, 4096), (2, 1536, 576), (5, 576, 49152), (1, 100, 8), (16, 320, 264)])
+@pytest.mark.parametrize("m,k,n", [(1, 576, 1536), (1, 4096, 4096), (2, 1536, 576), (5, 576, 49152), (2, 320, 100000), (1, 100, 8), (16, 320, 264)])
 def test_gemv_f16_matches_numpy(m, k, n):
     import torch
     from meganeura_b200._lib import check, lib

@@ -66,7 +66,7 @@ class _SelfExchange:
 
 
 @pytest.mark.parametrize("fmt", [O.FMT_Q4, O.FMT_Q8])
-@pytest.mark.parametrize("dims", [(1024, 2048, 1536), (576, 1536, 576), (4096, 3072, 4096)])
+@pytest.mark.parametrize("dims", [(1024, 2048, 1536), (576, 1536, 576), (4096, 3072, 4096), (4096, 512, 768), (12288, 512, 18992)])
 def test_chained_gemvs_through_gathered_vectors(fmt, dims):
     """op0 pushes its output; op1 waits for it and takes its activations from the gathered vector;
     op1's own output is pushed too and closes the step.  Two steps in a row: stamps only grow."""

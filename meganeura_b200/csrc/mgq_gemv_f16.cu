@@ -88,9 +88,10 @@ int launch_gemv_f16(const float *x, const void *w, const float *addend, float *y
     MGQ_CUDA(cudaGetDevice(&dev));
     MGQ_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    // 64-column tiles (128-byte row segments) when there are enough of them to give every SM a couple
-    // of CTAs, else 32-column tiles (256-column tiles measured slower: 514 vs 396 us on 4096x151936)
-    const int lanes = (n + 63) / 64 >= 2u * (uint32_t)sms ? 8 : 4;
+    // Narrow column tiles win: 32 columns (64-byte row segments, 64 K-slices per CTA) measured 329 us
+    // on 4096x151936 against 351 / 373 / 514 us for 64 / 128 / 256 columns; 16 columns when even that
+    // gives an SM fewer than eight CTAs (4096x24576: 62 vs 72 us, 4096x4096: 20 vs 35 us).
+    const int lanes = (n + 31) / 32 >= 8u * (uint32_t)sms ? 4 : 2;
     for (uint32_t r0 = 0; r0 < m; r0 += kF16Rows) {
         const uint32_t rows = m - r0 < (uint32_t)kF16Rows ? m - r0 : (uint32_t)kF16Rows;
         cudaLaunchConfig_t lc{};
@@ -106,7 +107,7 @@ int launch_gemv_f16(const float *x, const void *w, const float *addend, float *y
         const float *ar = addend ? addend + (size_t)r0 * n : nullptr;
         float *yr = y + (size_t)r0 * n;
         const __half *wh = static_cast<const __half *>(w);
-        if (lanes == 8) MGQ_CUDA(cudaLaunchKernelEx(&lc, gemv_f16_kernel<8>, xr, wh, ar, yr, rows, k, n));
+        if (lanes == 2) MGQ_CUDA(cudaLaunchKernelEx(&lc, gemv_f16_kernel<2>, xr, wh, ar, yr, rows, k, n));
         else            MGQ_CUDA(cudaLaunchKernelEx(&lc, gemv_f16_kernel<4>, xr, wh, ar, yr, rows, k, n));
     }
     return MGQ_OK;

@@ -61,18 +61,17 @@ const char *mgq_version(void);
  *   "gemv.ctas_per_sm"          CTAs per SM a GEMV grid is sized for (default 3)
  *   "gemv.batch_mma"            1 (default): 3..16 rows run on the integer tensor-core kernel that reads
  *                               the weights once per 8 rows; 0: two rows at a time on the streaming kernels
- *   "gemv.lookahead_bytes"      most bytes of the following GEMV's weights that a GEMV asks L2 to
- *                               fetch (mgq_gemv_lookahead); 0 = look-ahead off (the default)
- *   "plan.columns_per_thread"   1, 2 or 4 for plans created afterwards (default 2: two CTAs per SM)
+ *   "gemv.wait_us"              time limit of the stamp polls of mgq_gemv_exchange / mgq_exchange_finish
+ *                               (default 20000)
+ *   "plan.consumer_threads"     512 or 768 consumer threads per CTA for plans created afterwards (default 768)
+ *   "plan.window_tiles"         ring tiles the producer keeps in flight (default: about 64 KB per SM)
+ *   "plan.tile_kb"              target size of a ring tile in KB (default 16)
+ *   "plan.deadline_us"          time limit of every wait inside the plan kernel (default 20000)
  *   "gemm.force_tiled"          1: never use the tcgen05 kernel (CUDA-core tiled kernel only)
  *   "session.horizontal_fusion" sessions built afterwards merge single-row matmuls that read the same
  *                               activation into one GEMV over the concatenated weight: 0 never,
  *                               1 gate|up under a SwiGLU only (the reference's rule,
  *                               src/optimize.rs:776-879), 2 every such group, e.g. q|k|v (default)
- *   "session.fuse_input"        1: a single-row RmsNorm / SwiGLU consumed only by the next GEMV is
- *                               computed inside that GEMV (mgq_gemv_rms_norm / _swiglu); 0 (default):
- *                               separate launches, measured faster (2.95 vs 3.17 ms per token on the
- *                               Qwen3-8B shape: the transform lengthens every CTA's start-up)
  *   "session.fuse_rope_cache"   1 (default): RoPE(q), RoPE(k), CacheWrite(k), CacheWrite(v) of a decode
  *                               layer run as one launch; 0: four dispatches like the reference */
 int mgq_set_option(const char *name, long value);
@@ -119,30 +118,6 @@ int mgq_gemv(int fmt, const float *x, const void *w, const float *addend, float 
 int mgq_gemv_f16(const float *x, const void *w_f16, const float *addend, float *y, uint32_t m, uint32_t k, uint32_t n, void *stream);
 int mgq_convert_f16(const float *src, size_t len, uint16_t *dst);
 
-/* GEMVs that compute their activations while loading them (no reference counterpart: the reference
- * runs SwiGLU / RmsNorm as dispatches of their own, src/compile.rs:1814-1830 and Op::RmsNorm):
- *   mgq_gemv_swiglu:    y = (silu(gate) * up) . dequant(w) (+ addend)        gate, up: [m, k]
- *   mgq_gemv_rms_norm:  y = (x * rsqrt(mean(x^2) + eps) * norm_weight) . dequant(w) (+ addend)
- * Same results as the separate operator followed by mgq_gemv up to f32 summation order.  m <= 2,
- * and only shapes the streaming kernels take: mgq_gemv_fusable(x, k, n) != 0 (256 <= k <= 32768, k*n/32 a multiple of 4, x 16-byte aligned); otherwise MGQ_ERR_SHAPE. */
-int mgq_gemv_swiglu(int fmt, const float *gate, const float *up, const void *w, const float *addend, float *y,
-                    uint32_t m, uint32_t k, uint32_t n, void *stream);
-int mgq_gemv_rms_norm(int fmt, const float *x, const float *norm_weight, float eps, const void *w, const float *addend, float *y,
-                      uint32_t m, uint32_t k, uint32_t n, void *stream);
-int mgq_gemv_fusable(const void *x, uint32_t k, uint32_t n);
-
-/* Look-ahead for chains of dependent GEMVs (no reference counterpart: the reference records its
- * dispatches into one command encoder and leaves overlap to the driver, src/runtime.rs:2860-2878).
- * Names the packed weights that the GEMV AFTER the next one will read.  The next mgq_gemv /
- * mgq_gemv_exchange / mgq_matmul (m <= MGQ_GEMV_MAX_M) issued by the calling host thread then also
- * asks L2 to start fetching up to "gemv.lookahead_bytes" of them, so HBM keeps streaming while
- * the chain waits on its own dependencies.  Off unless that option is set: on B200 the decode
- * chain is bound by per-kernel latency and instruction issue, and look-ahead measured within
- * +-2 % of no look-ahead.  The hint is consumed by that one call.
- * It only moves data into L2 earlier; results do not change.  next_w must be 16-byte aligned and
- * next_bytes readable device memory; NULL clears a pending hint. */
-int mgq_gemv_lookahead(const void *next_w, size_t next_bytes);
-
 /* ---- column-sharded GEMV with a fused all-gather over peer memory (no reference counterpart: the
  * reference is single-device, src/runtime.rs:1513-1531).
  *
@@ -152,10 +127,15 @@ int mgq_gemv_lookahead(const void *next_w, size_t next_bytes);
  * memory).  An element travels as one 8-byte {value, stamp} pair, stamp = *epoch + 1, written by a
  * single 64-bit store, so data and validity arrive together and no fence, counter or atomic is
  * needed.  With `wait_vec` set (the local gathered vector of length k that this GEMV consumes),
- * every thread first polls -- with an iteration limit, after which *error is raised -- the stamps
- * of the 32 elements of its block.  mgq_exchange_finish ends a token: it polls all `length` stamps
+ * every thread first polls -- with a time limit ("gemv.wait_us"), after which *error is raised --
+ * the stamps of the 32 elements of its block.  mgq_exchange_finish ends a token: it polls all `length` stamps
  * of the last gathered vector and then increments *epoch.  Stamps only grow; nothing is reset
  * between tokens, so a token can be replayed from a CUDA graph.  m = 1 only.
+ * Reuse rule: a gathered vector may be pushed again (next token) only after every rank's consumers
+ * of it have finished.  mgq_exchange_finish on one rank says nothing about the other ranks' readers;
+ * a token of three or more exchanging ops satisfies the rule by construction (a rank can finish the
+ * token only after every rank has pushed the last op, which each rank does after consuming all the
+ * vectors before it); a shorter chain needs a host-side barrier between tokens.
  * x may be NULL when wait_vec is set: the GEMV then takes its activations from the gathered vector
  * itself (the values it has just found valid), which is how a sharded model chains its layers.  A
  * non-NULL x must be data of this GPU's own stream (it is read through the read-only cache). */
@@ -202,7 +182,9 @@ int mgq_device_status(void);
  *                       pitch = 2*half_n       src/shaders/swiglu_concat.wgsl, binary.wgsl (swiglu)
  * mgq_cached_attention: one query token over cache rows 0..*kv_pos, grouped-query heads, scale
  *                       1/sqrt(head_dim), softmax in f32; head_dim 64 or 128 (the reference's
- *                       shader is fixed at 64), at most 8 query heads per KV head.  `workspace`
+ *                       shader is fixed at 64), at most 8 query heads per KV head, max_seq at
+ *                       most 4096 rows (MGQ_ERR_SHAPE beyond; a session checks it when it is
+ *                       built).  `workspace`
  *                       is mgq_cached_attention_workspace(...) bytes of zero-initialised device
  *                       memory owned by the caller (split-context partials and counters; it
  *                       returns to its initial state).  Calls that share a workspace must be
@@ -243,13 +225,22 @@ int mgq_matmul(int fmt, const void *a, int a_dtype, const void *w, const float *
 int mgq_matmul_host(int fmt, const void *a_host, int a_dtype, const void *w_dev, const float *addend_host,
                     float *c_host, uint32_t m, uint32_t k, uint32_t n);
 
-/* ---- plan kernel: a static list of single-row GEMVs run by ONE persistent cooperative launch.
- * Stands in for Session::step replaying ExecutionPlan.dispatches in barrier groups inside one
- * submission (src/runtime.rs:2843-2959; barrier groups 1202-1256).  The weight pipeline runs
- * across op boundaries; op i starts reading its activations only after ops [0, wait_for) have
- * completed on every CTA (wait_for = 0: no dependency; wait_for = i: depends on the op before it).
+/* ---- plan kernel: a static list of single-row GEMVs run by ONE persistent cooperative launch
+ * (one CTA per SM).  Stands in for Session::step replaying ExecutionPlan.dispatches in barrier
+ * groups inside one submission (src/runtime.rs:2843-2959; barrier groups 1202-1256).  A producer
+ * thread per CTA streams the packed weights of all ops through a shared-memory ring with bulk
+ * copies and runs ahead across op boundaries; op i starts reading its activations only after
+ * ops [0, wait_for) have completed (wait_for = 0: no dependency; wait_for = i: depends on the op
+ * before it).  When x is a range of the output y of an earlier op that is waited for, the plan
+ * moves those values between the two ops as {value, stamp} elements of a vector it owns, and the
+ * consumer waits per 32-element block instead of for whole ops; any other x is read as a plain
+ * vector once every CTA has counted itself out of op wait_for - 1.  y always receives the plain
+ * result.  An addend must be complete before the op that produces this op's activations starts.
  * All pointers are device pointers and must stay valid for the plan's lifetime.
- * Limits: m = 1, 256 <= K <= 12288, K*N/32 a multiple of 4, 16-byte aligned w and x. */
+ * Limits: m = 1, 256 <= K <= 24576 (K/32 a multiple of 4; less otherwise), K*N/32 a multiple
+ * of 4, 16-byte aligned w and x.  Launches of one plan must not overlap.  Every device-side wait
+ * has a time limit ("plan.deadline_us", default 20 ms), after which the launch finishes with
+ * undefined results and mgq_plan_check reports MGQ_ERR_TIMEOUT. */
 typedef struct mgq_plan mgq_plan;
 typedef struct mgq_plan_op {
     int fmt;                 /* MGQ_FMT_Q4 / MGQ_FMT_Q8 */
@@ -264,28 +255,50 @@ typedef struct mgq_plan_op {
 int mgq_plan_create(const mgq_plan_op *ops, size_t count, mgq_plan **out);
 /* Enqueues the whole list as one kernel on `stream` (capturable in a CUDA graph). */
 int mgq_plan_launch(mgq_plan *plan, void *stream);
-/* Synchronises `stream` and returns MGQ_ERR_TIMEOUT if a grid barrier of an earlier launch gave
- * up waiting (every device-side wait is bounded; results of such a launch are undefined). */
+/* Synchronises `stream` and returns MGQ_ERR_TIMEOUT if a wait of an earlier launch gave up
+ * (results of such a launch are undefined; the plan is rearmed). */
 int mgq_plan_check(mgq_plan *plan, void *stream);
-int mgq_plan_info(const mgq_plan *plan, uint32_t *grid, uint32_t *threads, uint32_t *columns_per_thread,
-                  size_t *smem_bytes);
+int mgq_plan_info(const mgq_plan *plan, uint32_t *grid, uint32_t *threads, uint32_t *ring_slots, size_t *smem_bytes);
 void mgq_plan_destroy(mgq_plan *plan);
+
+/* The same kernel with caller-owned gathered vectors: the column-sharded multi-GPU decode step as
+ * one launch per rank (no reference counterpart, like mgq_gemv_exchange whose protocol it uses).
+ * links[i].push_dev (device memory, may be NULL): op i also stores its leading gather_cols columns
+ * as {value, stamp} elements into every listed rank's vector, with plain stores over NVLink.
+ * links[i].wait_vec (may be NULL): op i takes its k activations from this LOCAL gathered vector,
+ * waiting per block for this token's stamps; x and wait_for of the op are then ignored.
+ * `epoch` is the token index (stamp = *epoch + 1) and `error` the timeout flag, both in local
+ * device memory; the launch adds one to *epoch when it ends.  With final_vec set the launch also
+ * waits until all final_len elements of that local vector (normally the last op's) carry this
+ * token's stamp, so that the host may read it after the launch.  A gathered vector may be written
+ * again only after every rank has consumed it: chains of three or more linked ops satisfy this by
+ * construction, because a rank can start the next token only after every rank has contributed to
+ * the last ops of this one. */
+typedef struct mgq_plan_link {
+    const mgq_exchange_push *push_dev;
+    const mgq_exchange_elem *wait_vec;
+} mgq_plan_link;
+int mgq_plan_create_linked(const mgq_plan_op *ops, const mgq_plan_link *links, size_t count, unsigned long long *epoch,
+                           unsigned int *error, const mgq_exchange_elem *final_vec, uint32_t final_len, mgq_plan **out);
 
 /* Allocation-free variant of the plan kernel.  No counterpart in meganeura: the reference's
  * session allocates all its buffers when it is built and has no second, allocation-free way to run.
  *
  * Runs `count` single-row GEMVs (same op rules as mgq_plan_create) as one persistent kernel on
  * `stream` and returns when they have finished (it synchronises the stream; MGQ_ERR_TIMEOUT if a
- * grid barrier gave up).  It never calls cudaMalloc/cudaFree or any allocating routine: the
- * kernel's scratch -- op descriptors, barrier counters, error word -- is a fixed device array of
- * MGQ_STATIC_PLAN_MAX_OPS entries (about 25 KB) that every GPU using the library holds until the
- * process exits.  It is meant for callers that must not allocate on their execution path, e.g. a
+ * wait gave up).  It never calls cudaMalloc/cudaFree or any allocating routine: the kernel's
+ * scratch -- op descriptors, arrival counters, token index, error word -- is a fixed device array
+ * of MGQ_STATIC_PLAN_MAX_OPS entries (about 35 KB) that every GPU using the library holds until
+ * the process exits; dependent ops wait on the arrival counters (no gathered vectors).  It is meant for callers that must not allocate on their execution path, e.g. a
  * serving loop with a fixed device-memory budget or a host application that forbids cudaMalloc after
  * start-up (it can synchronise the device and can fail when memory is tight).
  *
  *   - count > MGQ_STATIC_PLAN_MAX_OPS is rejected with MGQ_ERR_SIZE.
  *   - The first call on each device looks up the array's device address and opts the kernels into
  *     their shared-memory size; make that first call before starting any stream capture.
+ *   - The call copies the descriptors in, launches, reads the error word back and synchronises
+ *     `stream`, so it cannot itself be part of a stream capture (MGQ_ERR_STATE on a capturing
+ *     stream), and `stream` must belong to the device that is current on the calling thread.
  *   - All calls on a device share the one array, and it keeps the previous call's contents; the
  *     entry point rewrites the descriptors and zeroes the counters itself, but two calls that
  *     overlap on the same GPU (different streams or threads) race on it. */
@@ -295,10 +308,11 @@ int mgq_plan_run_static(const mgq_plan_op *ops, size_t count, void *stream);
 /* ---- Graph / Session surface (src/graph.rs:714-795, src/train.rs:380-389,
  *      src/runtime.rs:2327-2345, 2496-2550, 2612-2643, 2786-2791, 2835-2959).
  *
- * Only the nodes on the quantized-matmul path exist: inputs, parameters (f32 vectors are
- * accepted only as addends; matmul weights must be Q4/Q8), matmul and add.  MatMul+Add is
- * fused to FusedMatMulAdd like apply_matmul_add_fusions (src/optimize.rs:724-767) and the
- * plan's dispatches carry the reference's shader names, workgroups, params and labels. */
+ * The nodes of the quantized-matmul path and of a decode step exist: inputs, parameters (matmul
+ * weights must be Q4, Q8 or f16; f32 parameters are addends, norm weights, tables and caches),
+ * matmul, add and the decode-step operators below.  MatMul+Add is fused to FusedMatMulAdd like
+ * apply_matmul_add_fusions (src/optimize.rs:724-767) and the plan's dispatches carry the
+ * reference's shader names, workgroups, params and labels. */
 typedef struct mgq_graph mgq_graph;
 typedef struct mgq_session mgq_session;
 

@@ -63,10 +63,6 @@ SIGNATURES = {
     "mgq_gemv_f16": (_int, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_convert_f16": (_int, [_vp, _sz, _vp]),
     "mgq_graph_parameter_f16": (_int, [_vp, ctypes.c_char_p, _szp, _sz]),
-    "mgq_gemv_swiglu": (_int, [_int, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
-    "mgq_gemv_rms_norm": (_int, [_int, _vp, _vp, ctypes.c_float, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
-    "mgq_gemv_fusable": (_int, [_vp, _u32, _u32]),
-    "mgq_gemv_lookahead": (_int, [_vp, _sz]),
     "mgq_embedding": (_int, [_vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_rms_norm": (_int, [_vp, _vp, _vp, _u32, _u32, ctypes.c_float, _vp]),
     "mgq_rope_dynamic": (_int, [_vp, _vp, _vp, _u32, _u32, _u32, ctypes.c_float, _vp]),
@@ -83,6 +79,7 @@ SIGNATURES = {
     "mgq_matmul": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_matmul_host": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32]),
     "mgq_plan_create": (_int, [_vp, _sz, ctypes.POINTER(_vp)]),
+    "mgq_plan_create_linked": (_int, [_vp, _vp, _sz, _vp, _vp, _vp, _u32, ctypes.POINTER(_vp)]),
     "mgq_plan_launch": (_int, [_vp, _vp]),
     "mgq_plan_check": (_int, [_vp, _vp]),
     "mgq_plan_info": (_int, [_vp, ctypes.POINTER(_u32), ctypes.POINTER(_u32), ctypes.POINTER(_u32), _szp]),
@@ -136,6 +133,11 @@ class PlanOp(ctypes.Structure):
     """mgq_plan_op"""
     _fields_ = [("fmt", ctypes.c_int), ("x", _vp), ("w", _vp), ("addend", _vp), ("y", _vp),
                 ("m", _u32), ("k", _u32), ("n", _u32), ("wait_for", _u32)]
+
+
+class PlanLink(ctypes.Structure):
+    """mgq_plan_link"""
+    _fields_ = [("push_dev", _vp), ("wait_vec", _vp)]
 
 
 class ExchangePush(ctypes.Structure):

@@ -157,8 +157,6 @@ int mgq_argmax(const float *logits, uint32_t n, void *workspace, uint32_t *out_t
     return launch_argmax(logits, n, workspace, out_token, next_token, kv_pos, history, history_cap, stream);
 }
 
-int mgq_gemv_lookahead(const void *next_w, size_t next_bytes) { return set_gemv_lookahead(next_w, next_bytes); }
-
 int mgq_gemv_f16(const float *x, const void *w_f16, const float *addend, float *y, uint32_t m, uint32_t k, uint32_t n, void *stream)
 {
     if (!x || !w_f16 || !y) return fail(MGQ_ERR_NULL, "null operand pointer");
@@ -166,28 +164,6 @@ int mgq_gemv_f16(const float *x, const void *w_f16, const float *addend, float *
     if (m > MGQ_GEMV_MAX_M) return fail(MGQ_ERR_SHAPE, "gemv takes at most %d rows, got %u", MGQ_GEMV_MAX_M, m);
     return launch_gemv_f16(x, w_f16, addend, y, m, k, n, stream);
 }
-
-int mgq_gemv_swiglu(int fmt, const float *gate, const float *up, const void *w, const float *addend, float *y,
-                    uint32_t m, uint32_t k, uint32_t n, void *stream)
-{
-    if (!up) return fail(MGQ_ERR_NULL, "gemv_swiglu: null up operand");
-    if (int rc = check_matmul_args(fmt, gate, w, y, m, k, n)) return rc;
-    if (m > 2) return fail(MGQ_ERR_SHAPE, "gemv_swiglu takes at most 2 rows, got %u", m);
-    GemvInput in{up, 1, 0.f};
-    return launch_gemv(fmt, gate, w, addend, y, m, k, n, stream, nullptr, &in);
-}
-
-int mgq_gemv_rms_norm(int fmt, const float *x, const float *norm_weight, float eps, const void *w, const float *addend, float *y,
-                      uint32_t m, uint32_t k, uint32_t n, void *stream)
-{
-    if (!norm_weight) return fail(MGQ_ERR_NULL, "gemv_rms_norm: null norm weight");
-    if (int rc = check_matmul_args(fmt, x, w, y, m, k, n)) return rc;
-    if (m > 2) return fail(MGQ_ERR_SHAPE, "gemv_rms_norm takes at most 2 rows, got %u", m);
-    GemvInput in{norm_weight, 2, eps};
-    return launch_gemv(fmt, x, w, addend, y, m, k, n, stream, nullptr, &in);
-}
-
-int mgq_gemv_fusable(const void *x, uint32_t k, uint32_t n) { return gemv_streamable(x, k, n) ? 1 : 0; }
 
 int mgq_gemv_exchange(int fmt, const float *x, const void *w, const float *addend, float *y, uint32_t k, uint32_t n,
                       const mgq_exchange_push *push_dev, const mgq_exchange_elem *wait_vec,

@@ -75,7 +75,7 @@ __device__ __forceinline__ CtaRange cta_range(const GemvParams &p)
     return r;
 }
 
-template <int MT, int C, int TS, bool XF = false>      // XF: activations go through a fused transform (GemvParams::xform)
+template <int MT, int C, int TS>
 __global__ void __launch_bounds__(TS) gemv_q4_kernel(const GemvParams p)
 {
     constexpr int STAGES = kStages, ROUND = kStages * C;
@@ -84,7 +84,6 @@ __global__ void __launch_bounds__(TS) gemv_q4_kernel(const GemvParams p)
     uint4 *s_nib = reinterpret_cast<uint4 *>(smem) + t;                                  // [ROUND][TS], own slot
     uint32_t *s_hdr = reinterpret_cast<uint32_t *>(smem + ROUND * TS * 16) + t;          // [ROUND][TS], own slot
     float *s_red = reinterpret_cast<float *>(smem + ROUND * TS * 20);                    // [2][MT][ROUND][TS] (+ [TS])
-    MGQ_STAMP(p, 0);
 
     const CtaRange cr = cta_range(p);
     const uint32_t tt = t < p.active ? t : p.active - 1;
@@ -114,19 +113,16 @@ __global__ void __launch_bounds__(TS) gemv_q4_kernel(const GemvParams p)
     };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) issue(s, std::true_type{});       // weights first: they depend on nothing
-    prefetch_ahead(p);
     grid_launch_dependents();
     grid_dependency_wait();                                                 // x, addend and y belong to earlier kernels
     exchange_poll(p, t % p.bpc);                                            // ... or to other GPUs
-    MGQ_STAMP(p, 1);
 
     XBlock xb[MT];
 #pragma unroll
     for (int r = 0; r < MT; r++) {
         // x is either a local vector (read-only path: the CTAs of an SM share one fetch) or, when the
         // caller passed none, the gathered vector that was just polled (written by other GPUs: L2 only)
-        if (XF)       load_x_fused<1>(p, r, b, t < p.bpc, s_red, xb[r]);
-        else if (p.x) load_x<1, false>(p.x + (size_t)r * p.k, b, xb[r]);
+        if (p.x) load_x<1, false>(p.x + (size_t)r * p.k, b, xb[r]);
         else          load_x_gathered<1>(p.wait_vec, b, xb[r]);
     }
     const ReduceSlot slot = make_slot<ROUND, TS>(p);
@@ -156,7 +152,6 @@ __global__ void __launch_bounds__(TS) gemv_q4_kernel(const GemvParams p)
                 }
             }
         }
-        if (round == 0) MGQ_STAMP(p, 2);
         reduce_store<MT, ROUND, true, TS>(p, slot, s_red + (round & 1) * MT * ROUND * TS, part, cr.g0 + g, cr.g1,
                                           p.push ? s_red + 2 * MT * ROUND * TS : nullptr);
     };
@@ -167,12 +162,11 @@ __global__ void __launch_bounds__(TS) gemv_q4_kernel(const GemvParams p)
     g_next = g + (STAGES - 1) * C;
     for (; g < cr.n_g; g += ROUND, round++) do_round(g, round, std::true_type{});
     cp_async_wait<0>();
-    MGQ_STAMP(p, 3);
 }
 
 // ------------------------------------------------------------------------------------ Q8
 
-template <int MT, int C, int TS, bool XF = false>
+template <int MT, int C, int TS>
 __global__ void __launch_bounds__(TS) gemv_q8_kernel(const GemvParams p)
 {
     constexpr int STAGES = kStages, ROUND = kStages * C;
@@ -180,7 +174,6 @@ __global__ void __launch_bounds__(TS) gemv_q8_kernel(const GemvParams p)
     const uint32_t t = threadIdx.x, lane = t & 31u, warp = t >> 5;
     uint8_t *s_w = smem + warp * (ROUND * kQ8WarpStage);                                 // this warp's ring [ROUND][1152]
     float *s_red = reinterpret_cast<float *>(smem + (TS / 32) * ROUND * kQ8WarpStage);   // [2][MT][ROUND][TS] (+ [TS])
-    MGQ_STAMP(p, 0);
 
     const CtaRange cr = cta_range(p);
     const uint32_t tt = t < p.active ? t : p.active - 1;
@@ -226,17 +219,14 @@ __global__ void __launch_bounds__(TS) gemv_q8_kernel(const GemvParams p)
     };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) issue(s, std::true_type{});
-    prefetch_ahead(p);
     grid_launch_dependents();
     grid_dependency_wait();
     exchange_poll(p, t % p.bpc);
-    MGQ_STAMP(p, 1);
 
     XBlock xb[MT];
 #pragma unroll
     for (int r = 0; r < MT; r++) {
-        if (XF)       load_x_fused<0>(p, r, b, t < p.bpc, s_red, xb[r]);
-        else if (p.x) load_x<0, false>(p.x + (size_t)r * p.k, b, xb[r]);
+        if (p.x) load_x<0, false>(p.x + (size_t)r * p.k, b, xb[r]);
         else          load_x_gathered<0>(p.wait_vec, b, xb[r]);
     }
     const ReduceSlot slot = make_slot<ROUND, TS>(p);
@@ -266,7 +256,6 @@ __global__ void __launch_bounds__(TS) gemv_q8_kernel(const GemvParams p)
                 }
             }
         }
-        if (round == 0) MGQ_STAMP(p, 2);
         reduce_store<MT, ROUND, true, TS>(p, slot, s_red + (round & 1) * MT * ROUND * TS, part, cr.g0 + g, cr.g1,
                                           p.push ? s_red + 2 * MT * ROUND * TS : nullptr);
     };
@@ -276,7 +265,6 @@ __global__ void __launch_bounds__(TS) gemv_q8_kernel(const GemvParams p)
     g_next = g + (STAGES - 1) * C;
     for (; g < cr.n_g; g += ROUND, round++) do_round(g, round, std::true_type{});
     cp_async_wait<0>();
-    MGQ_STAMP(p, 3);
 }
 
 // ------------------------------------------------------------------------------ generic path
@@ -341,16 +329,9 @@ struct Tuning {
     int ctas_per_sm = 0;       // "gemv.ctas_per_sm"
     int serial = -1;           // "gemv.serial_dispatch": 1 turns programmatic dependent launch off
     int batch_mma = 1;          // "gemv.batch_mma": 3..16 rows run on the mma kernel (0: pairs of rows on the streaming kernels)
-    long ahead_cap = 0;         // "gemv.lookahead_bytes": most bytes of the next GEMV's weights requested into L2 (0 = off)
+    long wait_us = 0;           // "gemv.wait_us": time limit of the exchange's stamp polls (0: 20000)
 };
 Tuning g_tuning;
-
-// Set by mgq_gemv_lookahead, consumed by the next GEMV launched from the same host thread.
-struct Lookahead {
-    const uint8_t *w = nullptr;
-    size_t bytes = 0;
-};
-thread_local Lookahead t_lookahead;
 
 // Largest column count per group that fits `threads` and keeps cpi*bpc a multiple of 4
 // (so that a Q8 warp's 36-byte blocks always start on a 16-byte boundary).
@@ -423,32 +404,27 @@ Config choose_config(int fmt, uint32_t bpc, uint32_t n, int mt, int sms)
 
 using KernelFn = void (*)(const GemvParams);
 
-template <int MT, int C, bool XF>
+template <int MT, int C>
 KernelFn pick_by_threads(int fmt, uint32_t threads)
 {
     const bool q4 = fmt == MGQ_FMT_Q4;
     switch (stride_class(threads)) {
-        case 128: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 128, XF> : (KernelFn)gemv_q8_kernel<MT, C, 128, XF>;
-        case 256: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 256, XF> : (KernelFn)gemv_q8_kernel<MT, C, 256, XF>;
-        case 384: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 384, XF> : (KernelFn)gemv_q8_kernel<MT, C, 384, XF>;
-        case 512: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 512, XF> : (KernelFn)gemv_q8_kernel<MT, C, 512, XF>;
+        case 128: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 128> : (KernelFn)gemv_q8_kernel<MT, C, 128>;
+        case 256: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 256> : (KernelFn)gemv_q8_kernel<MT, C, 256>;
+        case 384: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 384> : (KernelFn)gemv_q8_kernel<MT, C, 384>;
+        case 512: return q4 ? (KernelFn)gemv_q4_kernel<MT, C, 512> : (KernelFn)gemv_q8_kernel<MT, C, 512>;
         default: return nullptr;
     }
 }
 
-// Kernels with a fused input transform exist for single rows only (mt == 1).
-KernelFn pick_kernel(int fmt, int mt, const Config &c, bool xf)
+KernelFn pick_kernel(int fmt, int mt, const Config &c)
 {
     if (c.threads > 512) {
-        if (mt != 1 || c.cols_per_thread != 1 || xf) return nullptr;
+        if (mt != 1 || c.cols_per_thread != 1) return nullptr;
         return fmt == MGQ_FMT_Q4 ? (KernelFn)gemv_q4_kernel<1, 1, 1024> : (KernelFn)gemv_q8_kernel<1, 1, 1024>;
     }
-    if (xf) {
-        if (mt != 1) return nullptr;
-        return c.cols_per_thread == 2 ? pick_by_threads<1, 2, true>(fmt, c.threads) : pick_by_threads<1, 1, true>(fmt, c.threads);
-    }
-    if (c.cols_per_thread == 2) return mt == 2 ? pick_by_threads<2, 2, false>(fmt, c.threads) : pick_by_threads<1, 2, false>(fmt, c.threads);
-    return mt == 2 ? pick_by_threads<2, 1, false>(fmt, c.threads) : pick_by_threads<1, 1, false>(fmt, c.threads);
+    if (c.cols_per_thread == 2) return mt == 2 ? pick_by_threads<2, 2>(fmt, c.threads) : pick_by_threads<1, 2>(fmt, c.threads);
+    return mt == 2 ? pick_by_threads<2, 1>(fmt, c.threads) : pick_by_threads<1, 1>(fmt, c.threads);
 }
 
 struct DeviceInfo {
@@ -523,23 +499,9 @@ bool overlap_allowed()
     return allowed;
 }
 
-#ifdef MGQ_GEMV_TRACE
-unsigned long long *g_trace = nullptr;
-#endif
+unsigned long long exchange_wait_ns() { return (unsigned long long)(g_tuning.wait_us > 0 ? g_tuning.wait_us : 20000) * 1000ull; }
 
 }  // namespace
-
-#ifdef MGQ_GEMV_TRACE
-extern "C" void mgq_debug_set_trace(unsigned long long *dev_buffer) { g_trace = dev_buffer; }
-#endif
-
-int set_gemv_lookahead(const void *w, size_t bytes)
-{
-    if (w && reinterpret_cast<uintptr_t>(w) % 16 != 0) return fail(MGQ_ERR_ALIGN, "look-ahead weights must be 16-byte aligned");
-    t_lookahead.w = static_cast<const uint8_t *>(w);
-    t_lookahead.bytes = w ? bytes : 0;
-    return MGQ_OK;
-}
 
 int set_gemv_option(const char *name, long value)
 {
@@ -553,9 +515,9 @@ int set_gemv_option(const char *name, long value)
         g_tuning.serial = value < 0 ? -1 : (value ? 1 : 0);
     } else if (!std::strcmp(name, "gemv.batch_mma")) {
         g_tuning.batch_mma = value ? 1 : 0;
-    } else if (!std::strcmp(name, "gemv.lookahead_bytes")) {
-        if (value < 0 || value > (1l << 30)) return fail(MGQ_ERR_SHAPE, "%s out of range", name);
-        g_tuning.ahead_cap = value;
+    } else if (!std::strcmp(name, "gemv.wait_us")) {
+        if (value < 0 || value > 10000000) return fail(MGQ_ERR_SHAPE, "%s out of range", name);
+        g_tuning.wait_us = value;
     } else {
         return fail(MGQ_ERR_NAME, "unknown option: %s", name);
     }
@@ -565,16 +527,21 @@ int set_gemv_option(const char *name, long value)
 // Ends a token on this GPU: waits (bounded) until every element of the last gathered vector carries
 // this token's stamp, then the block that finishes last advances the local token index.
 __global__ void exchange_finish_kernel(const float2 *last_vec, uint32_t length, unsigned long long *epoch,
-                                       unsigned int *error, unsigned int *blocks_done)
+                                       unsigned int *error, unsigned int *blocks_done, unsigned long long wait_ns)
 {
     const uint32_t stamp = dev::exchange_stamp(epoch);
     if (last_vec) {
         for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < length; i += gridDim.x * blockDim.x) {
+            unsigned long long t0 = 0;
             for (uint32_t spins = 0;; spins++) {
                 uint32_t got;
                 asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(got) : "l"(&last_vec[i].y) : "memory");
                 if (got == stamp) break;
-                if (spins > dev::kExchangeSpinLimit) { atomicExch(error, 1u); break; }
+                if ((spins & 31u) == 31u) {
+                    const unsigned long long now = dev::global_timer_ns();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > wait_ns) { atomicExch(error, 1u); break; }
+                }
             }
         }
     }
@@ -597,7 +564,7 @@ int launch_exchange_finish(const void *last_vec, uint32_t length, unsigned long 
     if (grid > 148) grid = 148;
     if (grid < 1) grid = 1;
     exchange_finish_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream_v)>>>(
-        static_cast<const float2 *>(last_vec), length, epoch, error, blocks_done);
+        static_cast<const float2 *>(last_vec), length, epoch, error, blocks_done, exchange_wait_ns());
     MGQ_CUDA(cudaGetLastError());
     return MGQ_OK;
 }
@@ -609,7 +576,7 @@ bool gemv_streamable(const void *x, uint32_t k, uint32_t n)
 }
 
 int launch_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
-                uint32_t m, uint32_t k, uint32_t n, void *stream_v, const GemvExchange *xchg, const GemvInput *xin)
+                uint32_t m, uint32_t k, uint32_t n, void *stream_v, const GemvExchange *xchg)
 {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
     const uint32_t bpc = k / 32;
@@ -622,22 +589,14 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
         p.wait_vec = static_cast<const float2 *>(xchg->wait_vec);
         p.epoch = xchg->epoch;
         p.xerror = xchg->error;
+        p.wait_ns = exchange_wait_ns();
     }
 
-    const Lookahead ahead = t_lookahead;
-    t_lookahead = Lookahead{};
-    if (!xchg && !(xin && xin->xform) && g_tuning.batch_mma && gemv_mma_eligible(m, k, n, x, w))
+    if (!xchg && g_tuning.batch_mma && gemv_mma_eligible(m, k, n, x, w))
         return launch_gemv_mma(fmt, x, w, addend, y, m, k, n, stream_v);
-    if (xin && xin->xform != 0) {
-        if (reinterpret_cast<uintptr_t>(xin->x2) % 16 != 0) return fail(MGQ_ERR_ALIGN, "the second activation operand must be 16-byte aligned");
-        p.x2 = xin->x2;
-        p.xform = (uint32_t)xin->xform;
-        p.eps = xin->eps;
-    }
     const bool streamable = gemv_streamable(x, k, n);
     if (!streamable) {
         if (xchg) return fail(MGQ_ERR_SHAPE, "this shape has no exchanging GEMV kernel (K=%u N=%u)", k, n);
-        if (p.xform) return fail(MGQ_ERR_SHAPE, "this shape has no GEMV kernel with a fused input transform (K=%u N=%u)", k, n);
         p.x = x; p.addend = addend; p.y = y;
         const uint32_t warps = 8, grid = (n + warps - 1) / warps;
         if (fmt == MGQ_FMT_Q4) gemv_generic_kernel<MGQ_FMT_Q4><<<grid, warps * 32, 0, stream>>>(p, m);
@@ -651,15 +610,15 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
 
     // Rows are processed two at a time (their activations live in registers); more rows re-read W.
     for (uint32_t r0 = 0; r0 < m;) {
-        const int mt = (m - r0 >= 2 && bpc <= 512 && !p.xform) ? 2 : 1;
+        const int mt = (m - r0 >= 2 && bpc <= 512) ? 2 : 1;
         const Config cfg = choose_config(fmt, bpc, n, mt, di.sms);
         p.cpi = cfg.cpi;
         p.active = cfg.cpi * bpc;
         p.red_shift = cfg.red_shift;
         p.red_chunk = cfg.red_chunk;
         p.total_iters = (n + cfg.cpi - 1) / cfg.cpi;
-        KernelFn fn = pick_kernel(fmt, mt, cfg, p.xform != 0);
-        if (!fn) return fail(MGQ_ERR_SHAPE, "no GEMV kernel for K=%u%s", k, p.xform ? " with a fused input transform" : "");
+        KernelFn fn = pick_kernel(fmt, mt, cfg);
+        if (!fn) return fail(MGQ_ERR_SHAPE, "no GEMV kernel for K=%u", k);
         const size_t smem = smem_bytes(fmt, cfg.threads, (int)cfg.cols_per_thread, mt);
         int occ = 0;
         if (int rc = kernel_occupancy(fn, cfg.threads, smem, occ)) return rc;
@@ -671,16 +630,15 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
         if (!g_tuning.ctas_per_sm && stages_total >= 64u * (uint32_t)di.sms * (uint32_t)occ) per_sm = occ;
         if (per_sm > occ) per_sm = occ;
         // wide CTAs (K >= 12288) with only a few stages each: one CTA per SM halves the per-CTA start-up
-        // (activation fetch and preparation) and the partly filled last round (12 layers: 534 vs 545 us)
+        // (activation fetch and preparation) and the partly filled last round
         if (!g_tuning.ctas_per_sm && cfg.threads >= 384 && stages_total < 8u * (uint32_t)di.sms * (uint32_t)per_sm) per_sm = 1;
         uint32_t grid = (uint32_t)di.sms * (uint32_t)per_sm;
         if (grid > stages_total) grid = stages_total;
         // With programmatic dependent launch the CTAs of the next kernel take whatever room is left on
         // an SM while this one still runs; the hardware packs them onto the first SMs that have room,
         // which leaves the other SMs short of work, and co-resident CTAs that only wait were measured
-        // to cost more than their early prefetch gains (12 Qwen3-8B-shaped layers: 547 us with room
-        // for exactly per_sm CTAs, 643 us with room for 2*per_sm).  So the shared-memory request is
-        // padded until exactly per_sm CTAs fit: a successor's CTA starts when one of ours exits.
+        // to cost more than their early prefetch gains.  So the shared-memory request is padded until
+        // exactly per_sm CTAs fit: a successor's CTA starts when one of ours exits.
         size_t launch_smem = smem;
         if (overlap_allowed() && occ > per_sm) {
             const size_t share = di.smem_per_sm / (size_t)per_sm;
@@ -688,20 +646,8 @@ int launch_gemv(int fmt, const float *x, const void *w, const float *addend, flo
             if (launch_smem > di.smem_optin) launch_smem = di.smem_optin;
         }
         p.x = x + (size_t)r0 * k;
-        if (p.xform == kXformSwiglu) p.x2 = xin->x2 + (size_t)r0 * k;          // up has rows like gate; a norm weight has one
         p.addend = addend ? addend + (size_t)r0 * n : nullptr;
         p.y = y + (size_t)r0 * n;
-        p.ahead = nullptr;
-        p.ahead_per_cta = 0;
-        if (ahead.w && r0 + mt >= m && g_tuning.ahead_cap > 0) {          // the last launch of this call looks ahead
-            const size_t want = ahead.bytes < (size_t)g_tuning.ahead_cap ? ahead.bytes : (size_t)g_tuning.ahead_cap;
-            p.ahead = ahead.w;
-            p.ahead_per_cta = (uint32_t)(want / grid / 512u * 512u);
-        }
-#ifdef MGQ_GEMV_TRACE
-        p.trace = g_trace;
-        if (g_trace) g_trace += (size_t)4096 * 4;
-#endif
         cudaLaunchConfig_t lc{};
         lc.gridDim = dim3(grid, 1, 1);
         lc.blockDim = dim3(cfg.threads, 1, 1);

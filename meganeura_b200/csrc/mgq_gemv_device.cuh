@@ -29,16 +29,7 @@ struct GemvParams {
     const float2 *wait_vec;                   // local gathered {value, stamp} vector (length k) that must carry this token's stamps
     const unsigned long long *epoch;          // local token index
     unsigned int *xerror;                     // raised when the bounded wait runs out
-    // activation transform fused into the load (kXform*): x2 is `up` (SwiGLU) or the norm weight (RMSNorm)
-    const float *x2;
-    uint32_t xform;
-    float eps;
-    // look-ahead: packed weights of the GEMV that follows this one in the stream (may be null)
-    const uint8_t *ahead;
-    uint32_t ahead_per_cta;                   // bytes each CTA asks L2 to fetch, a multiple of 512
-#ifdef MGQ_GEMV_TRACE
-    unsigned long long *trace;   // [gridDim.x][4] globaltimer stamps: start, after dependency wait, first block done, end
-#endif
+    unsigned long long wait_ns;               // time limit of the stamp poll
 };
 
 // Fused all-gather of a column-sharded GEMV.  Instead of a collective after the kernel, the lane
@@ -54,7 +45,13 @@ struct ExchangePush {                          // one per exchanging GEMV, in de
     uint32_t reserved;
     float2 *dst[kMaxPeers];                    // rank p's gathered {value, stamp} vector; this rank fills [rank*gather_cols, +gather_cols)
 };
-constexpr uint32_t kExchangeSpinLimit = 1u << 20;
+
+__device__ __forceinline__ unsigned long long global_timer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ uint32_t exchange_stamp(const unsigned long long *epoch)
 {
@@ -78,6 +75,7 @@ __device__ __forceinline__ void exchange_poll(const GemvParams &p, uint32_t b)
     const uint4 *src = together ? reinterpret_cast<const uint4 *>(p.wait_vec + 32u * (b - lane)) + lane
                                 : reinterpret_cast<const uint4 *>(p.wait_vec + 32u * b);
     const uint32_t step = together ? 32u : 1u;
+    unsigned long long t0 = 0;
     for (uint32_t spins = 0;; spins++) {
         uint32_t ok = 1;
 #pragma unroll
@@ -89,25 +87,15 @@ __device__ __forceinline__ void exchange_poll(const GemvParams &p, uint32_t b)
         }
         if (together) ok = __all_sync(0xffffffffu, ok);
         if (ok) break;
-        if (spins > kExchangeSpinLimit) { atomicExch(p.xerror, 1u); break; }
-        // once any thread of the step has given up, the step is lost: later waiters leave at once
-        if ((spins & 1023u) == 1023u && *reinterpret_cast<const volatile uint32_t *>(p.xerror) != 0u) break;
+        if ((spins & 31u) == 31u) {
+            // once any thread of the step has given up, the step is lost: later waiters leave at once
+            if (*reinterpret_cast<const volatile uint32_t *>(p.xerror) != 0u) break;
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > p.wait_ns) { atomicExch(p.xerror, 1u); break; }
+        }
     }
 }
-
-#if defined(MGQ_GEMV_TRACE) || defined(MGQ_PLAN_TRACE)
-__device__ __forceinline__ unsigned long long now_ns()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#endif
-#ifdef MGQ_GEMV_TRACE
-#define MGQ_STAMP(p, slot) do { if ((p).trace && threadIdx.x == 0) (p).trace[blockIdx.x * 4 + (slot)] = now_ns(); } while (0)
-#else
-#define MGQ_STAMP(p, slot) do { } while (0)
-#endif
 
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem)
 {
@@ -132,19 +120,6 @@ __device__ __forceinline__ void cp_async_wait()
 // weights (immutable after upload) are fetched there.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
-
-// A decode step is a chain of dependent GEMVs, and between two of them (dependency release,
-// activation load, reduction) HBM would sit idle.  So each CTA, right after queueing its own first
-// weight stages, asks L2 to start fetching a slice of the NEXT GEMV's packed weights: the request
-// holds no shared memory or registers, HBM keeps streaming through the gaps, and the next kernel
-// finds its weights in L2.  Weights are immutable, so this is legal before the dependency wait.
-__device__ __forceinline__ void prefetch_ahead(const GemvParams &p)
-{
-    if (p.ahead_per_cta == 0 || threadIdx.x >= 32) return;
-    const uint32_t chunk = p.ahead_per_cta >> 5;                                           // per lane, a multiple of 16
-    const uint8_t *src = p.ahead + (size_t)blockIdx.x * p.ahead_per_cta + (size_t)threadIdx.x * chunk;
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(src), "r"(chunk) : "memory");
-}
 
 // dp4a with mixed signedness (a: packed codes, b: packed activation bytes).
 __device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c)
@@ -232,57 +207,6 @@ __device__ __forceinline__ void load_x(const float *xrow, uint32_t b, XBlock &xb
     for (int j = 0; j < 8; j++) {
         const float4 t = COHERENT ? __ldcg(xp + j) : __ldg(xp + j);
         v[4 * j + 0] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
-    }
-    prepare_x<ORDER>(v, xb);
-}
-
-// What a decode graph computes right before a GEMV can be computed while the GEMV loads its
-// activations instead of in a launch of its own (every thread redoes it for its 32 elements):
-//   kXformSwiglu   x = silu(gate) * up                          (gate = p.x, up = p.x2)
-//   kXformRmsNorm  x = x * rsqrt(mean(x^2) + eps) * weight      (weight = p.x2; the mean runs over the
-//                  whole row, so the CTA adds up the squares of one thread per block: one barrier)
-constexpr uint32_t kXformNone = 0, kXformSwiglu = 1, kXformRmsNorm = 2;
-
-template <int ORDER>
-__device__ __forceinline__ void load_x_fused(const GemvParams &p, uint32_t row, uint32_t b, bool first_copy, float *scratch, XBlock &xb)
-{
-    const float4 *xp = reinterpret_cast<const float4 *>(p.x + (size_t)row * p.k + 32u * b);
-    const float4 *wp = reinterpret_cast<const float4 *>(p.x2 + (p.xform == kXformSwiglu ? (size_t)row * p.k : 0) + 32u * b);
-    float v[32];
-#pragma unroll
-    for (int j = 0; j < 8; j++) {
-        const float4 t = __ldg(xp + j);
-        v[4 * j + 0] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
-    }
-    float r = 1.f;
-    if (p.xform == kXformRmsNorm) {
-        float ss = 0.f;
-#pragma unroll
-        for (int i = 0; i < 32; i++) ss = fmaf(v[i], v[i], ss);
-        if (!first_copy) ss = 0.f;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if ((threadIdx.x & 31u) == 0) scratch[threadIdx.x >> 5] = ss;
-        __syncthreads();
-        float total = 0.f;
-        for (uint32_t i = 0; i < (blockDim.x + 31u) / 32u; i++) total += scratch[i];
-        __syncthreads();                                      // scratch is reused (next row, then the reduction)
-        r = rsqrtf(total / (float)p.k + p.eps);
-    }
-    // the second operand is consumed in two halves of 16 so that it never occupies 32 registers
-#pragma unroll
-    for (int h = 0; h < 2; h++) {
-        float w[16];
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float4 u = __ldg(wp + 4 * h + j);
-            w[4 * j + 0] = u.x; w[4 * j + 1] = u.y; w[4 * j + 2] = u.z; w[4 * j + 3] = u.w;
-        }
-#pragma unroll
-        for (int i = 0; i < 16; i++) {
-            const float x = v[16 * h + i];
-            v[16 * h + i] = p.xform == kXformSwiglu ? x * (1.0f / (1.0f + expf(-x))) * w[i] : x * r * w[i];
-        }
     }
     prepare_x<ORDER>(v, xb);
 }

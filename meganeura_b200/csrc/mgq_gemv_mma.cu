@@ -317,8 +317,12 @@ __global__ void sum_slices_kernel(const float *part, const float *addend, float 
     y[i] = addend ? s + addend[i] : s;
 }
 
-// Partial sums of sliced launches: one buffer per device, grown on demand (never during a stream
-// capture: the first call of a shape should come before any capture, like every other first launch).
+// Partial sums of sliced launches (K > 4096): one buffer per device.  A buffer that has been handed
+// to a launch is never freed or moved -- a CUDA graph may have captured its address -- so when a
+// larger request arrives a new, larger buffer is allocated and the old one is kept until the process
+// exits.  The first call of a given size must therefore come before any stream capture (cudaMalloc is
+// not allowed while capturing), and launches that use the buffer must be ordered on one stream per
+// device: two streams running sliced GEMVs at the same time would mix their partial sums.
 struct Scratch {
     float *ptr = nullptr;
     size_t bytes = 0;
@@ -368,11 +372,13 @@ int launch_gemv_mma(int fmt, const float *x, const void *w, const float *addend,
             std::lock_guard<std::mutex> lock(g_scratch_mu);
             if (dev < 0 || dev >= 64) return fail(MGQ_ERR_CUDA, "device index %d out of range", dev);
             if (g_scratch[dev].bytes < need) {
-                if (g_scratch[dev].ptr) MGQ_CUDA(cudaFree(g_scratch[dev].ptr));
-                g_scratch[dev].ptr = nullptr;
-                g_scratch[dev].bytes = 0;
-                MGQ_CUDA(cudaMalloc(&g_scratch[dev].ptr, need));
-                g_scratch[dev].bytes = need;
+                // reserve for the widest batch (16 rows run as two launches of 8) so that a later,
+                // larger batch of the same shape does not need a second buffer
+                const size_t want = (size_t)p.slices * 8 * n * sizeof(float);
+                float *fresh = nullptr;
+                MGQ_CUDA(cudaMalloc(&fresh, want));
+                g_scratch[dev].ptr = fresh;               // the previous buffer stays allocated (see above)
+                g_scratch[dev].bytes = want;
             }
             p.y = g_scratch[dev].ptr;
         }

@@ -24,17 +24,9 @@ struct GemvExchange {
     unsigned int *error;
 };
 
-// Activation transform computed while a GEMV loads x (see mgq_gemv_swiglu / mgq_gemv_rms_norm).
-struct GemvInput {
-    const float *x2;                          // up (SwiGLU) or norm weight (RMSNorm)
-    int xform;                                // 0 none, 1 SwiGLU, 2 RMSNorm
-    float eps;
-};
-
 // Launchers implemented in the .cu files (all pointers are device pointers).
 int launch_gemv(int fmt, const float *x, const void *w, const float *addend, float *y,
-                uint32_t m, uint32_t k, uint32_t n, void *stream, const GemvExchange *xchg = nullptr,
-                const GemvInput *xin = nullptr);
+                uint32_t m, uint32_t k, uint32_t n, void *stream, const GemvExchange *xchg = nullptr);
 // Tensor-core (mma, int8 digit planes) GEMV for 3..16 rows (mgq_gemv_mma.cu).
 bool gemv_mma_eligible(uint32_t m, uint32_t k, uint32_t n, const void *x, const void *w);
 int launch_gemv_mma(int fmt, const float *x, const void *w, const float *addend, float *y,
@@ -45,7 +37,6 @@ bool gemv_streamable(const void *x, uint32_t k, uint32_t n);   // the streaming 
 int launch_exchange_finish(const void *last_vec, uint32_t length, unsigned long long *epoch,
                            unsigned int *error, unsigned int *blocks_done, void *stream);
 int set_gemv_option(const char *name, long value);
-int set_gemv_lookahead(const void *w, size_t bytes);
 int set_plan_option(const char *name, long value);
 int set_gemm_option(const char *name, long value);
 int set_session_option(const char *name, long value);

@@ -3,399 +3,776 @@
 // in barrier groups inside one submission (src/runtime.rs:2843-2959, groups 1202-1256).
 //
 // Why: a decode token is ~150 dependent GEMVs of 10-60 MB.  Launched one by one, each pays a
-// dependency-release + activation-fetch + first-round latency of 2-5 us during which HBM idles.
-// Here every CTA walks the whole list; the shared-memory weight ring is one continuous pipeline
-// across ops (weights are immutable, so the ring keeps prefetching the next op's weights while
-// the CTA waits at the barrier of the current one), and dependent ops are separated by a grid
-// barrier built from per-op arrival counters in global memory:
+// dependency-release + activation-fetch + first-round latency during which HBM idles.  Here one
+// CTA per SM walks the whole list, split into two roles:
 //
-//   writer side:  y stores -> __threadfence -> __syncthreads -> thread 0: atomicAdd(done[op])
-//   reader side:  thread 0 spins (bounded) on ld.acquire(done[wait_for-1]) == gridDim.x
-//                 -> __syncthreads -> activations are read with ld.global.cg (L2, never L1)
+//   * producer (one elected thread): streams this CTA's share of every op's packed weights into a
+//     shared-memory ring with 1-D bulk copies (cp.async.bulk, completion counted on an mbarrier per
+//     slot).  Weights are immutable, so the producer does not wait for any dependency: it runs
+//     ahead across op boundaries until the ring is full, which keeps HBM streaming while the
+//     consumers wait for the previous op's results.  It keeps at most `window` tiles in flight:
+//     more would only queue in the memory system in front of the latency-critical activation loads.
+//   * consumers (TC threads): thread t owns block-in-column b = t % bpc of column t / bpc of each
+//     pass, holds that block's activations in registers as byte planes (dp4a block dot products,
+//     mgq_gemv_device.cuh), takes tiles out of the ring, and finishes column sums through shared
+//     memory and warp shuffles in an order that depends only on K.
 //
-// Every spin has an iteration limit; when it runs out the CTA raises the plan's error word and
-// carries on (results are then undefined, nothing hangs), and the host reports
-// MGQ_ERR_TIMEOUT.  The CTA that arrives last at the final op zeroes the counters, so a launch
-// can be replayed from a CUDA graph with no host-side reset.
+// Dependencies between ops are data flow, not grid barriers.  An op publishes its leading columns
+// as 8-byte {value, stamp} elements (stamp = token index + 1, one 64-bit store per element, so a
+// reader that sees the stamp has the value and no fence is needed) into a vector that the consuming
+// op polls: first two pieces of the block it needs (cheap), then the whole block, re-read until
+// every stamp matches.  The same vector may live in every peer GPU's memory (mgq_exchange_push),
+// which makes the column-sharded multi-GPU step the same code: remote data always lands in the
+// consumer GPU's own memory.  Ops whose activations are an arbitrary plain vector use a per-op
+// arrival counter instead (release: stores, __threadfence, atomicAdd; acquire: ld.acquire poll).
 //
-// The arithmetic per block is the GEMV kernels' (mgq_gemv_device.cuh); the thread count is fixed
-// for the whole plan and each op's column grouping is derived from it.
+// Every wait (mbarrier, stamp, counter) has a deadline read from %globaltimer.  When one runs out
+// the CTA raises the plan's error word and an abort flag that makes all later waits of the CTA fall
+// through at once: the launch finishes with undefined results, nothing hangs, bulk copies still in
+// flight are waited for, and the host reports MGQ_ERR_TIMEOUT.
 #include <cuda_runtime.h>
 
 #include <cstring>
 #include <mutex>
-#include <type_traits>
 #include <vector>
 
 #include "mgq_gemv_device.cuh"
 #include "mgq_internal.h"
 
-struct mgq_plan {
-    std::vector<mgq_plan_op> ops;
-    void *dev_ops = nullptr;              // PlanOp[count]
-    unsigned long long *dev_done = nullptr;   // arrival counters [count] + error word behind them
-    unsigned int *dev_error = nullptr;
-    uint32_t threads = 0, grid = 0, cols = 0, step_bytes = 0;
-    size_t smem = 0;
-    int device = 0;
-    void *kernel = nullptr;
-    uint64_t launches = 0;
-};
-
 namespace mgq {
 namespace {
 using namespace dev;
 
-constexpr int kPlanStages = 4;
-constexpr uint32_t kSpinLimit = 1u << 22;          // ~1 s of L2 round trips before a wait gives up
+constexpr int kRound = 4;                      // passes between two column reductions
+constexpr uint32_t kMaxCachedOps = 160;        // op descriptors kept in shared memory
+constexpr uint32_t kMaxSlots = 16;
 
-struct PlanOp {
-    GemvParams p;
-    uint32_t fmt;
-    uint32_t wait_for;       // ops [0, wait_for) must be complete before this op reads or writes anything
+struct ChainOp {                               // 128 bytes
+    const uint8_t *w;
+    const float *x;                            // plain activations (when xs is null)
+    const unsigned long long *xs;              // k {value, stamp} elements this op consumes, or null
+    const float *addend;
+    float *y;
+    const ExchangePush *push;                  // where the leading columns are published, or null
+    unsigned long long num_blocks;
+    uint32_t k, n, bpc, fmt;
+    uint32_t lanes;                            // columns per pass
+    uint32_t active;                           // lanes * bpc threads carry a block
+    uint32_t ppt;                              // passes per ring tile (1, 2 or 4)
+    uint32_t col_align;                        // CTA column ranges start on multiples of this (16-byte aligned copies)
+    uint32_t hdr_off;                          // Q4: byte offset of the headers inside a ring slot
+    uint32_t wait_for;                         // plain activations: ops [0, wait_for) must have arrived (0: none)
+    uint32_t arrive;                           // 1: CTAs count themselves in done[op] when they finish the op
+    uint32_t red_shift, red_chunk;
+    uint32_t share_x;                          // 1: the first bpc threads prepare the activations for everyone
+    uint32_t pad[4];
+};
+static_assert(sizeof(ChainOp) == 128, "ChainOp is copied in 16-byte pieces");
+
+struct ChainArgs {
+    const ChainOp *ops;
+    uint32_t n_ops, n_cached;
+    uint32_t slots, slot_bytes, window;
+    uint32_t xchg_bytes;
+    unsigned long long *epoch;                 // token index; the CTA that finishes last adds one
+    unsigned long long *done;                  // [n_ops] arrival counters (monotonic: G per token)
+    unsigned int *error;
+    unsigned int *finish;                      // CTAs that have finished the launch (returns to zero)
+    const unsigned long long *final_vec;       // gathered vector whose stamps must all be in before the token ends, or null
+    uint32_t final_len;
+    unsigned long long deadline_ns;
 };
 
-__device__ __forceinline__ unsigned long long ld_acquire(const unsigned long long *p)
+__device__ __forceinline__ unsigned long long global_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded waiting: expired() is called once per failed try; it looks at the abort flag and the
+// clock every 32nd time.
+struct Waiter {
+    unsigned long long t0 = 0;
+    uint32_t spins = 0;
+    __device__ __forceinline__ bool expired(const ChainArgs &a, volatile uint32_t *abort_flag)
+    {
+        if ((++spins & 31u) != 0) return false;
+        if (*abort_flag) return true;
+        const unsigned long long now = global_ns();
+        if (t0 == 0) { t0 = now; return false; }
+        if (now - t0 <= a.deadline_ns) return false;
+        *abort_flag = 1u;
+        atomicExch(a.error, 1u);
+        return true;
+    }
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// 1-D bulk copy global -> this CTA's shared memory; both addresses 16-byte aligned, bytes % 16 == 0.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, const ChainArgs &a, volatile uint32_t *abort_flag)
+{
+    Waiter w;
+    while (!mbar_try(bar, parity))
+        if (w.expired(a, abort_flag)) break;
+}
+__device__ __forceinline__ void consumer_sync(uint32_t threads)
+{
+    asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
+}
+
+__device__ __forceinline__ ulonglong2 ld_pair2(const ulonglong2 *p)
+{
+    ulonglong2 v;
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(v.x), "=l"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long *p)
 {
     unsigned long long v;
     asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
-
-// Weight-side cursor: which step of which op this thread fetches next.  It runs kPlanStages-1
-// steps ahead of the compute side through the same padded sequence (every op is padded to whole
-// rounds, so ring slots stay compile-time constants).
-struct FetchCursor {
-    uint32_t op;
-    uint32_t steps_left;        // padded steps of the current op still to issue
-    uint32_t fmt;
-    uint32_t g_next;            // next group inside this CTA's range
-    uint32_t limit;             // Q4: groups in which this thread has a column; Q8: groups of this CTA
-    uint32_t stride;            // elements (Q4) or bytes (Q8) between consecutive groups
-    uint32_t full, last, last_group;   // Q8: blocks this warp owns per group / in the matrix's final group
-    const uint4 *nib;
-    const uint32_t *hdr;
-    const uint8_t *src;
-};
-
-template <int C, int MINB>
-__global__ void __launch_bounds__(384, MINB)
-plan_kernel(const PlanOp *__restrict__ ops, uint32_t n_ops, uint32_t step_bytes,
-            unsigned long long *done, unsigned int *error
-#ifdef MGQ_PLAN_TRACE
-            , unsigned long long *trace      // [n_ops][gridDim.x][6] globaltimer stamps
-#endif
-            )
+__device__ __forceinline__ void st_elem(unsigned long long *p, float value, uint32_t stamp)
 {
-#ifdef MGQ_PLAN_TRACE
-#define PLAN_STAMP(op_, slot_) do { if (trace && threadIdx.x == 0) trace[((size_t)(op_) * gridDim.x + blockIdx.x) * 6 + (slot_)] = now_ns(); } while (0)
-#else
-#define PLAN_STAMP(op_, slot_) do { } while (0)
-#endif
-    constexpr int STAGES = kPlanStages, ROUND = STAGES * C;
-    extern __shared__ __align__(16) uint8_t smem[];
-    const uint32_t T = blockDim.x, t = threadIdx.x, lane = t & 31u, warp = t >> 5, G = gridDim.x;
-    uint8_t *ring = smem;                                                        // [STAGES][step_bytes]
-    float *s_red = reinterpret_cast<float *>(smem + (size_t)STAGES * step_bytes);  // [2][ROUND][T]
-    // A step's slot is divided into one private area per warp (C*640 B used by Q4, C*1152 B by Q8),
-    // so no warp ever writes where another one reads, whatever the formats of neighbouring ops.
-    const uint32_t warp_bytes = step_bytes / (T >> 5);
+    const unsigned long long v = (unsigned long long)__float_as_uint(value) | ((unsigned long long)stamp << 32);
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
 
-    auto cta_range = [&](const GemvParams &p, uint32_t &g0, uint32_t &g1) {
-        g0 = (uint32_t)((unsigned long long)blockIdx.x * p.total_iters / G);
-        g1 = (uint32_t)((unsigned long long)(blockIdx.x + 1) * p.total_iters / G);
-    };
-    auto my_groups = [&](const GemvParams &p, uint32_t g1, uint32_t n_g) {
-        const bool has_block = t < p.active;
-        const uint32_t csub = t / p.bpc;
-        uint32_t my_n = has_block ? n_g : 0u;
-        if (has_block && g1 == p.total_iters && n_g > 0 && (p.total_iters - 1) * p.cpi + csub >= p.n) my_n = n_g - 1;
-        return my_n;
-    };
+// This CTA's share of an op: a contiguous column range, cut into passes of `lanes` columns and ring
+// tiles of `ppt` passes.  Producer and consumers derive it from the same numbers.
+struct Share {
+    uint32_t c0, ncols, passes, tiles;
+};
+__device__ __forceinline__ Share share_of(const ChainOp &o)
+{
+    const uint32_t units = o.n / o.col_align;
+    const uint32_t u0 = (uint32_t)((unsigned long long)blockIdx.x * units / gridDim.x);
+    const uint32_t u1 = (uint32_t)((unsigned long long)(blockIdx.x + 1) * units / gridDim.x);
+    Share s;
+    s.c0 = u0 * o.col_align;
+    s.ncols = (u1 - u0) * o.col_align;
+    s.passes = (s.ncols + o.lanes - 1) / o.lanes;
+    s.tiles = (s.passes + o.ppt - 1) / o.ppt;
+    return s;
+}
 
-    // ------------------------------------------------------------------ weight side
-    FetchCursor f{};
-    f.op = 0xFFFFFFFFu;
-    auto fetch_setup = [&]() {                      // advance to the next op in which this CTA has work
-        for (;;) {
-            f.op++;
-            if (f.op >= n_ops) { f.steps_left = 0xFFFFFFFFu; f.fmt = 0; return; }
-            const GemvParams p = ops[f.op].p;
-            uint32_t g0, g1;
-            cta_range(p, g0, g1);
-            const uint32_t n_g = g1 - g0;
-            if (n_g == 0) continue;
-            const uint32_t steps = (n_g + C - 1) / C;
-            f.steps_left = (steps + STAGES - 1) / STAGES * STAGES;
-            f.fmt = ops[f.op].fmt;
-            f.g_next = 0;
-            if (f.fmt == MGQ_FMT_Q4) {
-                const unsigned long long first = (unsigned long long)g0 * p.active + t;
-                f.hdr = reinterpret_cast<const uint32_t *>(p.w) + first;
-                f.nib = reinterpret_cast<const uint4 *>(p.w + p.num_blocks * 4) + first;
-                f.stride = p.active;
-                f.limit = my_groups(p, g1, n_g);
-            } else {
-                const uint32_t w0 = warp * 32u;
-                f.full = p.active > w0 ? min(32u, p.active - w0) : 0u;
-                const uint32_t last_live = (p.n - (p.total_iters - 1) * p.cpi) * p.bpc;
-                f.last = last_live > w0 ? min(32u, last_live - w0) : 0u;
-                f.last_group = g1 == p.total_iters ? n_g - 1 : 0xFFFFFFFFu;
-                f.src = p.w + ((unsigned long long)g0 * p.active + w0) * 36ull + 16u * lane;
-                f.stride = p.active * 36u;
-                f.limit = n_g;
-            }
-            return;
+// The 32 activations of block b out of a gathered {value, stamp} vector: poll the first and the last
+// piece, then read the block until every element carries this token's stamp.
+__device__ __forceinline__ void acquire_stamped(const unsigned long long *xs, uint32_t b, uint32_t stamp, const ChainArgs &a,
+                                                volatile uint32_t *abort_flag, float (&v)[32])
+{
+    const ulonglong2 *src = reinterpret_cast<const ulonglong2 *>(xs + 32u * b);
+    Waiter w;
+    for (;;) {
+        const ulonglong2 p = ld_pair2(src), q = ld_pair2(src + 15);
+        if (((uint32_t)(p.x >> 32) == stamp) & ((uint32_t)(p.y >> 32) == stamp) & ((uint32_t)(q.x >> 32) == stamp) &
+            ((uint32_t)(q.y >> 32) == stamp)) break;
+        if (w.expired(a, abort_flag)) break;
+    }
+    for (;;) {
+        uint32_t ok = 1;
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const ulonglong2 p = ld_pair2(src + j);
+            v[2 * j] = __uint_as_float((uint32_t)p.x);
+            v[2 * j + 1] = __uint_as_float((uint32_t)p.y);
+            ok &= ((uint32_t)(p.x >> 32) == stamp) & ((uint32_t)(p.y >> 32) == stamp);
         }
-    };
-    auto fetch_step = [&](int slot) {
-        if (f.steps_left == 0) fetch_setup();
-        uint8_t *base = ring + (size_t)slot * step_bytes;
-        if (f.fmt == MGQ_FMT_Q4) {
-            uint8_t *area = base + (size_t)warp * warp_bytes;          // only this warp touches its area
-            uint4 *s_nib = reinterpret_cast<uint4 *>(area) + lane;
-            uint32_t *s_hdr = reinterpret_cast<uint32_t *>(area + C * 512) + lane;
+        if (ok) break;
+        if (w.expired(a, abort_flag)) break;
+    }
+}
+
+__device__ __forceinline__ void acquire_plain(const ChainOp &o, uint32_t b, unsigned long long target, const ChainArgs &a,
+                                              volatile uint32_t *abort_flag, float (&v)[32])
+{
+    if (o.wait_for) {
+        Waiter w;
+        while (ld_acquire_u64(a.done + (o.wait_for - 1)) < target)
+            if (w.expired(a, abort_flag)) break;
+    }
+    const float4 *xp = reinterpret_cast<const float4 *>(o.x + 32u * b);
 #pragma unroll
-            for (int j = 0; j < C; j++) {
-                if (f.g_next + j < f.limit) {
-                    cp_async16(s_nib + j * 32, f.nib);
-                    cp_async4(s_hdr + j * 32, f.hdr);
+    for (int j = 0; j < 8; j++) {
+        const float4 q = __ldcg(xp + j);
+        v[4 * j + 0] = q.x; v[4 * j + 1] = q.y; v[4 * j + 2] = q.z; v[4 * j + 3] = q.w;
+    }
+}
+
+template <int TC>
+__global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const ChainArgs a)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    // [barriers 256 B][op descriptors][shared activations][reduction 2 x kRound x TC floats][ring]
+    unsigned long long *bars = reinterpret_cast<unsigned long long *>(smem);       // full[slots], empty[slots]
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + 2 * kMaxSlots * 8);
+    ChainOp *s_ops = reinterpret_cast<ChainOp *>(smem + 384);
+    uint32_t *s_xchg = reinterpret_cast<uint32_t *>(smem + 384 + (size_t)a.n_cached * sizeof(ChainOp));
+    float *s_red = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(s_xchg) + a.xchg_bytes);
+    uint8_t *ring = reinterpret_cast<uint8_t *>(s_red) + (size_t)2 * kRound * TC * sizeof(float);
+    const uint32_t t = threadIdx.x, G = gridDim.x;
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + a.slots * 8u, ring0 = smem_u32(ring);
+
+    if (t == 0) {
+        for (uint32_t s = 0; s < a.slots; s++) {
+            mbar_init(full0 + 8u * s, 1u);
+            mbar_init(empty0 + 8u * s, TC / 32u);
+        }
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    {
+        const uint4 *src = reinterpret_cast<const uint4 *>(a.ops);
+        uint4 *dst = reinterpret_cast<uint4 *>(s_ops);
+        for (uint32_t i = t; i < a.n_cached * (uint32_t)(sizeof(ChainOp) / 16); i += blockDim.x) dst[i] = __ldg(src + i);
+    }
+    const unsigned long long epoch = *reinterpret_cast<volatile const unsigned long long *>(a.epoch);
+    const uint32_t stamp = (uint32_t)epoch + 1u;
+    __syncthreads();
+
+    if (t >= TC) {
+        // ------------------------------------------------------------------ producer
+        if (t == TC) {
+            uint32_t slot = 0, fill = 0;           // slot to fill next, and how often the ring has wrapped
+            uint32_t wslot = 0, wfill = 0;         // the tile `window` positions behind it
+            uint32_t seq = 0;
+            for (uint32_t op = 0; op < a.n_ops; op++) {
+                const ChainOp &o = op < a.n_cached ? s_ops[op] : a.ops[op];
+                const Share sh = share_of(o);
+                const uint32_t tile_cols = o.ppt * o.lanes;
+                for (uint32_t tile = 0; tile < sh.tiles; tile++, seq++) {
+                    if (fill) mbar_wait(empty0 + 8u * slot, (fill - 1u) & 1u, a, abort_flag);
+                    if (seq >= a.window) {
+                        mbar_wait(full0 + 8u * wslot, wfill & 1u, a, abort_flag);
+                        if (++wslot == a.slots) { wslot = 0; wfill++; }
+                    }
+                    const uint32_t col = sh.c0 + tile * tile_cols;
+                    const uint32_t cols = min(tile_cols, sh.c0 + sh.ncols - col);
+                    const unsigned long long first = (unsigned long long)col * o.bpc;       // first block of the tile
+                    const uint32_t blocks = cols * o.bpc;
+                    const uint32_t bar = full0 + 8u * slot, dst = ring0 + slot * a.slot_bytes;
+                    if (o.fmt == MGQ_FMT_Q4) {
+                        mbar_expect(bar, blocks * 20u);
+                        bulk_load(dst, o.w + o.num_blocks * 4ull + first * 16ull, blocks * 16u, bar);
+                        bulk_load(dst + o.hdr_off, o.w + first * 4ull, blocks * 4u, bar);
+                    } else {
+                        mbar_expect(bar, blocks * 36u);
+                        bulk_load(dst, o.w + first * 36ull, blocks * 36u, bar);
+                    }
+                    if (++slot == a.slots) { slot = 0; fill++; }
                 }
-                f.nib += f.stride;
-                f.hdr += f.stride;
             }
-        } else if (f.fmt == MGQ_FMT_Q8) {
-            uint8_t *s_w = base + (size_t)warp * warp_bytes + 16u * lane;
-#pragma unroll
-            for (int j = 0; j < C; j++) {
-                const uint32_t gi = f.g_next + j;
-                if (gi < f.limit) {
-                    const uint32_t cnt = gi == f.last_group ? f.last : f.full;
-                    const uint32_t pieces = (cnt * 36u + 15u) >> 4;
-                    uint8_t *dst = s_w + j * kQ8WarpStage;
-                    if (lane < pieces) cp_async16(dst, f.src);
-                    if (lane + 32u < pieces) cp_async16(dst + 512, f.src + 512);
-                    if (lane + 64u < pieces) cp_async16(dst + 1024, f.src + 1024);
+            // Copies still in flight must land before the CTA may exit (the consumers normally wait for
+            // every tile themselves; after an abort they may not have).
+            if (*abort_flag) {
+                for (uint32_t back = 0; back < a.slots && back < seq; back++) {
+                    const uint32_t s = (slot + a.slots - 1u - back) % a.slots;
+                    const uint32_t f = s < slot ? fill : fill - 1u;
+                    const unsigned long long t0 = global_ns();
+                    while (!mbar_try(full0 + 8u * s, f & 1u))
+                        if (global_ns() - t0 > a.deadline_ns) break;
                 }
-                f.src += f.stride;
             }
         }
-        f.g_next += C;
-        if (f.steps_left != 0xFFFFFFFFu) f.steps_left--;
-        cp_async_commit();
-    };
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; s++) fetch_step(s);
+        __syncwarp();                               // the other lanes of the producer warp wait here for the elected one
+    } else {
+        // ------------------------------------------------------------------ consumers
+        const uint32_t lane = t & 31u;
+        uint32_t slot = 0, fill = 0, round = 0;
+        for (uint32_t op = 0; op < a.n_ops; op++) {
+            const ChainOp &o = op < a.n_cached ? s_ops[op] : a.ops[op];
+            const Share sh = share_of(o);
+            const uint32_t o_arrive = o.arrive;
+            if (sh.ncols != 0) {
+                // the fields the pass loop needs, in registers (the descriptor itself stays in shared memory)
+                const uint32_t bpc = o.bpc, o_active = o.active, o_lanes = o.lanes, o_ppt = o.ppt, o_hdr = o.hdr_off;
+                const uint32_t o_shift = o.red_shift, o_chunk = o.red_chunk;
+                const float *o_addend = o.addend;
+                float *o_y = o.y;
+                const ExchangePush *o_push = o.push;
+                const bool has_block = t < o_active;
+                const uint32_t b = t % bpc, lane_col = t / bpc;
+                const bool q4 = o.fmt == MGQ_FMT_Q4;
 
-    // ------------------------------------------------------------------ compute side
-    uint32_t parity = 0;
-    for (uint32_t op = 0; op < n_ops; op++) {
-        const GemvParams p = ops[op].p;
-        const uint32_t fmt = ops[op].fmt, wait_for = ops[op].wait_for;
-        uint32_t g0, g1;
-        cta_range(p, g0, g1);
-        const uint32_t n_g = g1 - g0;
-        PLAN_STAMP(op, 0);
-        if (n_g > 0) {
-            if (wait_for) {
-                if (t == 0) {
-                    uint32_t spins = 0;
-                    while (ld_acquire(done + (wait_for - 1)) < (unsigned long long)G) {
-                        if (++spins > kSpinLimit) { atomicExch(error, 1u); break; }
+                // ---- activations of this thread's block, as byte planes in registers
+                XBlock xb;
+                if (o.share_x ? t < bpc : has_block) {
+                    float v[32];
+                    if (o.xs) acquire_stamped(o.xs, b, stamp, a, abort_flag, v);
+                    else      acquire_plain(o, b, (unsigned long long)G * (epoch + 1ull), a, abort_flag, v);
+                    if (q4) prepare_x<1>(v, xb); else prepare_x<0>(v, xb);
+                    if (o.share_x) {
+                        uint32_t *dst = s_xchg + (t >> 5) * (26u * 32u) + lane;
+#pragma unroll
+                        for (int i = 0; i < 8; i++) { dst[i * 32] = xb.p0[i]; dst[(8 + i) * 32] = xb.p1[i]; dst[(16 + i) * 32] = xb.p2[i]; }
+                        dst[24 * 32] = __float_as_uint(xb.inv);
+                        dst[25 * 32] = __float_as_uint(xb.sum);
                     }
                 }
-                __syncthreads();
-            }
-            PLAN_STAMP(op, 1);
-            const uint32_t b = t % p.bpc;
-            const uint32_t my_n = my_groups(p, g1, n_g);
-            XBlock xb;
-            if (fmt == MGQ_FMT_Q4) load_x<1, true>(p.x, b, xb); else load_x<0, true>(p.x, b, xb);
-            const ReduceSlot slot = make_slot<ROUND>(p);
-            PLAN_STAMP(op, 2);
+                if (o.share_x) {
+                    consumer_sync(TC);
+                    const uint32_t *src = s_xchg + (b >> 5) * (26u * 32u) + (b & 31u);
+#pragma unroll
+                    for (int i = 0; i < 8; i++) { xb.p0[i] = src[i * 32]; xb.p1[i] = src[(8 + i) * 32]; xb.p2[i] = src[(16 + i) * 32]; }
+                    xb.inv = __uint_as_float(src[24 * 32]);
+                    xb.sum = __uint_as_float(src[25 * 32]);
+                }
 
-            // one copy of the round loop per format, so that only one format's block code is hot
-            auto run_rounds = [&](auto fmt_tag) {
-                constexpr int FMT = decltype(fmt_tag)::value;
-                for (uint32_t g = 0; g < n_g; g += ROUND) {
-                    float part[1][ROUND];
+                // ---- which column sum this thread finishes after each round (same for every round)
+                const uint32_t R = 1u << o_shift;
+                const uint32_t fin = t >> o_shift, li = t & (R - 1u);
+                const bool fin_valid = fin < (uint32_t)kRound * o_lanes;
+                const uint32_t fin_u = fin_valid ? fin / o_lanes : 0u, fin_j = fin_valid ? fin % o_lanes : 0u;
+                const uint32_t fin_first = li * o_chunk;
+                const uint32_t fin_cnt = (fin_valid && fin_first < bpc) ? min(o_chunk, bpc - fin_first) : 0u;
+                const uint32_t fin_src = fin_u * TC + fin_j * bpc + fin_first;
+                const bool fin_vec = (bpc % 4u == 0u) && (o_chunk % 4u == 0u);
+                // where published columns go (read early: the descriptor lives in global memory)
+                uint32_t pub_cols = 0, pub_world = 0, pub_rank = 0;
+                if (o_push && fin_valid && li == 0) {
+                    pub_cols = o_push->gather_cols; pub_world = o_push->world; pub_rank = o_push->rank;
+                }
+
+                for (uint32_t pass0 = 0; pass0 < sh.passes; pass0 += kRound, round++) {
+                    float part[kRound];
 #pragma unroll
-                    for (int u = 0; u < STAGES; u++) {
-                        __syncwarp();                   // staging areas are per warp: all lanes left the slot refilled next
-                        fetch_step((u + STAGES - 1) % STAGES);
-                        cp_async_wait<STAGES - 1>();
-                        __syncwarp();
-                        const uint8_t *area = ring + (size_t)u * step_bytes + (size_t)warp * warp_bytes;
-#pragma unroll
-                        for (int j = 0; j < C; j++) {
-                            float out = 0.f;
-                            if (g + u * C + j < my_n) {
-                                if (FMT == MGQ_FMT_Q4) {
-                                    const uint4 q = (reinterpret_cast<const uint4 *>(area) + lane)[j * 32];
-                                    const uint32_t h = (reinterpret_cast<const uint32_t *>(area + C * 512) + lane)[j * 32];
+                    for (int u = 0; u < kRound; u++) {
+                        part[u] = 0.f;
+                        const uint32_t pass = pass0 + u;
+                        if (pass < sh.passes) {                                   // CTA-uniform
+                            const uint32_t p = pass % o_ppt;
+                            if (p == 0) mbar_wait(full0 + 8u * slot, fill & 1u, a, abort_flag);
+                            const uint8_t *tile = ring + (size_t)slot * a.slot_bytes;
+                            const uint32_t idx = p * o_active + t;
+                            const bool live = has_block && pass * o_lanes + lane_col < sh.ncols;
+                            if (q4) {
+                                uint4 q = make_uint4(0, 0, 0, 0);
+                                uint32_t h = 0;
+                                if (live) {
+                                    q = reinterpret_cast<const uint4 *>(tile)[idx];
+                                    h = reinterpret_cast<const uint32_t *>(tile + o_hdr)[idx];
+                                }
+                                if (p + 1 == o_ppt || pass + 1 == sh.passes) {   // last pass of the tile: hand the slot back
+                                    __syncwarp();
+                                    if (lane == 0) mbar_arrive(empty0 + 8u * slot);
+                                    if (++slot == a.slots) { slot = 0; fill++; }
+                                }
+                                if (live) {
                                     const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&h));
-                                    out = fmaf(dm.x * xb.inv, dot_q4(q, xb), dm.y * xb.sum);
-                                } else {
-                                    const uint32_t *bp = reinterpret_cast<const uint32_t *>(area + j * kQ8WarpStage + 36u * lane);
-                                    const float scale = __half2float(__ushort_as_half((unsigned short)(bp[0] & 0xFFFFu)));
-                                    out = scale * xb.inv * dot_q8(bp + 1, xb);
+                                    part[u] = fmaf(dm.x * xb.inv, dot_q4(q, xb), dm.y * xb.sum);
+                                }
+                            } else {
+                                uint32_t c[9];
+#pragma unroll
+                                for (int i = 0; i < 9; i++) c[i] = 0;
+                                if (live) {
+                                    const uint32_t *bp = reinterpret_cast<const uint32_t *>(tile) + idx * 9u;
+#pragma unroll
+                                    for (int i = 0; i < 9; i++) c[i] = bp[i];
+                                }
+                                if (p + 1 == o_ppt || pass + 1 == sh.passes) {
+                                    __syncwarp();
+                                    if (lane == 0) mbar_arrive(empty0 + 8u * slot);
+                                    if (++slot == a.slots) { slot = 0; fill++; }
+                                }
+                                if (live) {
+                                    const float scale = __half2float(__ushort_as_half((unsigned short)(c[0] & 0xFFFFu)));
+                                    part[u] = scale * xb.inv * dot_q8(c + 1, xb);
                                 }
                             }
-                            part[0][u * C + j] = out;
                         }
                     }
-                    reduce_store<1, ROUND, true>(p, slot, s_red + (size_t)(parity & 1u) * ROUND * T, part, g0 + g, g1);
-                    parity++;
+                    // ---- finish the round's columns
+                    float *red = s_red + (size_t)(round & 1u) * kRound * TC;
+#pragma unroll
+                    for (int u = 0; u < kRound; u++) red[u * TC + t] = part[u];
+                    consumer_sync(TC);
+                    float s = 0.f;
+                    const float *src = red + fin_src;
+                    if (fin_vec) {
+                        for (uint32_t j = 0; j < fin_cnt; j += 4) {
+                            const float4 q = *reinterpret_cast<const float4 *>(src + j);
+                            s += (q.x + q.y) + (q.z + q.w);
+                        }
+                    } else {
+                        for (uint32_t j = 0; j < fin_cnt; j++) s += src[j];
+                    }
+                    if (o_shift > 4) s += __shfl_xor_sync(0xffffffffu, s, 16);
+                    if (o_shift > 3) s += __shfl_xor_sync(0xffffffffu, s, 8);
+                    if (o_shift > 2) s += __shfl_xor_sync(0xffffffffu, s, 4);
+                    if (o_shift > 1) s += __shfl_xor_sync(0xffffffffu, s, 2);
+                    if (o_shift > 0) s += __shfl_xor_sync(0xffffffffu, s, 1);
+                    const uint32_t rel = (pass0 + fin_u) * o_lanes + fin_j;                  // column inside this CTA's range
+                    if (fin_valid && li == 0 && rel < sh.ncols) {
+                        const uint32_t col = sh.c0 + rel;
+                        const float v = o_addend ? s + __ldcg(o_addend + col) : s;
+                        o_y[col] = v;
+                        if (col < pub_cols) {
+                            const size_t at = (size_t)pub_rank * pub_cols + col;
+                            for (uint32_t q = 0; q < pub_world; q++)
+                                st_elem(reinterpret_cast<unsigned long long *>(o_push->dst[q]) + at, v, stamp);
+                        }
+                    }
                 }
-            };
-            if (fmt == MGQ_FMT_Q4) run_rounds(std::integral_constant<int, MGQ_FMT_Q4>{});
-            else                   run_rounds(std::integral_constant<int, MGQ_FMT_Q8>{});
-        }
-        // publish this CTA's part of op: results first, then the arrival
-        PLAN_STAMP(op, 3);
-        __threadfence();
-        __syncthreads();
-        PLAN_STAMP(op, 4);
-        if (t == 0) {
-            const unsigned long long prev = atomicAdd(done + op, 1ull);
-            if (op == n_ops - 1 && prev == (unsigned long long)G - 1) {
-                // every CTA has finished every op and reads no counter any more: rearm for the next launch
-                for (uint32_t i = 0; i < n_ops; i++) done[i] = 0ull;
+            }
+            if (o_arrive) {
+                // publish this CTA's part of the op to readers of the plain vector: results, then the arrival
                 __threadfence();
+                consumer_sync(TC);
+                if (t == 0) atomicAdd(a.done + op, 1ull);
+            }
+        }
+        // ---- the token ends when the last gathered vector is complete on this GPU
+        if (a.final_vec) {
+            for (uint32_t i = blockIdx.x * TC + t; i < a.final_len; i += G * TC) {
+                Waiter w;
+                for (;;) {
+                    unsigned long long e;
+                    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(e) : "l"(a.final_vec + i) : "memory");
+                    if ((uint32_t)(e >> 32) == stamp) break;
+                    if (w.expired(a, abort_flag)) break;
+                }
             }
         }
     }
-    cp_async_wait<0>();
+    __syncthreads();
+    if (t == 0) {
+        __threadfence();
+        if (atomicAdd(a.finish, 1u) == G - 1u) {
+            atomicExch(a.finish, 0u);
+            *reinterpret_cast<volatile unsigned long long *>(a.epoch) = epoch + 1ull;
+            __threadfence();
+        }
+    }
 }
 
-int g_plan_cols = 0;
-int plan_cols_option() { return g_plan_cols; }
+// ------------------------------------------------------------------------------- host side
 
-uint32_t columns_for(uint32_t threads, uint32_t bpc)
+struct PlanTuning {
+    int consumers = 0;          // "plan.consumer_threads": 512 or 768 (0: 768)
+    int window = 0;             // "plan.window_tiles": ring tiles in flight (0: automatic)
+    int slot_kb = 0;            // "plan.tile_kb": target size of a ring tile in KB (0: automatic)
+    long deadline_us = 0;       // "plan.deadline_us": limit of every device-side wait (0: 20000)
+};
+PlanTuning g_plan_tuning;
+
+struct Layout {
+    uint32_t tc = 0, slots = 0, slot_bytes = 0, window = 0, xchg_bytes = 0, n_cached = 0;
+    size_t smem = 0;
+};
+
+inline uint32_t gcd_u32(uint32_t a, uint32_t b) { while (b) { const uint32_t r = a % b; a = b; b = r; } return a; }
+
+// Fills the kernel-side fields of one op that depend only on its shape and the consumer count.
+int shape_op(ChainOp &d, size_t i, uint32_t tc, uint32_t tile_target)
 {
-    uint32_t cpi = threads / bpc;
-    const uint32_t need = bpc % 4 == 0 ? 1u : (bpc % 2 == 0 ? 2u : 4u);
-    return cpi - cpi % need;
+    const uint32_t bpc = d.bpc;
+    d.col_align = 4u / gcd_u32(bpc, 4u);
+    uint32_t lanes = tc / bpc;
+    lanes -= lanes % d.col_align;
+    if (lanes == 0)
+        return fail(MGQ_ERR_SHAPE, "op %zu: K=%u is outside the plan kernel's range (256 <= K <= %u)", i, d.k, tc / d.col_align * 32u);
+    d.lanes = lanes;
+    d.active = lanes * bpc;
+    const uint32_t per_block = d.fmt == MGQ_FMT_Q4 ? 20u : 36u;
+    const uint32_t pass_bytes = d.active * per_block;
+    d.ppt = 1;
+    while (d.ppt < (uint32_t)kRound && pass_bytes * d.ppt * 2u <= tile_target) d.ppt *= 2;
+    d.hdr_off = d.ppt * d.active * 16u;
+    // finishing lanes per column: a power of two, at most 32, as many as a round leaves room for;
+    // all of it follows from K and the consumer count, so a column's sum does not depend on N
+    const uint32_t cols_per_round = (uint32_t)kRound * lanes;
+    d.red_shift = 0;
+    while (d.red_shift < 5 && (cols_per_round << (d.red_shift + 1)) <= tc && (2u << d.red_shift) <= bpc) d.red_shift++;
+    const uint32_t fl = 1u << d.red_shift;
+    d.red_chunk = (bpc + fl - 1) / fl;
+    if (d.red_chunk % 4 != 0 && bpc % 4 == 0 && d.red_chunk > 4) d.red_chunk = (d.red_chunk + 3u) & ~3u;
+    d.share_x = lanes >= 2 ? 1u : 0u;
+    return MGQ_OK;
 }
+
+int check_op(const mgq_plan_op &o, size_t i)
+{
+    if (!o.w || !o.y) return fail(MGQ_ERR_NULL, "op %zu: null operand pointer", i);
+    if (!is_quant(o.fmt)) return fail(MGQ_ERR_FORMAT, "op %zu: weight format %d is not Q4/Q8", i, o.fmt);
+    if (o.m != 1) return fail(MGQ_ERR_SHAPE, "op %zu: the plan kernel takes single-row GEMVs (m=%u)", i, o.m);
+    if (o.k == 0 || o.n == 0 || o.k % 32 != 0) return fail(MGQ_ERR_SHAPE, "op %zu: bad shape k=%u n=%u", i, o.k, o.n);
+    const uint32_t bpc = o.k / 32;
+    const unsigned long long nb = (unsigned long long)bpc * o.n;
+    if (bpc < 8 || nb % 4 != 0)
+        return fail(MGQ_ERR_SHAPE, "op %zu: K=%u N=%u is outside the plan kernel's range (K >= 256, K*N/32 %% 4 == 0)", i, o.k, o.n);
+    if (reinterpret_cast<uintptr_t>(o.w) % 16 != 0 || reinterpret_cast<uintptr_t>(o.x) % 16 != 0)
+        return fail(MGQ_ERR_ALIGN, "op %zu: weights and activations must be 16-byte aligned", i);
+    return MGQ_OK;
+}
+
+void base_op(ChainOp &d, const mgq_plan_op &o)
+{
+    std::memset(&d, 0, sizeof d);
+    d.w = static_cast<const uint8_t *>(o.w);
+    d.x = o.x; d.addend = o.addend; d.y = o.y;
+    d.k = o.k; d.n = o.n; d.bpc = o.k / 32; d.fmt = (uint32_t)o.fmt;
+    d.num_blocks = (unsigned long long)d.bpc * o.n;
+}
+
+// Shared-memory layout for a list of shaped ops.
+int layout_for(const ChainOp *ops, size_t count, uint32_t tc, int optin, Layout &L)
+{
+    uint32_t slot = 0, xchg = 0;
+    for (size_t i = 0; i < count; i++) {
+        const ChainOp &d = ops[i];
+        const uint32_t tile = d.ppt * d.active * (d.fmt == MGQ_FMT_Q4 ? 20u : 36u);
+        slot = tile > slot ? tile : slot;
+        if (d.share_x) {
+            const uint32_t need = (d.bpc + 31u) / 32u * 26u * 32u * 4u;
+            xchg = need > xchg ? need : xchg;
+        }
+    }
+    L.tc = tc;
+    L.slot_bytes = (slot + 127u) & ~127u;
+    L.xchg_bytes = (xchg + 127u) & ~127u;
+    L.n_cached = count < kMaxCachedOps ? (uint32_t)count : kMaxCachedOps;
+    const size_t fixed = 384 + (size_t)L.n_cached * sizeof(ChainOp) + L.xchg_bytes + (size_t)2 * kRound * tc * sizeof(float);
+    if (fixed + 2 * (size_t)L.slot_bytes > (size_t)optin)
+        return fail(MGQ_ERR_SHAPE, "plan needs %zu B of shared memory, device allows %d", fixed + 2 * (size_t)L.slot_bytes, optin);
+    uint32_t slots = (uint32_t)(((size_t)optin - fixed) / L.slot_bytes);
+    if (slots > kMaxSlots) slots = kMaxSlots;
+    L.slots = slots;
+    // bytes in flight per SM: about what hides the HBM latency at full rate, not more
+    uint32_t window = g_plan_tuning.window > 0 ? (uint32_t)g_plan_tuning.window : (65536u + L.slot_bytes - 1) / L.slot_bytes;
+    if (window >= slots) window = slots - 1;
+    if (window < 1) window = 1;
+    L.window = window;
+    L.smem = fixed + (size_t)slots * L.slot_bytes;
+    return MGQ_OK;
+}
+
+unsigned long long deadline_ns()
+{
+    const long us = g_plan_tuning.deadline_us > 0 ? g_plan_tuning.deadline_us : 20000;
+    return (unsigned long long)us * 1000ull;
+}
+
+void *kernel_for(uint32_t tc) { return tc == 512 ? (void *)chain_kernel<512> : (void *)chain_kernel<768>; }
+
+struct DeviceFacts { int device = 0, sms = 0, optin = 0; };
+int device_facts(DeviceFacts &f)
+{
+    MGQ_CUDA(cudaGetDevice(&f.device));
+    MGQ_CUDA(cudaDeviceGetAttribute(&f.sms, cudaDevAttrMultiProcessorCount, f.device));
+    MGQ_CUDA(cudaDeviceGetAttribute(&f.optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, f.device));
+    return MGQ_OK;
+}
+
+uint32_t consumer_threads() { return g_plan_tuning.consumers == 512 ? 512u : 768u; }
+uint32_t tile_target() { return g_plan_tuning.slot_kb > 0 ? (uint32_t)g_plan_tuning.slot_kb * 1024u : 16384u; }
 
 }  // namespace
+
+int set_plan_option(const char *name, long value)
+{
+    if (!std::strcmp(name, "plan.consumer_threads")) {
+        if (value != 0 && value != 512 && value != 768) return fail(MGQ_ERR_SHAPE, "%s must be 0, 512 or 768", name);
+        g_plan_tuning.consumers = (int)value;
+    } else if (!std::strcmp(name, "plan.window_tiles")) {
+        if (value < 0 || value > 15) return fail(MGQ_ERR_SHAPE, "%s out of range", name);
+        g_plan_tuning.window = (int)value;
+    } else if (!std::strcmp(name, "plan.tile_kb")) {
+        if (value < 0 || value > 64) return fail(MGQ_ERR_SHAPE, "%s out of range", name);
+        g_plan_tuning.slot_kb = (int)value;
+    } else if (!std::strcmp(name, "plan.deadline_us")) {
+        if (value < 0 || value > 10000000) return fail(MGQ_ERR_SHAPE, "%s out of range", name);
+        g_plan_tuning.deadline_us = value;
+    } else {
+        return fail(MGQ_ERR_NAME, "unknown option: %s", name);
+    }
+    return MGQ_OK;
+}
+
 }  // namespace mgq
 
 using namespace mgq;
 
-namespace mgq {
-int set_plan_option(const char *name, long value)
-{
-    if (!std::strcmp(name, "plan.columns_per_thread")) {
-        if (value != 0 && value != 1 && value != 2 && value != 4) return fail(MGQ_ERR_SHAPE, "%s must be 0, 1, 2 or 4", name);
-        g_plan_cols = (int)value;
-        return MGQ_OK;
-    }
-    return fail(MGQ_ERR_NAME, "unknown option: %s", name);
-}
-}  // namespace mgq
+struct mgq_plan {
+    size_t count = 0;
+    uint8_t *dev_block = nullptr;             // one allocation: descriptors, push records, counters, state words, gathered vectors
+    size_t dev_bytes = 0, state_off = 0, state_bytes = 0;
+    ChainArgs args{};
+    Layout layout;
+    uint32_t grid = 0;
+    int device = 0;
+    void *kernel = nullptr;
+    bool own_state = true;                    // epoch / error words live in dev_block
+    uint64_t launches = 0;
+};
 
-#ifdef MGQ_PLAN_TRACE
-static unsigned long long *g_plan_trace = nullptr;
-extern "C" void mgq_debug_set_plan_trace(unsigned long long *buf) { g_plan_trace = buf; }
-#endif
+namespace {
+
+int create_plan(const mgq_plan_op *ops, const mgq_plan_link *links, size_t count, unsigned long long *epoch, unsigned int *error,
+                const mgq_exchange_elem *final_vec, uint32_t final_len, mgq_plan **out)
+{
+    if (!ops || !out) return fail(MGQ_ERR_NULL, "null argument");
+    *out = nullptr;
+    if (count == 0 || count > 65535) return fail(MGQ_ERR_SHAPE, "a plan holds 1..65535 ops, got %zu", count);
+    const uint32_t tc = consumer_threads();
+    std::vector<ChainOp> host(count);
+    std::vector<uint32_t> publish(count, 0);        // columns op j publishes into a vector owned by the plan
+    std::vector<int> source(count, -1);
+    std::vector<size_t> source_off(count, 0);
+    for (size_t i = 0; i < count; i++) {
+        const mgq_plan_op &o = ops[i];
+        if (int rc = check_op(o, i)) return rc;
+        const bool linked_x = links && links[i].wait_vec;
+        if (!o.x && !linked_x) return fail(MGQ_ERR_NULL, "op %zu: null activation pointer", i);
+        ChainOp &d = host[i];
+        base_op(d, o);
+        if (int rc = shape_op(d, i, tc, tile_target())) return rc;
+        d.wait_for = o.wait_for > i ? (uint32_t)i : o.wait_for;
+        if (links) {
+            d.push = reinterpret_cast<const ExchangePush *>(links[i].push_dev);
+            d.xs = reinterpret_cast<const unsigned long long *>(links[i].wait_vec);
+            if (d.xs) d.wait_for = 0;
+            if (reinterpret_cast<uintptr_t>(d.xs) % 16 != 0) return fail(MGQ_ERR_ALIGN, "op %zu: the gathered vector must be 16-byte aligned", i);
+        } else if (d.wait_for) {
+            // activations that are a range of an earlier op's output travel as stamped elements
+            for (size_t j = d.wait_for; j-- > 0;) {
+                const float *y0 = ops[j].y, *y1 = ops[j].y + ops[j].n;
+                if (o.x >= y0 && o.x + o.k <= y1) {
+                    source[i] = (int)j;
+                    source_off[i] = (size_t)(o.x - y0);
+                    const uint32_t need = (uint32_t)source_off[i] + o.k;
+                    publish[j] = need > publish[j] ? need : publish[j];
+                    break;
+                }
+            }
+        }
+    }
+    for (size_t i = 0; i < count; i++)
+        if (!host[i].xs && source[i] < 0 && host[i].wait_for) host[host[i].wait_for - 1].arrive = 1;
+
+    DeviceFacts df;
+    if (int rc = device_facts(df)) return rc;
+    Layout L;
+    if (int rc = layout_for(host.data(), count, tc, df.optin, L)) return rc;
+
+    // device block: [ChainOp x count][ExchangePush x count][done u64 x count][epoch u64, error u32, finish u32][vectors]
+    size_t off = 0;
+    const size_t ops_off = off;      off += count * sizeof(ChainOp);
+    const size_t push_off = off;     off += count * sizeof(ExchangePush);
+    const size_t done_off = off;     off += count * sizeof(unsigned long long);
+    const size_t state_off = off;    off += 64;
+    off = (off + 255) & ~(size_t)255;
+    const size_t vec_off = off;
+    std::vector<size_t> vec_at(count, 0);
+    for (size_t j = 0; j < count; j++) {
+        if (!publish[j]) continue;
+        vec_at[j] = off;
+        off += ((size_t)publish[j] * 8 + 255) & ~(size_t)255;
+    }
+    mgq_plan *pl = new mgq_plan();
+    pl->count = count;
+    pl->device = df.device;
+    pl->layout = L;
+    pl->grid = (uint32_t)df.sms;
+    pl->kernel = kernel_for(tc);
+    pl->dev_bytes = off;
+    pl->state_off = done_off;
+    pl->state_bytes = off - done_off;
+    pl->own_state = epoch == nullptr;
+    int rc = cuda_check((int)cudaMalloc(&pl->dev_block, off), "cudaMalloc", __FILE__, __LINE__);
+    if (!rc) rc = cuda_check((int)cudaMemset(pl->dev_block, 0, off), "cudaMemset", __FILE__, __LINE__);
+    if (rc) { delete pl; return rc; }
+    (void)vec_off;
+    std::vector<ExchangePush> pushes(count);
+    std::memset(pushes.data(), 0, count * sizeof(ExchangePush));
+    for (size_t j = 0; j < count; j++) {
+        if (!publish[j]) continue;
+        pushes[j].world = 1; pushes[j].rank = 0; pushes[j].gather_cols = publish[j];
+        pushes[j].dst[0] = reinterpret_cast<float2 *>(pl->dev_block + vec_at[j]);
+        host[j].push = reinterpret_cast<const ExchangePush *>(pl->dev_block + push_off) + j;
+    }
+    for (size_t i = 0; i < count; i++)
+        if (source[i] >= 0) {
+            host[i].xs = reinterpret_cast<const unsigned long long *>(pl->dev_block + vec_at[source[i]]) + source_off[i];
+            host[i].wait_for = 0;
+        }
+    for (size_t i = 0; i < count; i++)
+        if (reinterpret_cast<uintptr_t>(host[i].xs) % 16 != 0) {
+            // an odd element offset into the producer's vector: fall back to the arrival counter of the op before
+            host[i].xs = nullptr;
+            host[i].wait_for = ops[i].wait_for > i ? (uint32_t)i : ops[i].wait_for;
+            if (host[i].wait_for) host[host[i].wait_for - 1].arrive = 1;
+        }
+    if (!rc) rc = cuda_check((int)cudaMemcpy(pl->dev_block + ops_off, host.data(), count * sizeof(ChainOp), cudaMemcpyHostToDevice), "cudaMemcpy", __FILE__, __LINE__);
+    if (!rc) rc = cuda_check((int)cudaMemcpy(pl->dev_block + push_off, pushes.data(), count * sizeof(ExchangePush), cudaMemcpyHostToDevice), "cudaMemcpy", __FILE__, __LINE__);
+    int occ = 0;
+    if (!rc) rc = cuda_check((int)cudaFuncSetAttribute(pl->kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, df.optin), "cudaFuncSetAttribute", __FILE__, __LINE__);
+    if (!rc) rc = cuda_check((int)cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, pl->kernel, (int)tc + 32, L.smem), "occupancy", __FILE__, __LINE__);
+    if (!rc && occ < 1) rc = fail(MGQ_ERR_CUDA, "plan kernel does not fit on an SM");
+    if (rc) { mgq_plan_destroy(pl); return rc; }
+    ChainArgs &a = pl->args;
+    a.ops = reinterpret_cast<const ChainOp *>(pl->dev_block + ops_off);
+    a.n_ops = (uint32_t)count; a.n_cached = L.n_cached;
+    a.slots = L.slots; a.slot_bytes = L.slot_bytes; a.window = L.window; a.xchg_bytes = L.xchg_bytes;
+    a.done = reinterpret_cast<unsigned long long *>(pl->dev_block + done_off);
+    a.epoch = epoch ? epoch : reinterpret_cast<unsigned long long *>(pl->dev_block + state_off);
+    a.error = error ? error : reinterpret_cast<unsigned int *>(pl->dev_block + state_off + 8);
+    a.finish = reinterpret_cast<unsigned int *>(pl->dev_block + state_off + 12);
+    a.final_vec = reinterpret_cast<const unsigned long long *>(final_vec);
+    a.final_len = final_vec ? final_len : 0;
+    a.deadline_ns = deadline_ns();
+    *out = pl;
+    return MGQ_OK;
+}
+
+}  // namespace
 
 extern "C" {
 
 int mgq_plan_create(const mgq_plan_op *ops, size_t count, mgq_plan **out)
 {
-    if (!ops || !out) return fail(MGQ_ERR_NULL, "null argument");
-    *out = nullptr;
-    if (count == 0 || count > 65535) return fail(MGQ_ERR_SHAPE, "a plan holds 1..65535 ops, got %zu", count);
-    const uint32_t threads = 384;
-    bool any_q8 = false;
-    std::vector<PlanOp> dev_ops(count);
-    for (size_t i = 0; i < count; i++) {
-        const mgq_plan_op &o = ops[i];
-        if (!o.x || !o.w || !o.y) return fail(MGQ_ERR_NULL, "op %zu: null operand pointer", i);
-        if (!is_quant(o.fmt)) return fail(MGQ_ERR_FORMAT, "op %zu: weight format %d is not Q4/Q8", i, o.fmt);
-        if (o.m != 1) return fail(MGQ_ERR_SHAPE, "op %zu: the plan kernel takes single-row GEMVs (m=%u)", i, o.m);
-        if (o.k == 0 || o.n == 0 || o.k % 32 != 0) return fail(MGQ_ERR_SHAPE, "op %zu: bad shape k=%u n=%u", i, o.k, o.n);
-        const uint32_t bpc = o.k / 32;
-        const unsigned long long nb = (unsigned long long)bpc * o.n;
-        if (bpc < 8 || bpc > threads || nb % 4 != 0)
-            return fail(MGQ_ERR_SHAPE, "op %zu: K=%u N=%u is outside the plan kernel's range (256 <= K <= %u, K*N/32 %% 4 == 0)",
-                        i, o.k, o.n, threads * 32);
-        if (reinterpret_cast<uintptr_t>(o.w) % 16 != 0 || reinterpret_cast<uintptr_t>(o.x) % 16 != 0)
-            return fail(MGQ_ERR_ALIGN, "op %zu: weights and activations must be 16-byte aligned", i);
-        any_q8 |= o.fmt == MGQ_FMT_Q8;
-        PlanOp &d = dev_ops[i];
-        std::memset(&d, 0, sizeof d);
-        d.p.x = o.x; d.p.w = static_cast<const uint8_t *>(o.w); d.p.addend = o.addend; d.p.y = o.y;
-        d.p.k = o.k; d.p.n = o.n; d.p.bpc = bpc;
-        d.p.cpi = columns_for(threads, bpc);
-        d.p.active = d.p.cpi * bpc;
-        d.p.total_iters = (o.n + d.p.cpi - 1) / d.p.cpi;
-        d.p.num_blocks = nb;
-        const uint32_t slots = (uint32_t)(kPlanStages * 4) * d.p.cpi;       // sized for 4 columns per thread: order depends on K only
-        d.p.red_shift = 0;
-        while (d.p.red_shift < 5 && (slots << (d.p.red_shift + 1)) <= threads && (2u << d.p.red_shift) <= bpc) d.p.red_shift++;
-        const uint32_t lanes = 1u << d.p.red_shift;
-        d.p.red_chunk = (bpc + lanes - 1) / lanes;
-        if (d.p.red_chunk % 4 != 0 && bpc % 4 == 0 && d.p.red_chunk > 4) d.p.red_chunk = (d.p.red_chunk + 3u) & ~3u;
-        d.fmt = (uint32_t)o.fmt;
-        d.wait_for = o.wait_for > i ? (uint32_t)i : o.wait_for;   // only earlier ops can be waited for
-    }
-    // columns per thread and step: 4 when the round still leaves a finishing lane per column and the
-    // ring fits (Q8 blocks need 36 B per thread and column, Q4 20 B), else 2
-    uint32_t max_cpi = 1;
-    for (const PlanOp &d : dev_ops) max_cpi = d.p.cpi > max_cpi ? d.p.cpi : max_cpi;
-    const uint32_t per_thread = any_q8 ? 36u : 20u;
-    // Two CTAs per SM with 2 columns per thread and step by default (CTA-wide barriers of one CTA
-    // overlap with the other's work); "plan.columns_per_thread" = 4 selects one wide CTA per SM.
-    uint32_t cols = plan_cols_option() == 4 ? 4 : 2;
-    auto smem_for = [&](uint32_t c) { return (size_t)kPlanStages * per_thread * threads * c + (size_t)2 * kPlanStages * c * threads * 4; };
-    if (cols == 4 && ((uint32_t)(kPlanStages * 4) * max_cpi > threads || smem_for(4) > 200 * 1024)) cols = 2;
-    if ((uint32_t)(kPlanStages * 2) * max_cpi > threads && cols == 2) cols = 1;
-    if (plan_cols_option() == 1) cols = 1;
+    return create_plan(ops, nullptr, count, nullptr, nullptr, nullptr, 0, out);
+}
 
-    mgq_plan *pl = new mgq_plan();
-    pl->ops.assign(ops, ops + count);
-    pl->threads = threads;
-    pl->cols = cols;
-    pl->step_bytes = per_thread * threads * cols;
-    pl->smem = smem_for(cols);
-    pl->kernel = cols == 4 ? (void *)plan_kernel<4, 1> : cols == 2 ? (void *)plan_kernel<2, 2> : (void *)plan_kernel<1, 2>;
-    int rc = cuda_check((int)cudaGetDevice(&pl->device), "cudaGetDevice", __FILE__, __LINE__);
-    int sms = 0, occ = 0, optin = 0;
-    if (!rc) rc = cuda_check((int)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, pl->device), "attr", __FILE__, __LINE__);
-    if (!rc) rc = cuda_check((int)cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, pl->device), "attr", __FILE__, __LINE__);
-    if (!rc && pl->smem > (size_t)optin) rc = fail(MGQ_ERR_SHAPE, "plan needs %zu B of shared memory, device allows %d", pl->smem, optin);
-    if (!rc) rc = cuda_check((int)cudaFuncSetAttribute(pl->kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, optin), "cudaFuncSetAttribute", __FILE__, __LINE__);
-    if (!rc) rc = cuda_check((int)cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, pl->kernel, (int)threads, pl->smem), "occupancy", __FILE__, __LINE__);
-    if (!rc && occ < 1) rc = fail(MGQ_ERR_CUDA, "plan kernel does not fit on an SM");
-    if (!rc) {
-        pl->grid = (uint32_t)sms * (uint32_t)occ;
-        rc = cuda_check((int)cudaMalloc(&pl->dev_ops, count * sizeof(PlanOp)), "cudaMalloc", __FILE__, __LINE__);
-    }
-    if (!rc) rc = cuda_check((int)cudaMemcpy(pl->dev_ops, dev_ops.data(), count * sizeof(PlanOp), cudaMemcpyHostToDevice), "cudaMemcpy", __FILE__, __LINE__);
-    if (!rc) rc = cuda_check((int)cudaMalloc(&pl->dev_done, (count + 1) * sizeof(unsigned long long)), "cudaMalloc", __FILE__, __LINE__);
-    if (!rc) rc = cuda_check((int)cudaMemset(pl->dev_done, 0, (count + 1) * sizeof(unsigned long long)), "cudaMemset", __FILE__, __LINE__);
-    if (rc) { mgq_plan_destroy(pl); return rc; }
-    pl->dev_error = reinterpret_cast<unsigned int *>(pl->dev_done + count);
-    *out = pl;
-    return MGQ_OK;
+int mgq_plan_create_linked(const mgq_plan_op *ops, const mgq_plan_link *links, size_t count, unsigned long long *epoch,
+                           unsigned int *error, const mgq_exchange_elem *final_vec, uint32_t final_len, mgq_plan **out)
+{
+    if (!links || !epoch || !error) return fail(MGQ_ERR_NULL, "null argument");
+    return create_plan(ops, links, count, epoch, error, final_vec, final_len, out);
 }
 
 int mgq_plan_launch(mgq_plan *pl, void *stream)
 {
     if (!pl) return fail(MGQ_ERR_NULL, "null plan");
-    const PlanOp *ops = static_cast<const PlanOp *>(pl->dev_ops);
-    uint32_t n_ops = (uint32_t)pl->ops.size(), step_bytes = pl->step_bytes;
-    unsigned long long *done = pl->dev_done;
-    unsigned int *error = pl->dev_error;
-#ifdef MGQ_PLAN_TRACE
-    unsigned long long *trace = g_plan_trace;
-    void *args[] = {&ops, &n_ops, &step_bytes, &done, &error, &trace};
-#else
-    void *args[] = {&ops, &n_ops, &step_bytes, &done, &error};
-#endif
-    MGQ_CUDA(cudaLaunchCooperativeKernel(pl->kernel, dim3(pl->grid), dim3(pl->threads), args, pl->smem,
+    pl->args.deadline_ns = deadline_ns();
+    void *args[] = {&pl->args};
+    MGQ_CUDA(cudaLaunchCooperativeKernel(pl->kernel, dim3(pl->grid), dim3(pl->layout.tc + 32), args, pl->layout.smem,
                                          static_cast<cudaStream_t>(stream)));
     pl->launches++;
     return MGQ_OK;
@@ -406,32 +783,32 @@ int mgq_plan_check(mgq_plan *pl, void *stream)
     if (!pl) return fail(MGQ_ERR_NULL, "null plan");
     unsigned int err = 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    MGQ_CUDA(cudaMemcpyAsync(&err, pl->dev_error, sizeof err, cudaMemcpyDeviceToHost, s));
+    MGQ_CUDA(cudaMemcpyAsync(&err, pl->args.error, sizeof err, cudaMemcpyDeviceToHost, s));
     MGQ_CUDA(cudaStreamSynchronize(s));
     if (err) {
-        // rearm: a timed-out run may have left counters behind
-        MGQ_CUDA(cudaMemsetAsync(pl->dev_done, 0, (pl->ops.size() + 1) * sizeof(unsigned long long), s));
+        // rearm: a timed-out launch leaves counters and stamps that no longer match the token index
+        MGQ_CUDA(cudaMemsetAsync(pl->args.error, 0, sizeof err, s));
+        if (pl->own_state) MGQ_CUDA(cudaMemsetAsync(pl->dev_block + pl->state_off, 0, pl->state_bytes, s));
         MGQ_CUDA(cudaStreamSynchronize(s));
-        return fail(MGQ_ERR_TIMEOUT, "a grid barrier of the plan kernel ran out of its wait limit");
+        return fail(MGQ_ERR_TIMEOUT, "a wait inside the plan kernel ran out of its time limit");
     }
     return MGQ_OK;
 }
 
-int mgq_plan_info(const mgq_plan *pl, uint32_t *grid, uint32_t *threads, uint32_t *columns_per_thread, size_t *smem_bytes)
+int mgq_plan_info(const mgq_plan *pl, uint32_t *grid, uint32_t *threads, uint32_t *ring_slots, size_t *smem_bytes)
 {
     if (!pl) return fail(MGQ_ERR_NULL, "null plan");
     if (grid) *grid = pl->grid;
-    if (threads) *threads = pl->threads;
-    if (columns_per_thread) *columns_per_thread = pl->cols;
-    if (smem_bytes) *smem_bytes = pl->smem;
+    if (threads) *threads = pl->layout.tc + 32;
+    if (ring_slots) *ring_slots = pl->layout.slots;
+    if (smem_bytes) *smem_bytes = pl->layout.smem;
     return MGQ_OK;
 }
 
 void mgq_plan_destroy(mgq_plan *pl)
 {
     if (!pl) return;
-    if (pl->dev_ops) cudaFree(pl->dev_ops);
-    if (pl->dev_done) cudaFree(pl->dev_done);
+    if (pl->dev_block) cudaFree(pl->dev_block);
     delete pl;
 }
 
@@ -444,16 +821,18 @@ void mgq_plan_destroy(mgq_plan *pl)
 // execution path: an inference loop that was given a fixed device-memory budget at start-up, or a
 // plug-in host that forbids cudaMalloc/cudaFree after initialisation because those calls can
 // synchronise the whole device and can fail late when memory is tight.  Such a caller cannot use
-// mgq_plan_create (it allocates the descriptor table and the barrier counters).
+// mgq_plan_create (it allocates the descriptor table, the counters and the gathered vectors).
 //
-// The kernel's scratch (descriptors, one arrival counter per op, the error word) lives in the
-// array below, which every GPU that loads this library carries until the process exits.  In host
-// code the array's name is only a stand-in; the device address comes from cudaGetSymbolAddress,
-// looked up once per device while that device is current.
+// The kernel's scratch (descriptors, one arrival counter per op, the token index, the error word
+// and the exit counter) lives in the array below, which every GPU that loads this library carries
+// until the process exits.  Dependent ops wait on the arrival counters here; stamped vectors would
+// need memory that grows with the ops' widths.  In host code the array's name is only a stand-in;
+// the device address comes from cudaGetSymbolAddress, looked up once per device while that device is
+// current.
 constexpr size_t kStaticMaxOps = MGQ_STATIC_PLAN_MAX_OPS;
-constexpr size_t kStaticOpsBytes = kStaticMaxOps * sizeof(mgq::PlanOp);
+constexpr size_t kStaticOpsBytes = kStaticMaxOps * sizeof(mgq::ChainOp);
 constexpr size_t kStaticDoneBytes = kStaticMaxOps * sizeof(unsigned long long);
-constexpr size_t kStaticScratchBytes = kStaticOpsBytes + kStaticDoneBytes + 256;     // + error word (own 256-byte line)
+constexpr size_t kStaticScratchBytes = kStaticOpsBytes + kStaticDoneBytes + 256;     // + state words (own 256-byte line)
 static __device__ __align__(256) unsigned char g_static_plan_scratch[kStaticScratchBytes];
 
 namespace {
@@ -462,11 +841,10 @@ struct StaticSetup {
     bool ready = false;
     unsigned char *scratch = nullptr;     // device address of g_static_plan_scratch on this device
     int sms = 0, optin = 0;
-    int occ[3] = {0, 0, 0};               // resident CTAs per SM for the 1-, 2- and 4-column kernels
 };
 
-// One-time, allocation-free preparation for the current device: symbol address, SM count, and the
-// shared-memory opt-in of the three kernel variants.
+// One-time, allocation-free preparation for the current device: symbol address, SM count and the
+// shared-memory opt-in of the kernel variants.
 int static_setup(StaticSetup *&out)
 {
     static std::mutex mu;
@@ -481,9 +859,8 @@ int static_setup(StaticSetup *&out)
         MGQ_CUDA(cudaGetSymbolAddress(&ptr, g_static_plan_scratch));
         MGQ_CUDA(cudaDeviceGetAttribute(&st.sms, cudaDevAttrMultiProcessorCount, dev));
         MGQ_CUDA(cudaDeviceGetAttribute(&st.optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-        MGQ_CUDA(cudaFuncSetAttribute(mgq::plan_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, st.optin));
-        MGQ_CUDA(cudaFuncSetAttribute(mgq::plan_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, st.optin));
-        MGQ_CUDA(cudaFuncSetAttribute(mgq::plan_kernel<4, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, st.optin));
+        MGQ_CUDA(cudaFuncSetAttribute(mgq::chain_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, st.optin));
+        MGQ_CUDA(cudaFuncSetAttribute(mgq::chain_kernel<768>, cudaFuncAttributeMaxDynamicSharedMemorySize, st.optin));
         st.scratch = static_cast<unsigned char *>(ptr);
         st.ready = true;
     }
@@ -502,75 +879,51 @@ extern "C" int mgq_plan_run_static(const mgq_plan_op *ops, size_t count, void *s
         return fail(MGQ_ERR_SIZE, "mgq_plan_run_static takes at most %zu ops (its scratch is a fixed %zu-byte device array), got %zu; "
                                   "use mgq_plan_create for longer lists", kStaticMaxOps, kStaticScratchBytes, count);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    const uint32_t threads = 384;
-    static thread_local PlanOp host_ops[kStaticMaxOps];      // fixed host staging, no heap
-    bool any_q8 = false;
-    uint32_t max_cpi = 1;
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    MGQ_CUDA(cudaStreamIsCapturing(stream, &capturing));
+    if (capturing != cudaStreamCaptureStatusNone)
+        return fail(MGQ_ERR_STATE, "mgq_plan_run_static synchronises its stream and cannot be part of a stream capture");
+    const uint32_t tc = consumer_threads();
+    static thread_local ChainOp host_ops[kStaticMaxOps];      // fixed host staging, no heap
     for (size_t i = 0; i < count; i++) {
         const mgq_plan_op &o = ops[i];
-        if (!o.x || !o.w || !o.y) return fail(MGQ_ERR_NULL, "op %zu: null operand pointer", i);
-        if (!is_quant(o.fmt)) return fail(MGQ_ERR_FORMAT, "op %zu: weight format %d is not Q4/Q8", i, o.fmt);
-        if (o.m != 1) return fail(MGQ_ERR_SHAPE, "op %zu: single-row GEMVs only (m=%u)", i, o.m);
-        if (o.k == 0 || o.n == 0 || o.k % 32 != 0) return fail(MGQ_ERR_SHAPE, "op %zu: bad shape k=%u n=%u", i, o.k, o.n);
-        const uint32_t bpc = o.k / 32;
-        const unsigned long long nb = (unsigned long long)bpc * o.n;
-        if (bpc < 8 || bpc > threads || nb % 4 != 0)
-            return fail(MGQ_ERR_SHAPE, "op %zu: K=%u N=%u is outside the plan kernel's range (256 <= K <= %u, K*N/32 %% 4 == 0)",
-                        i, o.k, o.n, threads * 32);
-        if (reinterpret_cast<uintptr_t>(o.w) % 16 != 0 || reinterpret_cast<uintptr_t>(o.x) % 16 != 0)
-            return fail(MGQ_ERR_ALIGN, "op %zu: weights and activations must be 16-byte aligned", i);
-        any_q8 |= o.fmt == MGQ_FMT_Q8;
-        PlanOp &d = host_ops[i];
-        std::memset(&d, 0, sizeof d);
-        d.p.x = o.x; d.p.w = static_cast<const uint8_t *>(o.w); d.p.addend = o.addend; d.p.y = o.y;
-        d.p.k = o.k; d.p.n = o.n; d.p.bpc = bpc;
-        d.p.cpi = columns_for(threads, bpc);
-        d.p.active = d.p.cpi * bpc;
-        d.p.total_iters = (o.n + d.p.cpi - 1) / d.p.cpi;
-        d.p.num_blocks = nb;
-        const uint32_t slots = (uint32_t)(kPlanStages * 4) * d.p.cpi;
-        d.p.red_shift = 0;
-        while (d.p.red_shift < 5 && (slots << (d.p.red_shift + 1)) <= threads && (2u << d.p.red_shift) <= bpc) d.p.red_shift++;
-        const uint32_t lanes = 1u << d.p.red_shift;
-        d.p.red_chunk = (bpc + lanes - 1) / lanes;
-        if (d.p.red_chunk % 4 != 0 && bpc % 4 == 0 && d.p.red_chunk > 4) d.p.red_chunk = (d.p.red_chunk + 3u) & ~3u;
-        d.fmt = (uint32_t)o.fmt;
+        if (int rc = check_op(o, i)) return rc;
+        if (!o.x) return fail(MGQ_ERR_NULL, "op %zu: null activation pointer", i);
+        ChainOp &d = host_ops[i];
+        base_op(d, o);
+        if (int rc = shape_op(d, i, tc, tile_target())) return rc;
         d.wait_for = o.wait_for > i ? (uint32_t)i : o.wait_for;
-        max_cpi = d.p.cpi > max_cpi ? d.p.cpi : max_cpi;
     }
+    for (size_t i = 0; i < count; i++)
+        if (host_ops[i].wait_for) host_ops[host_ops[i].wait_for - 1].arrive = 1;
     StaticSetup *st = nullptr;
     if (int rc = static_setup(st)) return rc;
-
-    // same kernel choice as mgq_plan_create's default: 2 columns per thread, 1 when a round would not fit
-    const uint32_t per_thread = any_q8 ? 36u : 20u;
-    const uint32_t cols = (uint32_t)(kPlanStages * 2) * max_cpi > threads ? 1u : 2u;
-    void *kernel = cols == 2 ? (void *)plan_kernel<2, 2> : (void *)plan_kernel<1, 2>;
-    const size_t smem = (size_t)kPlanStages * per_thread * threads * cols + (size_t)2 * kPlanStages * cols * threads * 4;
-    if (smem > (size_t)st->optin) return fail(MGQ_ERR_SHAPE, "plan needs %zu B of shared memory, device allows %d", smem, st->optin);
-    int &occ = st->occ[cols == 2 ? 1 : 0];
-    if (occ == 0) MGQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, (int)threads, smem));
+    Layout L;
+    if (int rc = layout_for(host_ops, count, tc, st->optin, L)) return rc;      // depends on the list: worked out on every call
+    void *kernel = kernel_for(tc);
+    int occ = 0;
+    MGQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, (int)tc + 32, L.smem));
     if (occ < 1) return fail(MGQ_ERR_CUDA, "plan kernel does not fit on an SM");
-    const uint32_t grid = (uint32_t)st->sms * (uint32_t)occ;
 
-    // The array still holds the previous call's descriptors, counters and error word: overwrite the
-    // first, zero the other two.  All of it is ordered on `stream` before the kernel.
-    unsigned char *d_ops = st->scratch, *d_done = st->scratch + kStaticOpsBytes, *d_err = d_done + kStaticDoneBytes;
-    MGQ_CUDA(cudaMemcpyAsync(d_ops, host_ops, count * sizeof(PlanOp), cudaMemcpyHostToDevice, stream));
+    // The array still holds the previous call's descriptors, counters and state words: overwrite the
+    // first, zero the others.  All of it is ordered on `stream` before the kernel.
+    unsigned char *d_ops = st->scratch, *d_done = st->scratch + kStaticOpsBytes, *d_state = d_done + kStaticDoneBytes;
+    MGQ_CUDA(cudaMemcpyAsync(d_ops, host_ops, count * sizeof(ChainOp), cudaMemcpyHostToDevice, stream));
     MGQ_CUDA(cudaMemsetAsync(d_done, 0, kStaticDoneBytes + 256, stream));
-    const PlanOp *k_ops = reinterpret_cast<const PlanOp *>(d_ops);
-    uint32_t n_ops = (uint32_t)count, step_bytes = per_thread * threads * cols;
-    unsigned long long *k_done = reinterpret_cast<unsigned long long *>(d_done);
-    unsigned int *k_err = reinterpret_cast<unsigned int *>(d_err);
-#ifdef MGQ_PLAN_TRACE
-    unsigned long long *trace = nullptr;
-    void *args[] = {&k_ops, &n_ops, &step_bytes, &k_done, &k_err, &trace};
-#else
-    void *args[] = {&k_ops, &n_ops, &step_bytes, &k_done, &k_err};
-#endif
-    MGQ_CUDA(cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(threads), args, smem, stream));
+    ChainArgs a{};
+    a.ops = reinterpret_cast<const ChainOp *>(d_ops);
+    a.n_ops = (uint32_t)count; a.n_cached = L.n_cached;
+    a.slots = L.slots; a.slot_bytes = L.slot_bytes; a.window = L.window; a.xchg_bytes = L.xchg_bytes;
+    a.done = reinterpret_cast<unsigned long long *>(d_done);
+    a.epoch = reinterpret_cast<unsigned long long *>(d_state);
+    a.error = reinterpret_cast<unsigned int *>(d_state + 8);
+    a.finish = reinterpret_cast<unsigned int *>(d_state + 12);
+    a.deadline_ns = deadline_ns();
+    void *args[] = {&a};
+    MGQ_CUDA(cudaLaunchCooperativeKernel(kernel, dim3((unsigned)st->sms), dim3(tc + 32), args, L.smem, stream));
     unsigned int err = 0;
-    MGQ_CUDA(cudaMemcpyAsync(&err, d_err, sizeof err, cudaMemcpyDeviceToHost, stream));
+    MGQ_CUDA(cudaMemcpyAsync(&err, d_state + 8, sizeof err, cudaMemcpyDeviceToHost, stream));
     MGQ_CUDA(cudaStreamSynchronize(stream));
-    if (err) return fail(MGQ_ERR_TIMEOUT, "a grid barrier of the plan kernel ran out of its wait limit");
+    if (err) return fail(MGQ_ERR_TIMEOUT, "a wait inside the plan kernel ran out of its time limit");
     return MGQ_OK;
 }

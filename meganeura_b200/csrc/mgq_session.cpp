@@ -62,7 +62,6 @@ struct Dispatch {
     int out;                      // node id of the output
     int extra[3];                 // further outputs of a merged dispatch (node ids, -1: none)
     int weight_format;
-    int xform;                    // GEMV with a fused input transform: 1 SwiGLU (in[3] = up), 2 RmsNorm (in[3] = weight)
     float f0;
     void *workspace;
     std::string label;
@@ -107,7 +106,6 @@ const char *shader_name(int s)
 }
 
 int g_fuse_rope_cache = 1;        // "session.fuse_rope_cache"
-int g_fuse_input = 0;             // "session.fuse_input"
 int g_horizontal_fusion = 2;      // "session.horizontal_fusion": 0 none, 1 gate|up only (the reference's), 2 every same-input GEMV group
 
 }  // namespace
@@ -118,10 +116,6 @@ int set_session_option(const char *name, long value)
     if (!std::strcmp(name, "session.horizontal_fusion")) {
         if (value < 0 || value > 2) return fail(MGQ_ERR_SHAPE, "%s must be 0, 1 or 2", name);
         g_horizontal_fusion = (int)value;
-        return MGQ_OK;
-    }
-    if (!std::strcmp(name, "session.fuse_input")) {
-        g_fuse_input = value ? 1 : 0;
         return MGQ_OK;
     }
     if (!std::strcmp(name, "session.fuse_rope_cache")) {
@@ -477,32 +471,6 @@ void merge_rope_cache(mgq_session *s)
     }
 }
 
-// A single-row RmsNorm or SwiGLU whose only consumer is the GEMV dispatched right after it is
-// computed by that GEMV while it loads its activations (mgq_gemv_rms_norm / mgq_gemv_swiglu).
-void merge_input_transforms(mgq_session *s)
-{
-    std::vector<Dispatch> &ds = s->dispatches;
-    auto is_output = [&](int id) { for (int o : s->outputs) if (o == id) return true; return false; };
-    for (size_t i = 0; i + 1 < ds.size(); i++) {
-        const Dispatch &p = ds[i];
-        Dispatch &d = ds[i + 1];
-        if (d.shader != MGQ_SHADER_MATMUL_GEMV && d.shader != MGQ_SHADER_MATMUL_GEMV_ADD) continue;
-        if (d.xform || d.params[0] != 1 || d.in[0] != p.out || !mgq::is_quant(d.weight_format)) continue;
-        int xform = 0;
-        if (p.shader == MGQ_SHADER_RMS_NORM && p.params[0] == 1) xform = 2;
-        if ((p.shader == MGQ_SHADER_SWIGLU || p.shader == MGQ_SHADER_SWIGLU_CONCAT) && p.in[1] >= 0 && p.params[0] == p.params[1]) xform = 1;
-        if (!xform || count_uses(s->nodes, p.out) != 1 || is_output(p.out)) continue;
-        if (!mgq_gemv_fusable(s->ptr(p.in[0]), d.params[1], d.params[2])) continue;
-        if (reinterpret_cast<uintptr_t>(s->ptr(p.in[1])) % 16 != 0) continue;
-        d.xform = xform;
-        d.in[0] = p.in[0];
-        d.in[3] = p.in[1];
-        d.f0 = p.f0;
-        d.label += xform == 2 ? "+RmsNorm" : "+SwiGLU";
-        ds.erase(ds.begin() + i);
-    }
-}
-
 void set_label(Dispatch &d, const char *fmt, ...)
 {
     char lab[128];
@@ -680,7 +648,6 @@ int mgq_build_inference_session(const mgq_graph *g, mgq_session **out)
         s->dispatches.push_back(d);
     }
     if (g_fuse_rope_cache) merge_rope_cache(s);
-    if (g_fuse_input) merge_input_transforms(s);
     *out = s;
     return MGQ_OK;
 }
@@ -917,11 +884,6 @@ static int run_dispatch(mgq_session *s, const Dispatch &d)
             const float *addend = d.in[2] >= 0 ? f(2) : nullptr;
             if (d.weight_format == MGQ_FMT_F16)
                 return mgq_gemv_f16(f(0), s->ptr(d.in[1]), addend, outp, d.params[0], d.params[1], d.params[2], s->stream);
-            if (d.xform == 1)
-                return mgq_gemv_swiglu(d.weight_format, f(0), f(3), s->ptr(d.in[1]), addend, outp, d.params[0], d.params[1], d.params[2], s->stream);
-            if (d.xform == 2)
-                return mgq_gemv_rms_norm(d.weight_format, f(0), f(3), d.f0, s->ptr(d.in[1]), addend, outp, d.params[0], d.params[1], d.params[2],
-                                         s->stream);
             return mgq_matmul(d.weight_format, s->ptr(d.in[0]), MGQ_A_F32, s->ptr(d.in[1]), addend, outp, d.params[0], d.params[1],
                               d.params[2], s->stream);
         }

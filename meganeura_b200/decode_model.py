@@ -126,10 +126,15 @@ def packed_weight_bytes(cfg: DecoderConfig) -> int:
 
 
 class DecodeSession:
-    """A decode session with synthetic weights: packed codes and scales as the benchmark
-    configurations describe them (synth.py), norm weights 1, a seeded N(0,1) embedding table."""
+    """A decode session with the weights the benchmark configurations describe for whole-model
+    decode: seeded f32 matrices ~ N(0, 0.02^2) run through the reference's quantizer, a different
+    seed for every tensor of every layer, norm weights 1, a seeded N(0,1) embedding table.  A
+    projection of N columns is the periodic extension of a quantized base of `base_cols` columns
+    (the lm_head of an eighth of the vocabulary), so the 30 GB of f32 an 8B-parameter model would
+    need are never materialised and start-up stays in seconds."""
 
-    def __init__(self, cfg: DecoderConfig, max_seq_len: int, seed: int = 0, greedy_history: int = 0):
+    def __init__(self, cfg: DecoderConfig, max_seq_len: int, seed: int = 0, greedy_history: int = 0, base_cols: int = 256):
+        from . import ops
         self.cfg, self.max_seq_len = cfg, max_seq_len
         g = Graph()
         logits, self.k_caches, self.v_caches = build_decode_graph(g, cfg, max_seq_len)
@@ -142,13 +147,17 @@ class DecodeSession:
         ones = np.ones(cfg.hidden_size, dtype=np.float32)
         for name in norm_weights(cfg):
             s.set_parameter(name, ones)
-        cache = {}
-        for name, fmt, k, n in quantized_weights(cfg):
-            key = (fmt, k, n)
-            if key not in cache:                     # one seeded tile per shape keeps start-up in seconds
-                base, n0, reps = synth.synth_weights_tiled(fmt, k, n, seed * 1009 + len(cache))
-                cache[key] = synth.tile_columns(fmt, base, k, n0, reps)
-            s.upload_param(name, cache[key])
+        for idx, (name, fmt, k, n) in enumerate(quantized_weights(cfg)):
+            cols = n
+            if name == "lm_head.weight":
+                while cols > 8192 and cols % 2 == 0 and (cols // 2) % 4 == 0:
+                    cols //= 2
+            else:
+                while cols > base_cols and cols % 2 == 0 and (cols // 2) % 4 == 0:
+                    cols //= 2
+            wrng = np.random.Generator(np.random.PCG64(seed * 1000003 + 17 * idx + 1))
+            w = wrng.standard_normal((k, cols), dtype=np.float32) * np.float32(0.02)
+            s.upload_param(name, synth.tile_columns(fmt, ops.quantize(fmt, w), k, cols, n // cols))
         if greedy_history:
             s.enable_greedy(0, "token_ids", "kv_pos", greedy_history)
 

@@ -15,13 +15,6 @@ def set_option(name: str, value: int) -> None:
     check(lib.mgq_set_option(name.encode(), int(value)))
 
 
-def lookahead(next_w) -> None:
-    """mgq_gemv_lookahead: the GEMV launched next also asks L2 to start fetching `next_w` (a device
-    uint8 tensor holding the packed weights of the GEMV after it)."""
-    check(lib.mgq_gemv_lookahead(next_w.data_ptr() if next_w is not None else None,
-                                 next_w.numel() * next_w.element_size() if next_w is not None else 0))
-
-
 def device_status() -> None:
     """Raises MgqError(MGQ_ERR_TIMEOUT) if a bounded device-side wait ran out (mgq_device_status)."""
     check(lib.mgq_device_status())
@@ -97,19 +90,29 @@ class Plan:
     """A static list of single-row GEMVs executed by one persistent kernel (mgq_plan_*).
 
     ops: iterable of (fmt, x, w, addend_or_None, y, k, n, wait_for) with torch CUDA tensors; the
-    tensors are kept alive by the plan.
+    tensors are kept alive by the plan.  With `links` (one (push_ptr, wait_ptr) pair of device
+    addresses or None per op) the plan uses caller-owned gathered vectors (mgq_plan_create_linked):
+    `epoch_ptr` / `error_ptr` are the token index and timeout flag in local device memory and
+    `final` = (vector address, length) is the gathered vector that must be complete when a launch ends.
     """
 
-    def __init__(self, ops_list):
+    def __init__(self, ops_list, links=None, epoch_ptr=None, error_ptr=None, final=None, keep=None):
         import ctypes
-        self._keep = []
+        self._keep = [keep]
         arr = (_lib.PlanOp * len(ops_list))()
         for i, (fmt, x, w, addend, y, k, n, wait_for) in enumerate(ops_list):
             self._keep.append((x, w, addend, y))
-            arr[i] = _lib.PlanOp(fmt, x.data_ptr(), w.data_ptr(), addend.data_ptr() if addend is not None else None,
-                                 y.data_ptr(), 1, k, n, wait_for)
+            arr[i] = _lib.PlanOp(fmt, x.data_ptr() if x is not None else None, w.data_ptr(),
+                                 addend.data_ptr() if addend is not None else None, y.data_ptr(), 1, k, n, wait_for)
         handle = ctypes.c_void_p()
-        check(lib.mgq_plan_create(arr, len(ops_list), ctypes.byref(handle)))
+        if links is None:
+            check(lib.mgq_plan_create(arr, len(ops_list), ctypes.byref(handle)))
+        else:
+            larr = (_lib.PlanLink * len(ops_list))()
+            for i, (push_ptr, wait_ptr) in enumerate(links):
+                larr[i] = _lib.PlanLink(push_ptr, wait_ptr)
+            fvec, flen = final if final is not None else (None, 0)
+            check(lib.mgq_plan_create_linked(arr, larr, len(ops_list), epoch_ptr, error_ptr, fvec, flen, ctypes.byref(handle)))
         self._h = handle
         self.count = len(ops_list)
 
@@ -123,7 +126,7 @@ class Plan:
         import ctypes
         g, t, c, s = ctypes.c_uint32(), ctypes.c_uint32(), ctypes.c_uint32(), ctypes.c_size_t()
         check(lib.mgq_plan_info(self._h, ctypes.byref(g), ctypes.byref(t), ctypes.byref(c), ctypes.byref(s)))
-        return {"grid": g.value, "threads": t.value, "columns_per_thread": c.value, "smem_bytes": s.value}
+        return {"grid": g.value, "threads": t.value, "ring_slots": c.value, "smem_bytes": s.value}
 
     def __del__(self):
         if getattr(self, "_h", None) and lib is not None:

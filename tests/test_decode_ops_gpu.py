@@ -148,27 +148,3 @@ def test_argmax_lowest_index_wins_and_feedback():
     # without feedback nothing but the token is written
     check(lib.mgq_argmax(ld.data_ptr(), 1000, ws.data_ptr(), tok.data_ptr(), None, None, None, 0, _stream()))
     assert int(tok.item()) == int(np.argmax(logits[:1000])) and int(pos.cpu().numpy()[0]) == 5
-
-
-@pytest.mark.parametrize("fmt", [O_FMT_Q4, O_FMT_Q8])
-@pytest.mark.parametrize("k,n", [(576, 960), (4096, 1024), (1536, 576), (12288, 512)])
-def test_gemv_with_fused_rms_norm_and_swiglu(fmt, k, n):
-    """mgq_gemv_rms_norm / mgq_gemv_swiglu against the oracle operator followed by the f64 oracle GEMV."""
-    import torch
-    from oracle import oracle as O
-    from meganeura_b200._lib import check, lib
-    rng = np.random.Generator(np.random.PCG64(k + n))
-    packed = O.synth_weights(fmt, k, n, seed=k)
-    wd = to_dev(packed)
-    x = (rng.standard_normal((1, k)) * 2).astype(np.float32)
-    nw = (1 + 0.2 * rng.standard_normal(k)).astype(np.float32)
-    up = rng.standard_normal((1, k)).astype(np.float32)
-    addend = rng.standard_normal((1, n)).astype(np.float32)
-    y = torch.zeros((1, n), dtype=torch.float32, device="cuda")
-    xd, nwd, upd, addd = to_dev(x), to_dev(nw), to_dev(up), to_dev(addend)
-    check(lib.mgq_gemv_rms_norm(fmt, xd.data_ptr(), nwd.data_ptr(), 1e-5, wd.data_ptr(), None, y.data_ptr(), 1, k, n, _stream()))
-    want = O.matmul_f64_np(fmt, D.rms_norm(x, nw, 1e-5), packed, k, n)
-    assert O.rel_l2(y.cpu().numpy(), want) <= 1e-4
-    check(lib.mgq_gemv_swiglu(fmt, xd.data_ptr(), upd.data_ptr(), wd.data_ptr(), addd.data_ptr(), y.data_ptr(), 1, k, n, _stream()))
-    want = O.matmul_f64_np(fmt, D.swiglu(x, up), packed, k, n, addend=addend)
-    assert O.rel_l2(y.cpu().numpy(), want) <= 1e-4

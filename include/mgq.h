@@ -63,9 +63,7 @@ const char *mgq_version(void);
  *                               the weights once per 8 rows; 0: two rows at a time on the streaming kernels
  *   "gemv.wait_us"              time limit of the stamp polls of mgq_gemv_exchange / mgq_exchange_finish
  *                               (default 20000)
- *   "plan.consumer_threads"     512 or 768 consumer threads per CTA for plans created afterwards (default 768)
  *   "plan.window_tiles"         ring tiles the producer keeps in flight (default: about 64 KB per SM)
- *   "plan.tile_kb"              target size of a ring tile in KB (default 16)
  *   "plan.deadline_us"          time limit of every wait inside the plan kernel (default 20000)
  *   "gemm.force_tiled"          1: never use the tcgen05 kernel (CUDA-core tiled kernel only)
  *   "session.horizontal_fusion" sessions built afterwards merge single-row matmuls that read the same
@@ -237,8 +235,7 @@ int mgq_matmul_host(int fmt, const void *a_host, int a_dtype, const void *w_dev,
  * vector once every CTA has counted itself out of op wait_for - 1.  y always receives the plain
  * result.  An addend must be complete before the op that produces this op's activations starts.
  * All pointers are device pointers and must stay valid for the plan's lifetime.
- * Limits: m = 1, 256 <= K <= 24576 (K/32 a multiple of 4; less otherwise), K*N/32 a multiple
- * of 4, 16-byte aligned w and x.  Launches of one plan must not overlap.  Every device-side wait
+ * Limits: m = 1, 256 <= K <= 12288, K*N/32 a multiple of 4, 16-byte aligned w and x.  Launches of one plan must not overlap.  Every device-side wait
  * has a time limit ("plan.deadline_us", default 20 ms), after which the launch finishes with
  * undefined results and mgq_plan_check reports MGQ_ERR_TIMEOUT. */
 typedef struct mgq_plan mgq_plan;

@@ -44,30 +44,32 @@ namespace {
 using namespace dev;
 
 constexpr int kRound = 4;                      // passes between two column reductions
-constexpr uint32_t kMaxCachedOps = 160;        // op descriptors kept in shared memory
+constexpr uint32_t kMaxCachedOps = 152;        // op descriptors kept in shared memory
+constexpr uint32_t kStageWords = 32 * 33;      // per leader warp: 32 blocks x 32 activations, rows padded to 33 words
 constexpr uint32_t kMaxSlots = 16;
+constexpr uint32_t kMaxBpc = 384;              // K <= 12288: the prepared activations of one op must fit their shared-memory stage
 
-struct ChainOp {                               // 128 bytes
+struct ChainOp {                               // 192 bytes
     const uint8_t *w;
     const float *x;                            // plain activations (when xs is null)
     const unsigned long long *xs;              // k {value, stamp} elements this op consumes, or null
     const float *addend;
     float *y;
-    const ExchangePush *push;                  // where the leading columns are published, or null
     unsigned long long num_blocks;
+    unsigned long long *pub_dst[kMaxPeers];    // rank p's gathered vector (pub_world entries)
     uint32_t k, n, bpc, fmt;
     uint32_t lanes;                            // columns per pass
     uint32_t active;                           // lanes * bpc threads carry a block
-    uint32_t ppt;                              // passes per ring tile (1, 2 or 4)
     uint32_t col_align;                        // CTA column ranges start on multiples of this (16-byte aligned copies)
     uint32_t hdr_off;                          // Q4: byte offset of the headers inside a ring slot
     uint32_t wait_for;                         // plain activations: ops [0, wait_for) must have arrived (0: none)
     uint32_t arrive;                           // 1: CTAs count themselves in done[op] when they finish the op
     uint32_t red_shift, red_chunk;
-    uint32_t share_x;                          // 1: the first bpc threads prepare the activations for everyone
+    uint32_t reserved1;
+    uint32_t pub_cols, pub_world, pub_rank;    // leading columns published as {value, stamp}, to how many ranks, as which rank
     uint32_t pad[4];
 };
-static_assert(sizeof(ChainOp) == 128, "ChainOp is copied in 16-byte pieces");
+static_assert(sizeof(ChainOp) == 192, "ChainOp is copied in 16-byte pieces");
 
 struct ChainArgs {
     const ChainOp *ops;
@@ -90,13 +92,22 @@ __device__ __forceinline__ unsigned long long global_ns()
     return t;
 }
 
+// The CTA's abort flag sits at a fixed place in dynamic shared memory (behind the ring barriers), so
+// no function needs a pointer to it.
+__device__ __forceinline__ volatile uint32_t *abort_flag_ptr()
+{
+    extern __shared__ __align__(128) uint8_t dyn_smem[];
+    return reinterpret_cast<volatile uint32_t *>(dyn_smem + 2 * kMaxSlots * 8);
+}
+
 // Bounded waiting: expired() is called once per failed try; it looks at the abort flag and the
 // clock every 32nd time.
 struct Waiter {
     unsigned long long t0 = 0;
     uint32_t spins = 0;
-    __device__ __forceinline__ bool expired(const ChainArgs &a, volatile uint32_t *abort_flag)
+    __device__ __forceinline__ bool expired(const ChainArgs &a)
     {
+        volatile uint32_t *abort_flag = abort_flag_ptr();
         if ((++spins & 31u) != 0) return false;
         if (*abort_flag) return true;
         const unsigned long long now = global_ns();
@@ -135,11 +146,18 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, const ChainArgs &a, volatile uint32_t *abort_flag)
+// The common case (the phase has completed, or completes within try_wait's own suspend time) is two
+// instructions; the bounded spin with its clock reads stays out of line so that it costs the callers
+// neither registers nor instruction-cache space.
+__device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity, const ChainArgs &a)
 {
     Waiter w;
     while (!mbar_try(bar, parity))
-        if (w.expired(a, abort_flag)) break;
+        if (w.expired(a)) break;
+}
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, const ChainArgs &a)
+{
+    if (!mbar_try(bar, parity)) mbar_wait_slow(bar, parity, a);
 }
 __device__ __forceinline__ void consumer_sync(uint32_t threads)
 {
@@ -164,10 +182,10 @@ __device__ __forceinline__ void st_elem(unsigned long long *p, float value, uint
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
-// This CTA's share of an op: a contiguous column range, cut into passes of `lanes` columns and ring
-// tiles of `ppt` passes.  Producer and consumers derive it from the same numbers.
+// This CTA's share of an op: a contiguous column range, cut into passes of `lanes` columns; a pass is
+// one ring tile.  Producer and consumers derive it from the same numbers.
 struct Share {
-    uint32_t c0, ncols, passes, tiles;
+    uint32_t c0, ncols, passes;
 };
 __device__ __forceinline__ Share share_of(const ChainOp &o)
 {
@@ -178,60 +196,155 @@ __device__ __forceinline__ Share share_of(const ChainOp &o)
     s.c0 = u0 * o.col_align;
     s.ncols = (u1 - u0) * o.col_align;
     s.passes = (s.ncols + o.lanes - 1) / o.lanes;
-    s.tiles = (s.passes + o.ppt - 1) / o.ppt;
     return s;
 }
 
-// The 32 activations of block b out of a gathered {value, stamp} vector: poll the first and the last
-// piece, then read the block until every element carries this token's stamp.
-__device__ __forceinline__ void acquire_stamped(const unsigned long long *xs, uint32_t b, uint32_t stamp, const ChainArgs &a,
-                                                volatile uint32_t *abort_flag, float (&v)[32])
+__device__ __forceinline__ void wait_counter(const ChainOp &o, unsigned long long target, const ChainArgs &a)
 {
-    const ulonglong2 *src = reinterpret_cast<const ulonglong2 *>(xs + 32u * b);
+    if (!o.wait_for) return;
     Waiter w;
-    for (;;) {
-        const ulonglong2 p = ld_pair2(src), q = ld_pair2(src + 15);
-        if (((uint32_t)(p.x >> 32) == stamp) & ((uint32_t)(p.y >> 32) == stamp) & ((uint32_t)(q.x >> 32) == stamp) &
-            ((uint32_t)(q.y >> 32) == stamp)) break;
-        if (w.expired(a, abort_flag)) break;
-    }
-    for (;;) {
-        uint32_t ok = 1;
-#pragma unroll
-        for (int j = 0; j < 16; j++) {
-            const ulonglong2 p = ld_pair2(src + j);
-            v[2 * j] = __uint_as_float((uint32_t)p.x);
-            v[2 * j + 1] = __uint_as_float((uint32_t)p.y);
-            ok &= ((uint32_t)(p.x >> 32) == stamp) & ((uint32_t)(p.y >> 32) == stamp);
+    while (ld_acquire_u64(a.done + (o.wait_for - 1)) < target)
+        if (w.expired(a)) break;
+}
+
+// One warp fetches the activations of its blocks [b0, b0 + nb), nb <= 32, together: consecutive lanes
+// read consecutive 16-byte pieces (whole 128-byte lines per instruction instead of one line per lane),
+// the values go through a shared-memory stage (rows of 33 words, free of bank conflicts both ways)
+// and lane l leaves with the 32 activations of block b0 + l.  Stamped vectors are first polled at the
+// first and last piece of each block, then fetched until every stamp matches.
+__device__ __forceinline__ void warp_fetch_x(const ChainOp &o, uint32_t b0, uint32_t nb, uint32_t stamp, unsigned long long target,
+                                             const ChainArgs &a, uint32_t *stage, float (&v)[32])
+{
+    const uint32_t lane = threadIdx.x & 31u;
+    if (o.xs) {
+        const ulonglong2 *src = reinterpret_cast<const ulonglong2 *>(o.xs + 32u * b0);     // 16 pieces of two elements per block
+        Waiter w;
+        for (;;) {
+            uint32_t ok = 1;
+            if (lane < nb) {
+                const ulonglong2 p = ld_pair2(src + 16u * lane), q = ld_pair2(src + 16u * lane + 15u);
+                ok = ((uint32_t)(p.x >> 32) == stamp) & ((uint32_t)(p.y >> 32) == stamp) & ((uint32_t)(q.x >> 32) == stamp) &
+                     ((uint32_t)(q.y >> 32) == stamp);
+            }
+            if (__all_sync(0xffffffffu, ok)) break;
+            if (__any_sync(0xffffffffu, w.expired(a))) break;
         }
-        if (ok) break;
-        if (w.expired(a, abort_flag)) break;
+        const uint32_t pieces = nb * 16u;
+        for (;;) {
+            uint32_t ok = 1;
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const uint32_t p = (uint32_t)j * 32u + lane;
+                if (p < pieces) {
+                    const ulonglong2 e = ld_pair2(src + p);
+                    ok &= ((uint32_t)(e.x >> 32) == stamp) & ((uint32_t)(e.y >> 32) == stamp);
+                    uint32_t *dst = stage + (p >> 4) * 33u + 2u * (p & 15u);
+                    dst[0] = (uint32_t)e.x;
+                    dst[1] = (uint32_t)e.y;
+                }
+            }
+            if (__all_sync(0xffffffffu, ok)) break;
+            if (__any_sync(0xffffffffu, w.expired(a))) break;
+        }
+    } else {
+        if (lane == 0) wait_counter(o, target, a);
+        __syncwarp();
+        const float4 *src = reinterpret_cast<const float4 *>(o.x + 32u * b0);              // 8 pieces of four values per block
+        const uint32_t pieces = nb * 8u;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const uint32_t p = (uint32_t)j * 32u + lane;
+            if (p < pieces) {
+                const float4 e = __ldcg(src + p);
+                uint32_t *dst = stage + (p >> 3) * 33u + 4u * (p & 7u);
+                dst[0] = __float_as_uint(e.x); dst[1] = __float_as_uint(e.y); dst[2] = __float_as_uint(e.z); dst[3] = __float_as_uint(e.w);
+            }
+        }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(stage[(lane < nb ? lane : 0u) * 33u + i]);
+    __syncwarp();                                   // the stage may be overwritten (prepared planes go to the same place)
+}
+
+// The producer: one thread streams this CTA's share of every op's weights into the ring.  Its own
+// function (not inlined) so that its loop state is allocated apart from the consumers' registers.
+__device__ __noinline__ void produce(const ChainArgs &a, const ChainOp *s_ops, uint32_t full0, uint32_t empty0, uint32_t ring0)
+{
+    uint32_t slot = 0, fill = 0;           // slot to fill next, and how often the ring has wrapped
+    uint32_t wslot = 0, wfill = 0;         // the tile `window` positions behind it
+    uint32_t seq = 0;
+    for (uint32_t op = 0; op < a.n_ops; op++) {
+        const ChainOp &o = op < a.n_cached ? s_ops[op] : a.ops[op];
+        const Share sh = share_of(o);
+        // per op: where this CTA's range starts and how large a full tile is; per tile only the
+        // waits, the copies and a few additions remain (the loop is one thread's latency chain)
+        const bool q4 = o.fmt == MGQ_FMT_Q4;
+        const uint32_t bpc = o.bpc, hdr_off = o.hdr_off;
+        const unsigned long long first = (unsigned long long)sh.c0 * bpc;
+        const uint8_t *src_a = q4 ? o.w + o.num_blocks * 4ull + first * 16ull : o.w + first * 36ull;
+        const uint8_t *src_h = o.w + first * 4ull;
+        uint32_t blocks_left = sh.ncols * bpc;
+        const uint32_t tile_blocks = o.lanes * bpc;
+        for (uint32_t tile = 0; tile < sh.passes; tile++, seq++) {
+            if (fill) mbar_wait(empty0 + 8u * slot, (fill - 1u) & 1u, a);
+            if (seq >= a.window) {
+                mbar_wait(full0 + 8u * wslot, wfill & 1u, a);
+                if (++wslot == a.slots) { wslot = 0; wfill++; }
+            }
+            const uint32_t blocks = min(tile_blocks, blocks_left);
+            blocks_left -= blocks;
+            const uint32_t bar = full0 + 8u * slot, dst = ring0 + slot * a.slot_bytes;
+            if (q4) {
+                mbar_expect(bar, blocks * 20u);
+                bulk_load(dst, src_a, blocks * 16u, bar);
+                bulk_load(dst + hdr_off, src_h, blocks * 4u, bar);
+                src_a += (size_t)tile_blocks * 16u;
+                src_h += (size_t)tile_blocks * 4u;
+            } else {
+                mbar_expect(bar, blocks * 36u);
+                bulk_load(dst, src_a, blocks * 36u, bar);
+                src_a += (size_t)tile_blocks * 36u;
+            }
+            if (++slot == a.slots) { slot = 0; fill++; }
+        }
+    }
+    // Copies still in flight must land before the CTA may exit (the consumers normally wait for
+    // every tile themselves; after an abort they may not have).
+    if (*abort_flag_ptr()) {
+        for (uint32_t back = 0; back < a.slots && back < seq; back++) {
+            const uint32_t s = (slot + a.slots - 1u - back) % a.slots;
+            const uint32_t f = s < slot ? fill : fill - 1u;
+            const unsigned long long t0 = global_ns();
+            while (!mbar_try(full0 + 8u * s, f & 1u))
+                if (global_ns() - t0 > a.deadline_ns) break;
+        }
     }
 }
 
-__device__ __forceinline__ void acquire_plain(const ChainOp &o, uint32_t b, unsigned long long target, const ChainArgs &a,
-                                              volatile uint32_t *abort_flag, float (&v)[32])
+// Once per op and thread: fetch (with the dependency wait), turn into byte planes.  Not inlined: the 32
+// raw activations and the conversion's temporaries stay in this function's own frame.
+__device__ __noinline__ void fetch_prepare_shared(const ChainOp &o, uint32_t w0, uint32_t stamp, unsigned long long target,
+                                                  const ChainArgs &a, uint32_t *stage)
 {
-    if (o.wait_for) {
-        Waiter w;
-        while (ld_acquire_u64(a.done + (o.wait_for - 1)) < target)
-            if (w.expired(a, abort_flag)) break;
-    }
-    const float4 *xp = reinterpret_cast<const float4 *>(o.x + 32u * b);
+    const uint32_t lane = threadIdx.x & 31u;
+    float v[32];
+    XBlock xb;
+    warp_fetch_x(o, w0, min(32u, o.bpc - w0), stamp, target, a, stage, v);
+    if (o.fmt == MGQ_FMT_Q4) prepare_x<1>(v, xb); else prepare_x<0>(v, xb);
+    uint32_t *dst = stage + lane;
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
-        const float4 q = __ldcg(xp + j);
-        v[4 * j + 0] = q.x; v[4 * j + 1] = q.y; v[4 * j + 2] = q.z; v[4 * j + 3] = q.w;
-    }
+    for (int i = 0; i < 8; i++) { dst[i * 32] = xb.p0[i]; dst[(8 + i) * 32] = xb.p1[i]; dst[(16 + i) * 32] = xb.p2[i]; }
+    dst[24 * 32] = __float_as_uint(xb.inv);
+    dst[25 * 32] = __float_as_uint(xb.sum);
 }
 
 template <int TC>
-__global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const ChainArgs a)
+__global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const __grid_constant__ ChainArgs a)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     // [barriers 256 B][op descriptors][shared activations][reduction 2 x kRound x TC floats][ring]
     unsigned long long *bars = reinterpret_cast<unsigned long long *>(smem);       // full[slots], empty[slots]
-    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + 2 * kMaxSlots * 8);
     ChainOp *s_ops = reinterpret_cast<ChainOp *>(smem + 384);
     uint32_t *s_xchg = reinterpret_cast<uint32_t *>(smem + 384 + (size_t)a.n_cached * sizeof(ChainOp));
     float *s_red = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(s_xchg) + a.xchg_bytes);
@@ -244,7 +357,7 @@ __global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const ChainArgs a)
             mbar_init(full0 + 8u * s, 1u);
             mbar_init(empty0 + 8u * s, TC / 32u);
         }
-        *abort_flag = 0u;
+        *abort_flag_ptr() = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     {
@@ -252,54 +365,12 @@ __global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const ChainArgs a)
         uint4 *dst = reinterpret_cast<uint4 *>(s_ops);
         for (uint32_t i = t; i < a.n_cached * (uint32_t)(sizeof(ChainOp) / 16); i += blockDim.x) dst[i] = __ldg(src + i);
     }
-    const unsigned long long epoch = *reinterpret_cast<volatile const unsigned long long *>(a.epoch);
-    const uint32_t stamp = (uint32_t)epoch + 1u;
+    const uint32_t stamp = (uint32_t)*reinterpret_cast<volatile const unsigned long long *>(a.epoch) + 1u;
     __syncthreads();
 
     if (t >= TC) {
         // ------------------------------------------------------------------ producer
-        if (t == TC) {
-            uint32_t slot = 0, fill = 0;           // slot to fill next, and how often the ring has wrapped
-            uint32_t wslot = 0, wfill = 0;         // the tile `window` positions behind it
-            uint32_t seq = 0;
-            for (uint32_t op = 0; op < a.n_ops; op++) {
-                const ChainOp &o = op < a.n_cached ? s_ops[op] : a.ops[op];
-                const Share sh = share_of(o);
-                const uint32_t tile_cols = o.ppt * o.lanes;
-                for (uint32_t tile = 0; tile < sh.tiles; tile++, seq++) {
-                    if (fill) mbar_wait(empty0 + 8u * slot, (fill - 1u) & 1u, a, abort_flag);
-                    if (seq >= a.window) {
-                        mbar_wait(full0 + 8u * wslot, wfill & 1u, a, abort_flag);
-                        if (++wslot == a.slots) { wslot = 0; wfill++; }
-                    }
-                    const uint32_t col = sh.c0 + tile * tile_cols;
-                    const uint32_t cols = min(tile_cols, sh.c0 + sh.ncols - col);
-                    const unsigned long long first = (unsigned long long)col * o.bpc;       // first block of the tile
-                    const uint32_t blocks = cols * o.bpc;
-                    const uint32_t bar = full0 + 8u * slot, dst = ring0 + slot * a.slot_bytes;
-                    if (o.fmt == MGQ_FMT_Q4) {
-                        mbar_expect(bar, blocks * 20u);
-                        bulk_load(dst, o.w + o.num_blocks * 4ull + first * 16ull, blocks * 16u, bar);
-                        bulk_load(dst + o.hdr_off, o.w + first * 4ull, blocks * 4u, bar);
-                    } else {
-                        mbar_expect(bar, blocks * 36u);
-                        bulk_load(dst, o.w + first * 36ull, blocks * 36u, bar);
-                    }
-                    if (++slot == a.slots) { slot = 0; fill++; }
-                }
-            }
-            // Copies still in flight must land before the CTA may exit (the consumers normally wait for
-            // every tile themselves; after an abort they may not have).
-            if (*abort_flag) {
-                for (uint32_t back = 0; back < a.slots && back < seq; back++) {
-                    const uint32_t s = (slot + a.slots - 1u - back) % a.slots;
-                    const uint32_t f = s < slot ? fill : fill - 1u;
-                    const unsigned long long t0 = global_ns();
-                    while (!mbar_try(full0 + 8u * s, f & 1u))
-                        if (global_ns() - t0 > a.deadline_ns) break;
-                }
-            }
-        }
+        if (t == TC) produce(a, s_ops, full0, empty0, ring0);
         __syncwarp();                               // the other lanes of the producer warp wait here for the elected one
     } else {
         // ------------------------------------------------------------------ consumers
@@ -311,78 +382,70 @@ __global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const ChainArgs a)
             const uint32_t o_arrive = o.arrive;
             if (sh.ncols != 0) {
                 // the fields the pass loop needs, in registers (the descriptor itself stays in shared memory)
-                const uint32_t bpc = o.bpc, o_active = o.active, o_lanes = o.lanes, o_ppt = o.ppt, o_hdr = o.hdr_off;
-                const uint32_t o_shift = o.red_shift, o_chunk = o.red_chunk;
-                const float *o_addend = o.addend;
-                float *o_y = o.y;
-                const ExchangePush *o_push = o.push;
-                const bool has_block = t < o_active;
+                const uint32_t bpc = o.bpc, o_lanes = o.lanes, o_hdr = o.hdr_off, o_shift = o.red_shift;
+                const bool has_block = t < o.active;
                 const uint32_t b = t % bpc, lane_col = t / bpc;
                 const bool q4 = o.fmt == MGQ_FMT_Q4;
 
+                // ---- which column sum this thread finishes after each round (same for every round);
+                //      worked out before the activations are waited for
+                uint32_t fin_src, fin_cnt, fin_rel;          // staging offset, partials to add, column inside a round
+                bool fin_writer;
+                {
+                    const uint32_t chunk = o.red_chunk;
+                    const uint32_t fin = t >> o_shift, li = t & ((1u << o_shift) - 1u);
+                    const bool valid = fin < (uint32_t)kRound * o_lanes;
+                    const uint32_t fu = valid ? fin / o_lanes : 0u, fj = valid ? fin % o_lanes : 0u;
+                    const uint32_t first = li * chunk;
+                    fin_cnt = (valid && first < bpc) ? min(chunk, bpc - first) : 0u;
+                    fin_src = fu * TC + fj * bpc + first;
+                    fin_rel = fu * o_lanes + fj;
+                    fin_writer = valid && li == 0;
+                    if (!((bpc % 4u == 0u) && (chunk % 4u == 0u))) fin_cnt |= 0x80000000u;     // top bit: scalar reads
+                }
+
                 // ---- activations of this thread's block, as byte planes in registers
                 XBlock xb;
-                if (o.share_x ? t < bpc : has_block) {
-                    float v[32];
-                    if (o.xs) acquire_stamped(o.xs, b, stamp, a, abort_flag, v);
-                    else      acquire_plain(o, b, (unsigned long long)G * (epoch + 1ull), a, abort_flag, v);
-                    if (q4) prepare_x<1>(v, xb); else prepare_x<0>(v, xb);
-                    if (o.share_x) {
-                        uint32_t *dst = s_xchg + (t >> 5) * (26u * 32u) + lane;
-#pragma unroll
-                        for (int i = 0; i < 8; i++) { dst[i * 32] = xb.p0[i]; dst[(8 + i) * 32] = xb.p1[i]; dst[(16 + i) * 32] = xb.p2[i]; }
-                        dst[24 * 32] = __float_as_uint(xb.inv);
-                        dst[25 * 32] = __float_as_uint(xb.sum);
-                    }
-                }
-                if (o.share_x) {
+                const unsigned long long target = (unsigned long long)G * stamp;
+                {
+                    // the first bpc threads fetch and prepare (a warp at a time, 32 blocks each), everyone reads the planes
+                    const uint32_t w0 = (t >> 5) * 32u;
+                    if (w0 < bpc) fetch_prepare_shared(o, w0, stamp, target, a, s_xchg + (t >> 5) * kStageWords);
                     consumer_sync(TC);
-                    const uint32_t *src = s_xchg + (b >> 5) * (26u * 32u) + (b & 31u);
+                    const uint32_t *src = s_xchg + (b >> 5) * kStageWords + (b & 31u);
 #pragma unroll
                     for (int i = 0; i < 8; i++) { xb.p0[i] = src[i * 32]; xb.p1[i] = src[(8 + i) * 32]; xb.p2[i] = src[(16 + i) * 32]; }
                     xb.inv = __uint_as_float(src[24 * 32]);
                     xb.sum = __uint_as_float(src[25 * 32]);
                 }
 
-                // ---- which column sum this thread finishes after each round (same for every round)
-                const uint32_t R = 1u << o_shift;
-                const uint32_t fin = t >> o_shift, li = t & (R - 1u);
-                const bool fin_valid = fin < (uint32_t)kRound * o_lanes;
-                const uint32_t fin_u = fin_valid ? fin / o_lanes : 0u, fin_j = fin_valid ? fin % o_lanes : 0u;
-                const uint32_t fin_first = li * o_chunk;
-                const uint32_t fin_cnt = (fin_valid && fin_first < bpc) ? min(o_chunk, bpc - fin_first) : 0u;
-                const uint32_t fin_src = fin_u * TC + fin_j * bpc + fin_first;
-                const bool fin_vec = (bpc % 4u == 0u) && (o_chunk % 4u == 0u);
-                // where published columns go (read early: the descriptor lives in global memory)
-                uint32_t pub_cols = 0, pub_world = 0, pub_rank = 0;
-                if (o_push && fin_valid && li == 0) {
-                    pub_cols = o_push->gather_cols; pub_world = o_push->world; pub_rank = o_push->rank;
-                }
-
                 for (uint32_t pass0 = 0; pass0 < sh.passes; pass0 += kRound, round++) {
+                    // the addend of the column this thread will store at the end of the round: asked for now
+                    const uint32_t rel = pass0 * o_lanes + fin_rel;                          // column inside this CTA's range
+                    const bool store = fin_writer && rel < sh.ncols;
+                    float add = 0.f;
+                    if (store && o.addend) add = __ldcg(o.addend + sh.c0 + rel);
                     float part[kRound];
 #pragma unroll
                     for (int u = 0; u < kRound; u++) {
                         part[u] = 0.f;
                         const uint32_t pass = pass0 + u;
                         if (pass < sh.passes) {                                   // CTA-uniform
-                            const uint32_t p = pass % o_ppt;
-                            if (p == 0) mbar_wait(full0 + 8u * slot, fill & 1u, a, abort_flag);
+                            // one lane per warp watches the barrier (32 lanes trying cost 32 shared-memory accesses)
+                            if (lane == 0) mbar_wait(full0 + 8u * slot, fill & 1u, a);
+                            __syncwarp();
                             const uint8_t *tile = ring + (size_t)slot * a.slot_bytes;
-                            const uint32_t idx = p * o_active + t;
                             const bool live = has_block && pass * o_lanes + lane_col < sh.ncols;
                             if (q4) {
                                 uint4 q = make_uint4(0, 0, 0, 0);
                                 uint32_t h = 0;
                                 if (live) {
-                                    q = reinterpret_cast<const uint4 *>(tile)[idx];
-                                    h = reinterpret_cast<const uint32_t *>(tile + o_hdr)[idx];
+                                    q = reinterpret_cast<const uint4 *>(tile)[t];
+                                    h = reinterpret_cast<const uint32_t *>(tile + o_hdr)[t];
                                 }
-                                if (p + 1 == o_ppt || pass + 1 == sh.passes) {   // last pass of the tile: hand the slot back
-                                    __syncwarp();
-                                    if (lane == 0) mbar_arrive(empty0 + 8u * slot);
-                                    if (++slot == a.slots) { slot = 0; fill++; }
-                                }
+                                __syncwarp();                                     // the data is in registers: hand the slot back
+                                if (lane == 0) mbar_arrive(empty0 + 8u * slot);
+                                if (++slot == a.slots) { slot = 0; fill++; }
                                 if (live) {
                                     const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&h));
                                     part[u] = fmaf(dm.x * xb.inv, dot_q4(q, xb), dm.y * xb.sum);
@@ -392,15 +455,13 @@ __global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const ChainArgs a)
 #pragma unroll
                                 for (int i = 0; i < 9; i++) c[i] = 0;
                                 if (live) {
-                                    const uint32_t *bp = reinterpret_cast<const uint32_t *>(tile) + idx * 9u;
+                                    const uint32_t *bp = reinterpret_cast<const uint32_t *>(tile) + t * 9u;
 #pragma unroll
                                     for (int i = 0; i < 9; i++) c[i] = bp[i];
                                 }
-                                if (p + 1 == o_ppt || pass + 1 == sh.passes) {
-                                    __syncwarp();
-                                    if (lane == 0) mbar_arrive(empty0 + 8u * slot);
-                                    if (++slot == a.slots) { slot = 0; fill++; }
-                                }
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(empty0 + 8u * slot);
+                                if (++slot == a.slots) { slot = 0; fill++; }
                                 if (live) {
                                     const float scale = __half2float(__ushort_as_half((unsigned short)(c[0] & 0xFFFFu)));
                                     part[u] = scale * xb.inv * dot_q8(c + 1, xb);
@@ -415,28 +476,27 @@ __global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const ChainArgs a)
                     consumer_sync(TC);
                     float s = 0.f;
                     const float *src = red + fin_src;
-                    if (fin_vec) {
+                    if (!(fin_cnt & 0x80000000u)) {
                         for (uint32_t j = 0; j < fin_cnt; j += 4) {
                             const float4 q = *reinterpret_cast<const float4 *>(src + j);
                             s += (q.x + q.y) + (q.z + q.w);
                         }
                     } else {
-                        for (uint32_t j = 0; j < fin_cnt; j++) s += src[j];
+                        for (uint32_t j = 0; j < (fin_cnt & 0x7FFFFFFFu); j++) s += src[j];
                     }
                     if (o_shift > 4) s += __shfl_xor_sync(0xffffffffu, s, 16);
                     if (o_shift > 3) s += __shfl_xor_sync(0xffffffffu, s, 8);
                     if (o_shift > 2) s += __shfl_xor_sync(0xffffffffu, s, 4);
                     if (o_shift > 1) s += __shfl_xor_sync(0xffffffffu, s, 2);
                     if (o_shift > 0) s += __shfl_xor_sync(0xffffffffu, s, 1);
-                    const uint32_t rel = (pass0 + fin_u) * o_lanes + fin_j;                  // column inside this CTA's range
-                    if (fin_valid && li == 0 && rel < sh.ncols) {
+                    if (store) {                           // the descriptor is in shared memory: nothing of it is held in registers
                         const uint32_t col = sh.c0 + rel;
-                        const float v = o_addend ? s + __ldcg(o_addend + col) : s;
-                        o_y[col] = v;
+                        const float v = o.addend ? s + add : s;
+                        o.y[col] = v;
+                        const uint32_t pub_cols = o.pub_cols;
                         if (col < pub_cols) {
-                            const size_t at = (size_t)pub_rank * pub_cols + col;
-                            for (uint32_t q = 0; q < pub_world; q++)
-                                st_elem(reinterpret_cast<unsigned long long *>(o_push->dst[q]) + at, v, stamp);
+                            const size_t at = (size_t)o.pub_rank * pub_cols + col;
+                            for (uint32_t q = 0; q < o.pub_world; q++) st_elem(o.pub_dst[q] + at, v, stamp);
                         }
                     }
                 }
@@ -456,7 +516,7 @@ __global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const ChainArgs a)
                     unsigned long long e;
                     asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(e) : "l"(a.final_vec + i) : "memory");
                     if ((uint32_t)(e >> 32) == stamp) break;
-                    if (w.expired(a, abort_flag)) break;
+                    if (w.expired(a)) break;
                 }
             }
         }
@@ -466,7 +526,7 @@ __global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const ChainArgs a)
         __threadfence();
         if (atomicAdd(a.finish, 1u) == G - 1u) {
             atomicExch(a.finish, 0u);
-            *reinterpret_cast<volatile unsigned long long *>(a.epoch) = epoch + 1ull;
+            *reinterpret_cast<volatile unsigned long long *>(a.epoch) = *reinterpret_cast<volatile unsigned long long *>(a.epoch) + 1ull;
             __threadfence();
         }
     }
@@ -475,9 +535,7 @@ __global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const ChainArgs a)
 // ------------------------------------------------------------------------------- host side
 
 struct PlanTuning {
-    int consumers = 0;          // "plan.consumer_threads": 512 or 768 (0: 768)
     int window = 0;             // "plan.window_tiles": ring tiles in flight (0: automatic)
-    int slot_kb = 0;            // "plan.tile_kb": target size of a ring tile in KB (0: automatic)
     long deadline_us = 0;       // "plan.deadline_us": limit of every device-side wait (0: 20000)
 };
 PlanTuning g_plan_tuning;
@@ -496,15 +554,14 @@ int shape_op(ChainOp &d, size_t i, uint32_t tc, uint32_t tile_target)
     d.col_align = 4u / gcd_u32(bpc, 4u);
     uint32_t lanes = tc / bpc;
     lanes -= lanes % d.col_align;
-    if (lanes == 0)
-        return fail(MGQ_ERR_SHAPE, "op %zu: K=%u is outside the plan kernel's range (256 <= K <= %u)", i, d.k, tc / d.col_align * 32u);
+    if (lanes == 0 || bpc > kMaxBpc)
+        return fail(MGQ_ERR_SHAPE, "op %zu: K=%u is outside the plan kernel's range (256 <= K <= %u)", i, d.k,
+                    (tc / d.col_align < kMaxBpc ? tc / d.col_align : kMaxBpc) * 32u);
     d.lanes = lanes;
     d.active = lanes * bpc;
     const uint32_t per_block = d.fmt == MGQ_FMT_Q4 ? 20u : 36u;
-    const uint32_t pass_bytes = d.active * per_block;
-    d.ppt = 1;
-    while (d.ppt < (uint32_t)kRound && pass_bytes * d.ppt * 2u <= tile_target) d.ppt *= 2;
-    d.hdr_off = d.ppt * d.active * 16u;
+    (void)per_block; (void)tile_target;
+    d.hdr_off = d.active * 16u;
     // finishing lanes per column: a power of two, at most 32, as many as a round leaves room for;
     // all of it follows from K and the consumer count, so a column's sum does not depend on N
     const uint32_t cols_per_round = (uint32_t)kRound * lanes;
@@ -513,7 +570,6 @@ int shape_op(ChainOp &d, size_t i, uint32_t tc, uint32_t tile_target)
     const uint32_t fl = 1u << d.red_shift;
     d.red_chunk = (bpc + fl - 1) / fl;
     if (d.red_chunk % 4 != 0 && bpc % 4 == 0 && d.red_chunk > 4) d.red_chunk = (d.red_chunk + 3u) & ~3u;
-    d.share_x = lanes >= 2 ? 1u : 0u;
     return MGQ_OK;
 }
 
@@ -547,12 +603,10 @@ int layout_for(const ChainOp *ops, size_t count, uint32_t tc, int optin, Layout 
     uint32_t slot = 0, xchg = 0;
     for (size_t i = 0; i < count; i++) {
         const ChainOp &d = ops[i];
-        const uint32_t tile = d.ppt * d.active * (d.fmt == MGQ_FMT_Q4 ? 20u : 36u);
+        const uint32_t tile = d.active * (d.fmt == MGQ_FMT_Q4 ? 20u : 36u);
         slot = tile > slot ? tile : slot;
-        if (d.share_x) {
-            const uint32_t need = (d.bpc + 31u) / 32u * 26u * 32u * 4u;
-            xchg = need > xchg ? need : xchg;
-        }
+        const uint32_t need = (d.bpc + 31u) / 32u * kStageWords * 4u;
+        xchg = need > xchg ? need : xchg;
     }
     L.tc = tc;
     L.slot_bytes = (slot + 127u) & ~127u;
@@ -579,7 +633,7 @@ unsigned long long deadline_ns()
     return (unsigned long long)us * 1000ull;
 }
 
-void *kernel_for(uint32_t tc) { return tc == 512 ? (void *)chain_kernel<512> : (void *)chain_kernel<768>; }
+void *kernel_for(uint32_t) { return (void *)chain_kernel<768>; }
 
 struct DeviceFacts { int device = 0, sms = 0, optin = 0; };
 int device_facts(DeviceFacts &f)
@@ -590,22 +644,16 @@ int device_facts(DeviceFacts &f)
     return MGQ_OK;
 }
 
-uint32_t consumer_threads() { return g_plan_tuning.consumers == 512 ? 512u : 768u; }
-uint32_t tile_target() { return g_plan_tuning.slot_kb > 0 ? (uint32_t)g_plan_tuning.slot_kb * 1024u : 16384u; }
+uint32_t consumer_threads() { return 768u; }
+uint32_t tile_target() { return 16384u; }
 
 }  // namespace
 
 int set_plan_option(const char *name, long value)
 {
-    if (!std::strcmp(name, "plan.consumer_threads")) {
-        if (value != 0 && value != 512 && value != 768) return fail(MGQ_ERR_SHAPE, "%s must be 0, 512 or 768", name);
-        g_plan_tuning.consumers = (int)value;
-    } else if (!std::strcmp(name, "plan.window_tiles")) {
+    if (!std::strcmp(name, "plan.window_tiles")) {
         if (value < 0 || value > 15) return fail(MGQ_ERR_SHAPE, "%s out of range", name);
         g_plan_tuning.window = (int)value;
-    } else if (!std::strcmp(name, "plan.tile_kb")) {
-        if (value < 0 || value > 64) return fail(MGQ_ERR_SHAPE, "%s out of range", name);
-        g_plan_tuning.slot_kb = (int)value;
     } else if (!std::strcmp(name, "plan.deadline_us")) {
         if (value < 0 || value > 10000000) return fail(MGQ_ERR_SHAPE, "%s out of range", name);
         g_plan_tuning.deadline_us = value;
@@ -655,7 +703,15 @@ int create_plan(const mgq_plan_op *ops, const mgq_plan_link *links, size_t count
         if (int rc = shape_op(d, i, tc, tile_target())) return rc;
         d.wait_for = o.wait_for > i ? (uint32_t)i : o.wait_for;
         if (links) {
-            d.push = reinterpret_cast<const ExchangePush *>(links[i].push_dev);
+            if (links[i].push_dev) {
+                // the caller's record lives in device memory: read it once, keep its contents in the descriptor
+                ExchangePush rec;
+                MGQ_CUDA(cudaMemcpy(&rec, links[i].push_dev, sizeof rec, cudaMemcpyDeviceToHost));
+                if (rec.world < 1 || rec.world > (uint32_t)kMaxPeers || rec.rank >= rec.world || rec.gather_cols > o.n)
+                    return fail(MGQ_ERR_SHAPE, "op %zu: bad exchange record (world=%u rank=%u gather_cols=%u)", i, rec.world, rec.rank, rec.gather_cols);
+                d.pub_world = rec.world; d.pub_rank = rec.rank; d.pub_cols = rec.gather_cols;
+                for (uint32_t q = 0; q < rec.world; q++) d.pub_dst[q] = reinterpret_cast<unsigned long long *>(rec.dst[q]);
+            }
             d.xs = reinterpret_cast<const unsigned long long *>(links[i].wait_vec);
             if (d.xs) d.wait_for = 0;
             if (reinterpret_cast<uintptr_t>(d.xs) % 16 != 0) return fail(MGQ_ERR_ALIGN, "op %zu: the gathered vector must be 16-byte aligned", i);
@@ -681,10 +737,9 @@ int create_plan(const mgq_plan_op *ops, const mgq_plan_link *links, size_t count
     Layout L;
     if (int rc = layout_for(host.data(), count, tc, df.optin, L)) return rc;
 
-    // device block: [ChainOp x count][ExchangePush x count][done u64 x count][epoch u64, error u32, finish u32][vectors]
+    // device block: [ChainOp x count][done u64 x count][epoch u64, error u32, finish u32][vectors]
     size_t off = 0;
     const size_t ops_off = off;      off += count * sizeof(ChainOp);
-    const size_t push_off = off;     off += count * sizeof(ExchangePush);
     const size_t done_off = off;     off += count * sizeof(unsigned long long);
     const size_t state_off = off;    off += 64;
     off = (off + 255) & ~(size_t)255;
@@ -709,13 +764,10 @@ int create_plan(const mgq_plan_op *ops, const mgq_plan_link *links, size_t count
     if (!rc) rc = cuda_check((int)cudaMemset(pl->dev_block, 0, off), "cudaMemset", __FILE__, __LINE__);
     if (rc) { delete pl; return rc; }
     (void)vec_off;
-    std::vector<ExchangePush> pushes(count);
-    std::memset(pushes.data(), 0, count * sizeof(ExchangePush));
     for (size_t j = 0; j < count; j++) {
         if (!publish[j]) continue;
-        pushes[j].world = 1; pushes[j].rank = 0; pushes[j].gather_cols = publish[j];
-        pushes[j].dst[0] = reinterpret_cast<float2 *>(pl->dev_block + vec_at[j]);
-        host[j].push = reinterpret_cast<const ExchangePush *>(pl->dev_block + push_off) + j;
+        host[j].pub_world = 1; host[j].pub_rank = 0; host[j].pub_cols = publish[j];
+        host[j].pub_dst[0] = reinterpret_cast<unsigned long long *>(pl->dev_block + vec_at[j]);
     }
     for (size_t i = 0; i < count; i++)
         if (source[i] >= 0) {
@@ -730,7 +782,6 @@ int create_plan(const mgq_plan_op *ops, const mgq_plan_link *links, size_t count
             if (host[i].wait_for) host[host[i].wait_for - 1].arrive = 1;
         }
     if (!rc) rc = cuda_check((int)cudaMemcpy(pl->dev_block + ops_off, host.data(), count * sizeof(ChainOp), cudaMemcpyHostToDevice), "cudaMemcpy", __FILE__, __LINE__);
-    if (!rc) rc = cuda_check((int)cudaMemcpy(pl->dev_block + push_off, pushes.data(), count * sizeof(ExchangePush), cudaMemcpyHostToDevice), "cudaMemcpy", __FILE__, __LINE__);
     int occ = 0;
     if (!rc) rc = cuda_check((int)cudaFuncSetAttribute(pl->kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, df.optin), "cudaFuncSetAttribute", __FILE__, __LINE__);
     if (!rc) rc = cuda_check((int)cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, pl->kernel, (int)tc + 32, L.smem), "occupancy", __FILE__, __LINE__);
@@ -859,7 +910,6 @@ int static_setup(StaticSetup *&out)
         MGQ_CUDA(cudaGetSymbolAddress(&ptr, g_static_plan_scratch));
         MGQ_CUDA(cudaDeviceGetAttribute(&st.sms, cudaDevAttrMultiProcessorCount, dev));
         MGQ_CUDA(cudaDeviceGetAttribute(&st.optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-        MGQ_CUDA(cudaFuncSetAttribute(mgq::chain_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, st.optin));
         MGQ_CUDA(cudaFuncSetAttribute(mgq::chain_kernel<768>, cudaFuncAttributeMaxDynamicSharedMemorySize, st.optin));
         st.scratch = static_cast<unsigned char *>(ptr);
         st.ready = true;

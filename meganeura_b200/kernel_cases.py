@@ -4,6 +4,7 @@
     python -m meganeura_b200.kernel_cases gemm q8 512x4096x14336 [--launches 3]
     python -m meganeura_b200.kernel_cases sweep q4            # the SmolLM2-135M decode shapes
     python -m meganeura_b200.kernel_cases decode qwen3-8b --layers 4 --steps 4 [--context 2048]
+    python -m meganeura_b200.kernel_cases chain q4 --layers 4 [--launches 3] [--no-head]   # the persistent plan kernel
 
 `gemv` rotates through enough distinct weight copies to exceed L2 several times over and replays
 the launches from a CUDA graph, so the printed GB/s is a streaming (cold-cache) figure; with
@@ -88,6 +89,34 @@ def gemm_case(fmt, m, k, n, launches=0):
     return tf
 
 
+def chain_case(fmt, layers, launches, head=True, peak_gbs=None):
+    """The decode GEMV chain (Qwen3-8B shapes, `layers` layers, optionally without the lm_head) as one
+    persistent plan kernel per token: `launches` plain launches for a profiler, else a timed loop."""
+    from . import decode_chain as dc
+    chain = dc.DecodeGemvChain(dc.QWEN3_8B, fmt, layers=layers, mode="plan")
+    if not head:
+        chain.ops_list.pop()
+    chain._build_plan()
+    nbytes = sum(dc.gemv_bytes(fmt, 1, op["spec"].k, op["n_loc"], op["spec"].residual) for op in chain.ops_list)
+    for _ in range(max(launches, 3)):
+        chain.plan.launch()
+    chain.plan.check()
+    if launches:
+        return None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        chain.plan.launch()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / 20
+    gbs = nbytes / us / 1e3
+    tail = f" ({gbs / peak_gbs * 100:.1f}% of {peak_gbs:.0f})" if peak_gbs else ""
+    print(f"chain {'Q4' if fmt == FMT_Q4 else 'Q8'} {layers} layers{' + lm_head' if head else ''}: {len(chain.ops_list)} GEMVs, "
+          f"{nbytes / 1e6:.1f} MB, {us:.1f} us per launch, {gbs:.1f} GB/s{tail}  {chain.plan.info()}")
+    return gbs
+
+
 def decode_case(model, layers, steps, context):
     """A few whole decode steps of a shortened model through the session (plain launches, no graph):
     what a profiler capture of the decode-step operators wants."""
@@ -110,7 +139,7 @@ def decode_case(model, layers, steps, context):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kind", choices=["gemv", "gemm", "sweep", "decode"])
+    ap.add_argument("kind", choices=["gemv", "gemm", "sweep", "decode", "chain"])
     ap.add_argument("fmt", help="q4 | q8, or the model for `decode` (qwen3-8b | smollm2-135m)")
     ap.add_argument("shape", nargs="?", default="")
     ap.add_argument("--launches", type=int, default=0)
@@ -120,6 +149,7 @@ def main():
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--no-head", action="store_true", help="chain: leave the lm_head out (a small profiler case)")
     args = ap.parse_args()
     if args.kind == "decode":
         if args.fmt not in ("qwen3-8b", "smollm2-135m"):
@@ -133,7 +163,9 @@ def main():
         warm @ warm
     torch.cuda.synchronize()
     del warm
-    if args.kind == "sweep":
+    if args.kind == "chain":
+        chain_case(fmt, args.layers, args.launches, head=not args.no_head, peak_gbs=args.peak_gbs)
+    elif args.kind == "sweep":
         for k, n in SMOLLM2_SHAPES:
             gemv_case(fmt, k, n, peak_gbs=args.peak_gbs, hot=args.hot)
     elif args.kind == "gemv":

@@ -58,7 +58,7 @@ def test_small_ops_leave_ctas_idle(coracle):
 def test_replay_rearms_the_barriers(coracle):
     plan = _chain(coracle, (O.FMT_Q8, O.FMT_Q4), [1024, 2048, 1024], replays=5)
     info = plan.info()
-    assert info["threads"] in (544, 800) and info["grid"] >= 100 and info["ring_slots"] >= 3
+    assert info["threads"] == 800 and info["grid"] >= 100 and info["ring_slots"] >= 3
 
 
 def test_plan_inside_cuda_graph(coracle):
@@ -128,15 +128,9 @@ def test_consumer_of_a_column_range(coracle):
     assert O.rel_l2(y2.cpu().numpy(), coracle.matmul(O.FMT_Q4, mid[:, 256:256 + k2], w2, k2, n2, wide=True)) <= 1e-4
 
 
-@pytest.mark.parametrize("threads", [512, 768])
-def test_consumer_thread_counts(coracle, threads):
-    from meganeura_b200 import ops
-    ops.set_option("plan.consumer_threads", threads)
-    try:
-        plan = _chain(coracle, (O.FMT_Q4, O.FMT_Q8), [4096, 1536, 12288, 576, 1024], addend_at=(2,), replays=2)
-        assert plan.info()["threads"] == threads + 32
-    finally:
-        ops.set_option("plan.consumer_threads", 0)
+def test_wide_and_narrow_ops_share_one_plan(coracle):
+    plan = _chain(coracle, (O.FMT_Q4, O.FMT_Q8), [4096, 1536, 12288, 576, 1024], addend_at=(2,), replays=2)
+    assert plan.info()["threads"] == 800
 
 
 def test_wait_that_nothing_satisfies_times_out(coracle):

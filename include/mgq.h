@@ -235,9 +235,10 @@ int mgq_matmul_host(int fmt, const void *a_host, int a_dtype, const void *w_dev,
  * vector once every CTA has counted itself out of op wait_for - 1.  y always receives the plain
  * result.  An addend must be complete before the op that produces this op's activations starts.
  * All pointers are device pointers and must stay valid for the plan's lifetime.
- * Limits: m = 1, 256 <= K <= 12288, K*N/32 a multiple of 4, 16-byte aligned w and x.  Launches of one plan must not overlap.  Every device-side wait
+ * Limits: at most MGQ_PLAN_MAX_OPS ops (MGQ_ERR_SIZE beyond: split the list), m = 1, 256 <= K <= 12288, K*N/32 a multiple of 4, 16-byte aligned w and x.  Launches of one plan must not overlap.  Every device-side wait
  * has a time limit ("plan.deadline_us", default 20 ms), after which the launch finishes with
  * undefined results and mgq_plan_check reports MGQ_ERR_TIMEOUT. */
+#define MGQ_PLAN_MAX_OPS 152                 /* ops per plan (their descriptors are kept in shared memory) */
 typedef struct mgq_plan mgq_plan;
 typedef struct mgq_plan_op {
     int fmt;                 /* MGQ_FMT_Q4 / MGQ_FMT_Q8 */
@@ -285,7 +286,7 @@ int mgq_plan_create_linked(const mgq_plan_op *ops, const mgq_plan_link *links, s
  * `stream` and returns when they have finished (it synchronises the stream; MGQ_ERR_TIMEOUT if a
  * wait gave up).  It never calls cudaMalloc/cudaFree or any allocating routine: the kernel's
  * scratch -- op descriptors, arrival counters, token index, error word -- is a fixed device array
- * of MGQ_STATIC_PLAN_MAX_OPS entries (about 35 KB) that every GPU using the library holds until
+ * of MGQ_STATIC_PLAN_MAX_OPS entries (about 18 KB) that every GPU using the library holds until
  * the process exits; dependent ops wait on the arrival counters (no gathered vectors).  It is meant for callers that must not allocate on their execution path, e.g. a
  * serving loop with a fixed device-memory budget or a host application that forbids cudaMalloc after
  * start-up (it can synchronise the device and can fail when memory is tight).
@@ -299,7 +300,7 @@ int mgq_plan_create_linked(const mgq_plan_op *ops, const mgq_plan_link *links, s
  *   - All calls on a device share the one array, and it keeps the previous call's contents; the
  *     entry point rewrites the descriptors and zeroes the counters itself, but two calls that
  *     overlap on the same GPU (different streams or threads) race on it. */
-#define MGQ_STATIC_PLAN_MAX_OPS 256
+#define MGQ_STATIC_PLAN_MAX_OPS 128
 int mgq_plan_run_static(const mgq_plan_op *ops, size_t count, void *stream);
 
 /* ---- Graph / Session surface (src/graph.rs:714-795, src/train.rs:380-389,

@@ -10,8 +10,7 @@
 //     shared-memory ring with 1-D bulk copies (cp.async.bulk, completion counted on an mbarrier per
 //     slot).  Weights are immutable, so the producer does not wait for any dependency: it runs
 //     ahead across op boundaries until the ring is full, which keeps HBM streaming while the
-//     consumers wait for the previous op's results.  It keeps at most `window` tiles in flight:
-//     more would only queue in the memory system in front of the latency-critical activation loads.
+//     consumers wait for the previous op's results.
 //   * consumers (TC threads): thread t owns block-in-column b = t % bpc of column t / bpc of each
 //     pass, holds that block's activations in registers as byte planes (dp4a block dot products,
 //     mgq_gemv_device.cuh), takes tiles out of the ring, and finishes column sums through shared
@@ -43,20 +42,21 @@ namespace mgq {
 namespace {
 using namespace dev;
 
-constexpr int kRound = 4;                      // passes between two column reductions
-constexpr uint32_t kMaxCachedOps = 152;        // op descriptors kept in shared memory
+constexpr uint32_t kConsumers = 768;           // consumer threads per CTA (the producer warp comes on top)
+constexpr uint32_t kConsumerWarps = kConsumers / 32;
+constexpr uint32_t kMaxOps = MGQ_PLAN_MAX_OPS;  // every op descriptor of a plan is kept in shared memory
 constexpr uint32_t kStageWords = 32 * 33;      // per leader warp: 32 blocks x 32 activations, rows padded to 33 words
-constexpr uint32_t kMaxSlots = 16;
+constexpr uint32_t kMaxSlots = 16;             // 2 groups of at most 8 slots
 constexpr uint32_t kMaxBpc = 384;              // K <= 12288: the prepared activations of one op must fit their shared-memory stage
 
-struct ChainOp {                               // 192 bytes
+struct ChainOp {                               // 128 bytes
     const uint8_t *w;
     const float *x;                            // plain activations (when xs is null)
     const unsigned long long *xs;              // k {value, stamp} elements this op consumes, or null
     const float *addend;
     float *y;
+    unsigned long long *const *pub_tab;        // [pub_world] in global memory: rank p's gathered vector
     unsigned long long num_blocks;
-    unsigned long long *pub_dst[kMaxPeers];    // rank p's gathered vector (pub_world entries)
     uint32_t k, n, bpc, fmt;
     uint32_t lanes;                            // columns per pass
     uint32_t active;                           // lanes * bpc threads carry a block
@@ -65,16 +65,16 @@ struct ChainOp {                               // 192 bytes
     uint32_t wait_for;                         // plain activations: ops [0, wait_for) must have arrived (0: none)
     uint32_t arrive;                           // 1: CTAs count themselves in done[op] when they finish the op
     uint32_t red_shift, red_chunk;
-    uint32_t reserved1;
     uint32_t pub_cols, pub_world, pub_rank;    // leading columns published as {value, stamp}, to how many ranks, as which rank
-    uint32_t pad[4];
+    uint32_t ppt;                              // passes per ring tile: 1 or 2
+    uint32_t pad[2];
 };
-static_assert(sizeof(ChainOp) == 192, "ChainOp is copied in 16-byte pieces");
+static_assert(sizeof(ChainOp) == 128, "ChainOp is copied in 16-byte pieces");
 
 struct ChainArgs {
     const ChainOp *ops;
-    uint32_t n_ops, n_cached;
-    uint32_t slots, slot_bytes, window;
+    uint32_t n_ops;
+    uint32_t slot_bytes;
     uint32_t xchg_bytes;
     unsigned long long *epoch;                 // token index; the CTA that finishes last adds one
     unsigned long long *done;                  // [n_ops] arrival counters (monotonic: G per token)
@@ -159,6 +159,45 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, const C
 {
     if (!mbar_try(bar, parity)) mbar_wait_slow(bar, parity, a);
 }
+__device__ __forceinline__ void mbar_arrive_if(uint32_t bar, bool yes)
+{
+    asm volatile("{\n .reg .pred p;\n setp.ne.u32 p, %1, 0;\n @p mbarrier.arrive.shared::cta.b64 _, [%0];\n}\n"
+                 ::"r"(bar), "r"((uint32_t)yes) : "memory");
+}
+// Shared-memory loads by 32-bit shared address; volatile so that they stay between the barrier wait
+// before them and the arrival after them.
+__device__ __forceinline__ uint4 lds128(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+// Q4 block dot product with the three byte planes recombined in integer arithmetic: |sum| is at most
+// 15*32*(64*65536 + 255*256 + 255) < 2^31, so the exact sum fits and one conversion remains.
+__device__ __forceinline__ float dot_q4_exact(const uint4 &q, const XBlock &xb)
+{
+    const uint32_t wv[4] = {q.x, q.y, q.z, q.w};
+    int a0 = 0, a1 = 0, a2 = 0;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const uint32_t lo = wv[j] & 0x0F0F0F0Fu, hi = (wv[j] >> 4) & 0x0F0F0F0Fu;
+        a0 = dp4a_uu(lo, xb.p0[2 * j], a0);
+        a1 = dp4a_uu(lo, xb.p1[2 * j], a1);
+        a2 = dp4a_us(lo, xb.p2[2 * j], a2);
+        a0 = dp4a_uu(hi, xb.p0[2 * j + 1], a0);
+        a1 = dp4a_uu(hi, xb.p1[2 * j + 1], a1);
+        a2 = dp4a_us(hi, xb.p2[2 * j + 1], a2);
+    }
+    return (float)(a2 * 65536 + a1 * 256 + a0);
+}
+
 __device__ __forceinline__ void consumer_sync(uint32_t threads)
 {
     asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
@@ -182,8 +221,8 @@ __device__ __forceinline__ void st_elem(unsigned long long *p, float value, uint
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
-// This CTA's share of an op: a contiguous column range, cut into passes of `lanes` columns; a pass is
-// one ring tile.  Producer and consumers derive it from the same numbers.
+// This CTA's share of an op: a contiguous column range, cut into passes of `lanes` columns; a ring
+// tile holds `ppt` passes (1 or 2).  Producer and consumers derive it from the same numbers.
 struct Share {
     uint32_t c0, ncols, passes;
 };
@@ -267,18 +306,25 @@ __device__ __forceinline__ void warp_fetch_x(const ChainOp &o, uint32_t b0, uint
     __syncwarp();                                   // the stage may be overwritten (prepared planes go to the same place)
 }
 
+// Ring layout.  A round is R passes (R tiles) followed by one column reduction; the ring has two
+// groups of R slots and round r (counted over all ops) uses group r & 1, its p-th pass slot
+// R * (r & 1) + p, for the (r >> 1)-th time.  An op's last round may hold fewer than R passes: the
+// slots it does not use are simply skipped that time.  So a slot's index and barrier parity follow
+// from the round counter alone -- neither side keeps ring state or computes a wrap -- and every
+// address inside a round is the round's base plus a compile-time multiple of the slot size.
+
 // The producer: one thread streams this CTA's share of every op's weights into the ring.  Its own
 // function (not inlined) so that its loop state is allocated apart from the consumers' registers.
-__device__ __noinline__ void produce(const ChainArgs &a, const ChainOp *s_ops, uint32_t full0, uint32_t empty0, uint32_t ring0)
+template <int R>
+__device__ __noinline__ void produce(const ChainArgs &a, const ChainOp *s_ops, uint32_t full0, uint32_t ring0)
 {
-    uint32_t slot = 0, fill = 0;           // slot to fill next, and how often the ring has wrapped
-    uint32_t wslot = 0, wfill = 0;         // the tile `window` positions behind it
-    uint32_t seq = 0;
+    const uint32_t empty0 = full0 + 2u * R * 8u;
+    uint32_t round = 0;
     for (uint32_t op = 0; op < a.n_ops; op++) {
-        const ChainOp &o = op < a.n_cached ? s_ops[op] : a.ops[op];
+        const ChainOp &o = s_ops[op];
         const Share sh = share_of(o);
         // per op: where this CTA's range starts and how large a full tile is; per tile only the
-        // waits, the copies and a few additions remain (the loop is one thread's latency chain)
+        // wait, the copies and a few additions remain (the loop is one thread's latency chain)
         const bool q4 = o.fmt == MGQ_FMT_Q4;
         const uint32_t bpc = o.bpc, hdr_off = o.hdr_off;
         const unsigned long long first = (unsigned long long)sh.c0 * bpc;
@@ -286,44 +332,57 @@ __device__ __noinline__ void produce(const ChainArgs &a, const ChainOp *s_ops, u
         const uint8_t *src_h = o.w + first * 4ull;
         uint32_t blocks_left = sh.ncols * bpc;
         const uint32_t tile_blocks = o.lanes * bpc;
-        for (uint32_t tile = 0; tile < sh.passes; tile++, seq++) {
-            if (fill) mbar_wait(empty0 + 8u * slot, (fill - 1u) & 1u, a);
-            if (seq >= a.window) {
-                mbar_wait(full0 + 8u * wslot, wfill & 1u, a);
-                if (++wslot == a.slots) { wslot = 0; wfill++; }
+        for (uint32_t pass0 = 0; pass0 < sh.passes; pass0 += R, round++) {
+            const uint32_t group = (round & 1u) * R, use = round >> 1;
+            const uint32_t n = min((uint32_t)R, sh.passes - pass0);
+            for (uint32_t p = 0; p < n; p++) {
+                const uint32_t slot = group + p;
+                if (use) mbar_wait(empty0 + 8u * slot, (use - 1u) & 1u, a);
+                const uint32_t blocks = min(tile_blocks, blocks_left);
+                blocks_left -= blocks;
+                const uint32_t bar = full0 + 8u * slot, dst = ring0 + slot * a.slot_bytes;
+                if (q4) {
+                    mbar_expect(bar, blocks * 20u);
+                    bulk_load(dst, src_a, blocks * 16u, bar);
+                    bulk_load(dst + hdr_off, src_h, blocks * 4u, bar);
+                    src_a += (size_t)tile_blocks * 16u;
+                    src_h += (size_t)tile_blocks * 4u;
+                } else {
+                    mbar_expect(bar, blocks * 36u);
+                    bulk_load(dst, src_a, blocks * 36u, bar);
+                    src_a += (size_t)tile_blocks * 36u;
+                }
             }
-            const uint32_t blocks = min(tile_blocks, blocks_left);
-            blocks_left -= blocks;
-            const uint32_t bar = full0 + 8u * slot, dst = ring0 + slot * a.slot_bytes;
-            if (q4) {
-                mbar_expect(bar, blocks * 20u);
-                bulk_load(dst, src_a, blocks * 16u, bar);
-                bulk_load(dst + hdr_off, src_h, blocks * 4u, bar);
-                src_a += (size_t)tile_blocks * 16u;
-                src_h += (size_t)tile_blocks * 4u;
-            } else {
-                mbar_expect(bar, blocks * 36u);
-                bulk_load(dst, src_a, blocks * 36u, bar);
-                src_a += (size_t)tile_blocks * 36u;
+            // slots of the group that this round leaves out: nobody will wait for or release them this
+            // time, so their barriers are stepped here to keep every slot's parity equal to use & 1
+            for (uint32_t p = n; p < (uint32_t)R; p++) {
+                const uint32_t slot = group + p;
+                if (use) mbar_wait(empty0 + 8u * slot, (use - 1u) & 1u, a);
+                mbar_arrive(full0 + 8u * slot);                       // completes the "full" phase with no bytes
+                for (uint32_t w = 0; w < kConsumerWarps; w++) mbar_arrive(empty0 + 8u * slot);
             }
-            if (++slot == a.slots) { slot = 0; fill++; }
         }
     }
     // Copies still in flight must land before the CTA may exit (the consumers normally wait for
-    // every tile themselves; after an abort they may not have).
-    if (*abort_flag_ptr()) {
-        for (uint32_t back = 0; back < a.slots && back < seq; back++) {
-            const uint32_t s = (slot + a.slots - 1u - back) % a.slots;
-            const uint32_t f = s < slot ? fill : fill - 1u;
+    // every tile themselves; after an abort they may not have).  Every slot's last use has been
+    // issued above; wait for the phase each slot is in, with the same deadline.
+    if (*abort_flag_ptr() && round) {
+        const uint32_t last = round - 1u;
+        for (uint32_t s = 0; s < 2u * R; s++) {
+            const uint32_t g = s / R;
+            if (g > last) continue;                                    // group never used
+            const uint32_t r_last = ((last & 1u) == g) ? last : last - 1u;
             const unsigned long long t0 = global_ns();
-            while (!mbar_try(full0 + 8u * s, f & 1u))
+            while (!mbar_try(full0 + 8u * s, (r_last >> 1) & 1u))
                 if (global_ns() - t0 > a.deadline_ns) break;
         }
     }
 }
 
-// Once per op and thread: fetch (with the dependency wait), turn into byte planes.  Not inlined: the 32
-// raw activations and the conversion's temporaries stay in this function's own frame.
+// Once per op, by the first bpc threads a warp at a time: fetch 32 blocks of activations (with the
+// dependency wait), turn them into byte planes and leave the planes in the warp's stage for
+// everyone.  Not inlined: the raw activations and the conversion's temporaries stay in this
+// function's own frame.
 __device__ __noinline__ void fetch_prepare_shared(const ChainOp &o, uint32_t w0, uint32_t stamp, unsigned long long target,
                                                   const ChainArgs &a, uint32_t *stage)
 {
@@ -339,23 +398,23 @@ __device__ __noinline__ void fetch_prepare_shared(const ChainOp &o, uint32_t w0,
     dst[25 * 32] = __float_as_uint(xb.sum);
 }
 
-template <int TC>
-__global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const __grid_constant__ ChainArgs a)
+template <int R>
+__global__ void __launch_bounds__(kConsumers + 32, 1) chain_kernel(const __grid_constant__ ChainArgs a)
 {
+    constexpr uint32_t TC = kConsumers;
     extern __shared__ __align__(128) uint8_t smem[];
-    // [barriers 256 B][op descriptors][shared activations][reduction 2 x kRound x TC floats][ring]
-    unsigned long long *bars = reinterpret_cast<unsigned long long *>(smem);       // full[slots], empty[slots]
+    // [barriers + abort flag 384 B][op descriptors][activation stages][reduction 2 x R x TC floats][ring 2 x R slots]
     ChainOp *s_ops = reinterpret_cast<ChainOp *>(smem + 384);
-    uint32_t *s_xchg = reinterpret_cast<uint32_t *>(smem + 384 + (size_t)a.n_cached * sizeof(ChainOp));
+    uint32_t *s_xchg = reinterpret_cast<uint32_t *>(smem + 384 + (size_t)a.n_ops * sizeof(ChainOp));
     float *s_red = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(s_xchg) + a.xchg_bytes);
-    uint8_t *ring = reinterpret_cast<uint8_t *>(s_red) + (size_t)2 * kRound * TC * sizeof(float);
     const uint32_t t = threadIdx.x, G = gridDim.x;
-    const uint32_t full0 = smem_u32(bars), empty0 = full0 + a.slots * 8u, ring0 = smem_u32(ring);
+    const uint32_t full0 = smem_u32(smem), empty0 = full0 + 2u * R * 8u;
+    const uint32_t ring0 = smem_u32(s_red) + 2u * R * TC * (uint32_t)sizeof(float);
 
     if (t == 0) {
-        for (uint32_t s = 0; s < a.slots; s++) {
+        for (uint32_t s = 0; s < 2u * R; s++) {
             mbar_init(full0 + 8u * s, 1u);
-            mbar_init(empty0 + 8u * s, TC / 32u);
+            mbar_init(empty0 + 8u * s, kConsumerWarps);
         }
         *abort_flag_ptr() = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -363,26 +422,26 @@ __global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const __grid_constant
     {
         const uint4 *src = reinterpret_cast<const uint4 *>(a.ops);
         uint4 *dst = reinterpret_cast<uint4 *>(s_ops);
-        for (uint32_t i = t; i < a.n_cached * (uint32_t)(sizeof(ChainOp) / 16); i += blockDim.x) dst[i] = __ldg(src + i);
+        for (uint32_t i = t; i < a.n_ops * (uint32_t)(sizeof(ChainOp) / 16); i += blockDim.x) dst[i] = __ldg(src + i);
     }
     const uint32_t stamp = (uint32_t)*reinterpret_cast<volatile const unsigned long long *>(a.epoch) + 1u;
     __syncthreads();
 
     if (t >= TC) {
         // ------------------------------------------------------------------ producer
-        if (t == TC) produce(a, s_ops, full0, empty0, ring0);
+        if (t == TC) produce<R>(a, s_ops, full0, ring0);
         __syncwarp();                               // the other lanes of the producer warp wait here for the elected one
     } else {
         // ------------------------------------------------------------------ consumers
         const uint32_t lane = t & 31u;
-        uint32_t slot = 0, fill = 0, round = 0;
+        const bool elected = lane == 0;
+        uint32_t round = 0;
         for (uint32_t op = 0; op < a.n_ops; op++) {
-            const ChainOp &o = op < a.n_cached ? s_ops[op] : a.ops[op];
+            const ChainOp &o = s_ops[op];
             const Share sh = share_of(o);
-            const uint32_t o_arrive = o.arrive;
             if (sh.ncols != 0) {
                 // the fields the pass loop needs, in registers (the descriptor itself stays in shared memory)
-                const uint32_t bpc = o.bpc, o_lanes = o.lanes, o_hdr = o.hdr_off, o_shift = o.red_shift;
+                const uint32_t bpc = o.bpc, o_lanes = o.lanes, o_shift = o.red_shift;
                 const bool has_block = t < o.active;
                 const uint32_t b = t % bpc, lane_col = t / bpc;
                 const bool q4 = o.fmt == MGQ_FMT_Q4;
@@ -394,7 +453,7 @@ __global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const __grid_constant
                 {
                     const uint32_t chunk = o.red_chunk;
                     const uint32_t fin = t >> o_shift, li = t & ((1u << o_shift) - 1u);
-                    const bool valid = fin < (uint32_t)kRound * o_lanes;
+                    const bool valid = fin < (uint32_t)R * o_lanes;
                     const uint32_t fu = valid ? fin / o_lanes : 0u, fj = valid ? fin % o_lanes : 0u;
                     const uint32_t first = li * chunk;
                     fin_cnt = (valid && first < bpc) ? min(chunk, bpc - first) : 0u;
@@ -404,13 +463,12 @@ __global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const __grid_constant
                     if (!((bpc % 4u == 0u) && (chunk % 4u == 0u))) fin_cnt |= 0x80000000u;     // top bit: scalar reads
                 }
 
-                // ---- activations of this thread's block, as byte planes in registers
+                // ---- activations of this thread's block, as byte planes in registers: the first bpc threads
+                //      fetch and prepare (a warp at a time, 32 blocks each), everyone reads the planes
                 XBlock xb;
-                const unsigned long long target = (unsigned long long)G * stamp;
                 {
-                    // the first bpc threads fetch and prepare (a warp at a time, 32 blocks each), everyone reads the planes
                     const uint32_t w0 = (t >> 5) * 32u;
-                    if (w0 < bpc) fetch_prepare_shared(o, w0, stamp, target, a, s_xchg + (t >> 5) * kStageWords);
+                    if (w0 < bpc) fetch_prepare_shared(o, w0, stamp, (unsigned long long)G * stamp, a, s_xchg + (t >> 5) * kStageWords);
                     consumer_sync(TC);
                     const uint32_t *src = s_xchg + (b >> 5) * kStageWords + (b & 31u);
 #pragma unroll
@@ -419,63 +477,88 @@ __global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const __grid_constant
                     xb.sum = __uint_as_float(src[25 * 32]);
                 }
 
-                for (uint32_t pass0 = 0; pass0 < sh.passes; pass0 += kRound, round++) {
-                    // the addend of the column this thread will store at the end of the round: asked for now
-                    const uint32_t rel = pass0 * o_lanes + fin_rel;                          // column inside this CTA's range
-                    const bool store = fin_writer && rel < sh.ncols;
-                    float add = 0.f;
-                    if (store && o.addend) add = __ldcg(o.addend + sh.c0 + rel);
-                    float part[kRound];
+                // shared-memory offsets of this thread's block inside a ring slot; threads beyond `active`
+                // shadow the last active thread in full rounds (nothing reads what they produce)
+                const uint32_t tt = has_block ? t : o.active - 1u;
+                const uint32_t off_a = q4 ? tt * 16u : tt * 36u, off_h = o.hdr_off + tt * 4u;
+
+                for (uint32_t pass0 = 0; pass0 < sh.passes; pass0 += R, round++) {
+                    const uint32_t group = (round & 1u) * R, parity = (round >> 1) & 1u;
+                    const uint32_t tile0 = ring0 + group * a.slot_bytes, full_g = full0 + 8u * group, empty_g = empty0 + 8u * group;
+                    // partial sums go straight to the staging buffer of this round (nothing is held across passes)
+                    float *part = s_red + (size_t)(round & 1u) * R * TC + t;
+                    if ((pass0 + R) * o_lanes <= sh.ncols) {
+                        // full round: R whole passes, no predicates.  The warp is converged, so the loads of all its
+                        // lanes are one instruction that precedes the elected lane's arrival in program order.
+                        if (q4) {
 #pragma unroll
-                    for (int u = 0; u < kRound; u++) {
-                        part[u] = 0.f;
-                        const uint32_t pass = pass0 + u;
-                        if (pass < sh.passes) {                                   // CTA-uniform
-                            // one lane per warp watches the barrier (32 lanes trying cost 32 shared-memory accesses)
-                            if (lane == 0) mbar_wait(full0 + 8u * slot, fill & 1u, a);
-                            __syncwarp();
-                            const uint8_t *tile = ring + (size_t)slot * a.slot_bytes;
-                            const bool live = has_block && pass * o_lanes + lane_col < sh.ncols;
-                            if (q4) {
+                            for (int u = 0; u < R; u++) {
+                                mbar_wait(full_g + 8u * u, parity, a);
+                                const uint32_t tile = tile0 + (uint32_t)u * a.slot_bytes;
+                                const uint4 q = lds128(tile + off_a);
+                                const uint32_t h = lds32(tile + off_h);
+                                mbar_arrive_if(empty_g + 8u * u, elected);
+                                const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&h));
+                                part[u * TC] = fmaf(dm.x * xb.inv, dot_q4_exact(q, xb), dm.y * xb.sum);
+                            }
+                        } else {
+#pragma unroll
+                            for (int u = 0; u < R; u++) {
+                                mbar_wait(full_g + 8u * u, parity, a);
+                                const uint32_t tile = tile0 + (uint32_t)u * a.slot_bytes + off_a;
+                                uint32_t c[9];
+#pragma unroll
+                                for (int i = 0; i < 9; i++) c[i] = lds32(tile + 4u * i);
+                                mbar_arrive_if(empty_g + 8u * u, elected);
+                                const float scale = __half2float(__ushort_as_half((unsigned short)(c[0] & 0xFFFFu)));
+                                part[u * TC] = scale * xb.inv * dot_q8(c + 1, xb);
+                            }
+                        }
+                    } else {
+                        // last round of the op: fewer than R passes, or a last pass with fewer columns
+#pragma unroll
+                        for (int u = 0; u < R; u++) {
+                            part[u * TC] = 0.f;
+                            const uint32_t pass = pass0 + u;
+                            if (pass < sh.passes) {                               // CTA-uniform
+                                mbar_wait(full_g + 8u * u, parity, a);
+                                const uint32_t tile = tile0 + (uint32_t)u * a.slot_bytes;
+                                const bool live = has_block && pass * o_lanes + lane_col < sh.ncols;
                                 uint4 q = make_uint4(0, 0, 0, 0);
-                                uint32_t h = 0;
-                                if (live) {
-                                    q = reinterpret_cast<const uint4 *>(tile)[t];
-                                    h = reinterpret_cast<const uint32_t *>(tile + o_hdr)[t];
-                                }
-                                __syncwarp();                                     // the data is in registers: hand the slot back
-                                if (lane == 0) mbar_arrive(empty0 + 8u * slot);
-                                if (++slot == a.slots) { slot = 0; fill++; }
-                                if (live) {
-                                    const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&h));
-                                    part[u] = fmaf(dm.x * xb.inv, dot_q4(q, xb), dm.y * xb.sum);
-                                }
-                            } else {
                                 uint32_t c[9];
 #pragma unroll
                                 for (int i = 0; i < 9; i++) c[i] = 0;
                                 if (live) {
-                                    const uint32_t *bp = reinterpret_cast<const uint32_t *>(tile) + t * 9u;
+                                    if (q4) {
+                                        q = lds128(tile + off_a);
+                                        c[0] = lds32(tile + off_h);
+                                    } else {
 #pragma unroll
-                                    for (int i = 0; i < 9; i++) c[i] = bp[i];
+                                        for (int i = 0; i < 9; i++) c[i] = lds32(tile + off_a + 4u * i);
+                                    }
                                 }
-                                __syncwarp();
-                                if (lane == 0) mbar_arrive(empty0 + 8u * slot);
-                                if (++slot == a.slots) { slot = 0; fill++; }
+                                __syncwarp();                                     // every lane's data is in registers: hand the slot back
+                                mbar_arrive_if(empty_g + 8u * u, elected);
                                 if (live) {
-                                    const float scale = __half2float(__ushort_as_half((unsigned short)(c[0] & 0xFFFFu)));
-                                    part[u] = scale * xb.inv * dot_q8(c + 1, xb);
+                                    if (q4) {
+                                        const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&c[0]));
+                                        part[u * TC] = fmaf(dm.x * xb.inv, dot_q4_exact(q, xb), dm.y * xb.sum);
+                                    } else {
+                                        const float scale = __half2float(__ushort_as_half((unsigned short)(c[0] & 0xFFFFu)));
+                                        part[u * TC] = scale * xb.inv * dot_q8(c + 1, xb);
+                                    }
                                 }
                             }
                         }
                     }
                     // ---- finish the round's columns
-                    float *red = s_red + (size_t)(round & 1u) * kRound * TC;
-#pragma unroll
-                    for (int u = 0; u < kRound; u++) red[u * TC + t] = part[u];
                     consumer_sync(TC);
+                    const uint32_t rel = pass0 * o_lanes + fin_rel;                          // column inside this CTA's range
+                    const bool store = fin_writer && rel < sh.ncols;
+                    float add = 0.f;
+                    if (store && o.addend) add = __ldcg(o.addend + sh.c0 + rel);             // in flight during the sums below
                     float s = 0.f;
-                    const float *src = red + fin_src;
+                    const float *src = s_red + (size_t)(round & 1u) * R * TC + fin_src;
                     if (!(fin_cnt & 0x80000000u)) {
                         for (uint32_t j = 0; j < fin_cnt; j += 4) {
                             const float4 q = *reinterpret_cast<const float4 *>(src + j);
@@ -484,11 +567,18 @@ __global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const __grid_constant
                     } else {
                         for (uint32_t j = 0; j < (fin_cnt & 0x7FFFFFFFu); j++) s += src[j];
                     }
-                    if (o_shift > 4) s += __shfl_xor_sync(0xffffffffu, s, 16);
-                    if (o_shift > 3) s += __shfl_xor_sync(0xffffffffu, s, 8);
-                    if (o_shift > 2) s += __shfl_xor_sync(0xffffffffu, s, 4);
-                    if (o_shift > 1) s += __shfl_xor_sync(0xffffffffu, s, 2);
-                    if (o_shift > 0) s += __shfl_xor_sync(0xffffffffu, s, 1);
+                    if (o_shift == 5) {                       // a whole warp per column
+                        s += __shfl_xor_sync(0xffffffffu, s, 16);
+                        s += __shfl_xor_sync(0xffffffffu, s, 8);
+                        s += __shfl_xor_sync(0xffffffffu, s, 4);
+                        s += __shfl_xor_sync(0xffffffffu, s, 2);
+                        s += __shfl_xor_sync(0xffffffffu, s, 1);
+                    } else {
+                        if (o_shift > 3) s += __shfl_xor_sync(0xffffffffu, s, 8);
+                        if (o_shift > 2) s += __shfl_xor_sync(0xffffffffu, s, 4);
+                        if (o_shift > 1) s += __shfl_xor_sync(0xffffffffu, s, 2);
+                        if (o_shift > 0) s += __shfl_xor_sync(0xffffffffu, s, 1);
+                    }
                     if (store) {                           // the descriptor is in shared memory: nothing of it is held in registers
                         const uint32_t col = sh.c0 + rel;
                         const float v = o.addend ? s + add : s;
@@ -496,12 +586,14 @@ __global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const __grid_constant
                         const uint32_t pub_cols = o.pub_cols;
                         if (col < pub_cols) {
                             const size_t at = (size_t)o.pub_rank * pub_cols + col;
-                            for (uint32_t q = 0; q < o.pub_world; q++) st_elem(o.pub_dst[q] + at, v, stamp);
+                            unsigned long long *const *tab = o.pub_tab;
+                            for (uint32_t q = 0; q < o.pub_world; q++)
+                                st_elem(reinterpret_cast<unsigned long long *>(__ldg(reinterpret_cast<const unsigned long long *>(tab + q))) + at, v, stamp);
                         }
                     }
                 }
             }
-            if (o_arrive) {
+            if (o.arrive) {
                 // publish this CTA's part of the op to readers of the plain vector: results, then the arrival
                 __threadfence();
                 consumer_sync(TC);
@@ -535,20 +627,19 @@ __global__ void __launch_bounds__(TC + 32, 1) chain_kernel(const __grid_constant
 // ------------------------------------------------------------------------------- host side
 
 struct PlanTuning {
-    int window = 0;             // "plan.window_tiles": ring tiles in flight (0: automatic)
     long deadline_us = 0;       // "plan.deadline_us": limit of every device-side wait (0: 20000)
 };
 PlanTuning g_plan_tuning;
 
 struct Layout {
-    uint32_t tc = 0, slots = 0, slot_bytes = 0, window = 0, xchg_bytes = 0, n_cached = 0;
+    uint32_t tc = 0, round = 0, slot_bytes = 0, xchg_bytes = 0;     // round: passes per round (the ring holds 2 * round slots)
     size_t smem = 0;
 };
 
 inline uint32_t gcd_u32(uint32_t a, uint32_t b) { while (b) { const uint32_t r = a % b; a = b; b = r; } return a; }
 
 // Fills the kernel-side fields of one op that depend only on its shape and the consumer count.
-int shape_op(ChainOp &d, size_t i, uint32_t tc, uint32_t tile_target)
+int shape_op(ChainOp &d, size_t i, uint32_t tc, uint32_t round)
 {
     const uint32_t bpc = d.bpc;
     d.col_align = 4u / gcd_u32(bpc, 4u);
@@ -559,12 +650,11 @@ int shape_op(ChainOp &d, size_t i, uint32_t tc, uint32_t tile_target)
                     (tc / d.col_align < kMaxBpc ? tc / d.col_align : kMaxBpc) * 32u);
     d.lanes = lanes;
     d.active = lanes * bpc;
-    const uint32_t per_block = d.fmt == MGQ_FMT_Q4 ? 20u : 36u;
-    (void)per_block; (void)tile_target;
+    d.ppt = 1;
     d.hdr_off = d.active * 16u;
     // finishing lanes per column: a power of two, at most 32, as many as a round leaves room for;
     // all of it follows from K and the consumer count, so a column's sum does not depend on N
-    const uint32_t cols_per_round = (uint32_t)kRound * lanes;
+    const uint32_t cols_per_round = round * lanes;
     d.red_shift = 0;
     while (d.red_shift < 5 && (cols_per_round << (d.red_shift + 1)) <= tc && (2u << d.red_shift) <= bpc) d.red_shift++;
     const uint32_t fl = 1u << d.red_shift;
@@ -597,8 +687,17 @@ void base_op(ChainOp &d, const mgq_plan_op &o)
     d.num_blocks = (unsigned long long)d.bpc * o.n;
 }
 
+// Passes per round for a list of ops: 4 when every op is Q4 (15 KB tiles), 2 when Q8 tiles (27 KB)
+// have to fit the ring as well.
+uint32_t round_for(const mgq_plan_op *ops, size_t count)
+{
+    for (size_t i = 0; i < count; i++)
+        if (ops[i].fmt == MGQ_FMT_Q8) return 2;
+    return 4;
+}
+
 // Shared-memory layout for a list of shaped ops.
-int layout_for(const ChainOp *ops, size_t count, uint32_t tc, int optin, Layout &L)
+int layout_for(const ChainOp *ops, size_t count, uint32_t tc, uint32_t round, int optin, Layout &L)
 {
     uint32_t slot = 0, xchg = 0;
     for (size_t i = 0; i < count; i++) {
@@ -609,21 +708,11 @@ int layout_for(const ChainOp *ops, size_t count, uint32_t tc, int optin, Layout 
         xchg = need > xchg ? need : xchg;
     }
     L.tc = tc;
+    L.round = round;
     L.slot_bytes = (slot + 127u) & ~127u;
     L.xchg_bytes = (xchg + 127u) & ~127u;
-    L.n_cached = count < kMaxCachedOps ? (uint32_t)count : kMaxCachedOps;
-    const size_t fixed = 384 + (size_t)L.n_cached * sizeof(ChainOp) + L.xchg_bytes + (size_t)2 * kRound * tc * sizeof(float);
-    if (fixed + 2 * (size_t)L.slot_bytes > (size_t)optin)
-        return fail(MGQ_ERR_SHAPE, "plan needs %zu B of shared memory, device allows %d", fixed + 2 * (size_t)L.slot_bytes, optin);
-    uint32_t slots = (uint32_t)(((size_t)optin - fixed) / L.slot_bytes);
-    if (slots > kMaxSlots) slots = kMaxSlots;
-    L.slots = slots;
-    // bytes in flight per SM: about what hides the HBM latency at full rate, not more
-    uint32_t window = g_plan_tuning.window > 0 ? (uint32_t)g_plan_tuning.window : (65536u + L.slot_bytes - 1) / L.slot_bytes;
-    if (window >= slots) window = slots - 1;
-    if (window < 1) window = 1;
-    L.window = window;
-    L.smem = fixed + (size_t)slots * L.slot_bytes;
+    L.smem = 384 + count * sizeof(ChainOp) + L.xchg_bytes + (size_t)2 * round * tc * sizeof(float) + (size_t)2 * round * L.slot_bytes;
+    if (L.smem > (size_t)optin) return fail(MGQ_ERR_SHAPE, "plan needs %zu B of shared memory, device allows %d", L.smem, optin);
     return MGQ_OK;
 }
 
@@ -633,7 +722,7 @@ unsigned long long deadline_ns()
     return (unsigned long long)us * 1000ull;
 }
 
-void *kernel_for(uint32_t) { return (void *)chain_kernel<768>; }
+void *kernel_for(uint32_t round) { return round == 4 ? (void *)chain_kernel<4> : (void *)chain_kernel<2>; }
 
 struct DeviceFacts { int device = 0, sms = 0, optin = 0; };
 int device_facts(DeviceFacts &f)
@@ -645,16 +734,12 @@ int device_facts(DeviceFacts &f)
 }
 
 uint32_t consumer_threads() { return 768u; }
-uint32_t tile_target() { return 16384u; }
 
 }  // namespace
 
 int set_plan_option(const char *name, long value)
 {
-    if (!std::strcmp(name, "plan.window_tiles")) {
-        if (value < 0 || value > 15) return fail(MGQ_ERR_SHAPE, "%s out of range", name);
-        g_plan_tuning.window = (int)value;
-    } else if (!std::strcmp(name, "plan.deadline_us")) {
+    if (!std::strcmp(name, "plan.deadline_us")) {
         if (value < 0 || value > 10000000) return fail(MGQ_ERR_SHAPE, "%s out of range", name);
         g_plan_tuning.deadline_us = value;
     } else {
@@ -687,10 +772,13 @@ int create_plan(const mgq_plan_op *ops, const mgq_plan_link *links, size_t count
 {
     if (!ops || !out) return fail(MGQ_ERR_NULL, "null argument");
     *out = nullptr;
-    if (count == 0 || count > 65535) return fail(MGQ_ERR_SHAPE, "a plan holds 1..65535 ops, got %zu", count);
-    const uint32_t tc = consumer_threads();
+    if (count == 0 || count > kMaxOps)
+        return fail(MGQ_ERR_SIZE, "a plan holds 1..%u ops (their descriptors live in shared memory), got %zu; split longer lists over several plans",
+                    kMaxOps, count);
+    const uint32_t tc = consumer_threads(), round = round_for(ops, count);
     std::vector<ChainOp> host(count);
     std::vector<uint32_t> publish(count, 0);        // columns op j publishes into a vector owned by the plan
+    std::vector<unsigned long long> tables(count * kMaxPeers, 0ull);   // per op: the gathered vector of every rank
     std::vector<int> source(count, -1);
     std::vector<size_t> source_off(count, 0);
     for (size_t i = 0; i < count; i++) {
@@ -700,7 +788,7 @@ int create_plan(const mgq_plan_op *ops, const mgq_plan_link *links, size_t count
         if (!o.x && !linked_x) return fail(MGQ_ERR_NULL, "op %zu: null activation pointer", i);
         ChainOp &d = host[i];
         base_op(d, o);
-        if (int rc = shape_op(d, i, tc, tile_target())) return rc;
+        if (int rc = shape_op(d, i, tc, round)) return rc;
         d.wait_for = o.wait_for > i ? (uint32_t)i : o.wait_for;
         if (links) {
             if (links[i].push_dev) {
@@ -710,7 +798,7 @@ int create_plan(const mgq_plan_op *ops, const mgq_plan_link *links, size_t count
                 if (rec.world < 1 || rec.world > (uint32_t)kMaxPeers || rec.rank >= rec.world || rec.gather_cols > o.n)
                     return fail(MGQ_ERR_SHAPE, "op %zu: bad exchange record (world=%u rank=%u gather_cols=%u)", i, rec.world, rec.rank, rec.gather_cols);
                 d.pub_world = rec.world; d.pub_rank = rec.rank; d.pub_cols = rec.gather_cols;
-                for (uint32_t q = 0; q < rec.world; q++) d.pub_dst[q] = reinterpret_cast<unsigned long long *>(rec.dst[q]);
+                for (uint32_t q = 0; q < rec.world; q++) tables[i * kMaxPeers + q] = reinterpret_cast<unsigned long long>(rec.dst[q]);
             }
             d.xs = reinterpret_cast<const unsigned long long *>(links[i].wait_vec);
             if (d.xs) d.wait_for = 0;
@@ -735,11 +823,12 @@ int create_plan(const mgq_plan_op *ops, const mgq_plan_link *links, size_t count
     DeviceFacts df;
     if (int rc = device_facts(df)) return rc;
     Layout L;
-    if (int rc = layout_for(host.data(), count, tc, df.optin, L)) return rc;
+    if (int rc = layout_for(host.data(), count, tc, round, df.optin, L)) return rc;
 
-    // device block: [ChainOp x count][done u64 x count][epoch u64, error u32, finish u32][vectors]
+    // device block: [ChainOp x count][destination tables 8 x u64 x count][done u64 x count][epoch u64, error u32, finish u32][vectors]
     size_t off = 0;
     const size_t ops_off = off;      off += count * sizeof(ChainOp);
+    const size_t tab_off = off;      off += count * kMaxPeers * sizeof(unsigned long long);
     const size_t done_off = off;     off += count * sizeof(unsigned long long);
     const size_t state_off = off;    off += 64;
     off = (off + 255) & ~(size_t)255;
@@ -755,7 +844,7 @@ int create_plan(const mgq_plan_op *ops, const mgq_plan_link *links, size_t count
     pl->device = df.device;
     pl->layout = L;
     pl->grid = (uint32_t)df.sms;
-    pl->kernel = kernel_for(tc);
+    pl->kernel = kernel_for(round);
     pl->dev_bytes = off;
     pl->state_off = done_off;
     pl->state_bytes = off - done_off;
@@ -765,10 +854,13 @@ int create_plan(const mgq_plan_op *ops, const mgq_plan_link *links, size_t count
     if (rc) { delete pl; return rc; }
     (void)vec_off;
     for (size_t j = 0; j < count; j++) {
-        if (!publish[j]) continue;
-        host[j].pub_world = 1; host[j].pub_rank = 0; host[j].pub_cols = publish[j];
-        host[j].pub_dst[0] = reinterpret_cast<unsigned long long *>(pl->dev_block + vec_at[j]);
+        if (publish[j]) {
+            host[j].pub_world = 1; host[j].pub_rank = 0; host[j].pub_cols = publish[j];
+            tables[j * kMaxPeers] = reinterpret_cast<unsigned long long>(pl->dev_block + vec_at[j]);
+        }
+        host[j].pub_tab = reinterpret_cast<unsigned long long *const *>(pl->dev_block + tab_off) + j * kMaxPeers;
     }
+    if (!rc) rc = cuda_check((int)cudaMemcpy(pl->dev_block + tab_off, tables.data(), tables.size() * sizeof(unsigned long long), cudaMemcpyHostToDevice), "cudaMemcpy", __FILE__, __LINE__);
     for (size_t i = 0; i < count; i++)
         if (source[i] >= 0) {
             host[i].xs = reinterpret_cast<const unsigned long long *>(pl->dev_block + vec_at[source[i]]) + source_off[i];
@@ -789,8 +881,8 @@ int create_plan(const mgq_plan_op *ops, const mgq_plan_link *links, size_t count
     if (rc) { mgq_plan_destroy(pl); return rc; }
     ChainArgs &a = pl->args;
     a.ops = reinterpret_cast<const ChainOp *>(pl->dev_block + ops_off);
-    a.n_ops = (uint32_t)count; a.n_cached = L.n_cached;
-    a.slots = L.slots; a.slot_bytes = L.slot_bytes; a.window = L.window; a.xchg_bytes = L.xchg_bytes;
+    a.n_ops = (uint32_t)count;
+    a.slot_bytes = L.slot_bytes; a.xchg_bytes = L.xchg_bytes;
     a.done = reinterpret_cast<unsigned long long *>(pl->dev_block + done_off);
     a.epoch = epoch ? epoch : reinterpret_cast<unsigned long long *>(pl->dev_block + state_off);
     a.error = error ? error : reinterpret_cast<unsigned int *>(pl->dev_block + state_off + 8);
@@ -851,7 +943,7 @@ int mgq_plan_info(const mgq_plan *pl, uint32_t *grid, uint32_t *threads, uint32_
     if (!pl) return fail(MGQ_ERR_NULL, "null plan");
     if (grid) *grid = pl->grid;
     if (threads) *threads = pl->layout.tc + 32;
-    if (ring_slots) *ring_slots = pl->layout.slots;
+    if (ring_slots) *ring_slots = 2 * pl->layout.round;
     if (smem_bytes) *smem_bytes = pl->layout.smem;
     return MGQ_OK;
 }
@@ -910,7 +1002,8 @@ int static_setup(StaticSetup *&out)
         MGQ_CUDA(cudaGetSymbolAddress(&ptr, g_static_plan_scratch));
         MGQ_CUDA(cudaDeviceGetAttribute(&st.sms, cudaDevAttrMultiProcessorCount, dev));
         MGQ_CUDA(cudaDeviceGetAttribute(&st.optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-        MGQ_CUDA(cudaFuncSetAttribute(mgq::chain_kernel<768>, cudaFuncAttributeMaxDynamicSharedMemorySize, st.optin));
+        MGQ_CUDA(cudaFuncSetAttribute(mgq::chain_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, st.optin));
+        MGQ_CUDA(cudaFuncSetAttribute(mgq::chain_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, st.optin));
         st.scratch = static_cast<unsigned char *>(ptr);
         st.ready = true;
     }
@@ -933,7 +1026,7 @@ extern "C" int mgq_plan_run_static(const mgq_plan_op *ops, size_t count, void *s
     MGQ_CUDA(cudaStreamIsCapturing(stream, &capturing));
     if (capturing != cudaStreamCaptureStatusNone)
         return fail(MGQ_ERR_STATE, "mgq_plan_run_static synchronises its stream and cannot be part of a stream capture");
-    const uint32_t tc = consumer_threads();
+    const uint32_t tc = consumer_threads(), round = round_for(ops, count);
     static thread_local ChainOp host_ops[kStaticMaxOps];      // fixed host staging, no heap
     for (size_t i = 0; i < count; i++) {
         const mgq_plan_op &o = ops[i];
@@ -941,7 +1034,7 @@ extern "C" int mgq_plan_run_static(const mgq_plan_op *ops, size_t count, void *s
         if (!o.x) return fail(MGQ_ERR_NULL, "op %zu: null activation pointer", i);
         ChainOp &d = host_ops[i];
         base_op(d, o);
-        if (int rc = shape_op(d, i, tc, tile_target())) return rc;
+        if (int rc = shape_op(d, i, tc, round)) return rc;
         d.wait_for = o.wait_for > i ? (uint32_t)i : o.wait_for;
     }
     for (size_t i = 0; i < count; i++)
@@ -949,8 +1042,8 @@ extern "C" int mgq_plan_run_static(const mgq_plan_op *ops, size_t count, void *s
     StaticSetup *st = nullptr;
     if (int rc = static_setup(st)) return rc;
     Layout L;
-    if (int rc = layout_for(host_ops, count, tc, st->optin, L)) return rc;      // depends on the list: worked out on every call
-    void *kernel = kernel_for(tc);
+    if (int rc = layout_for(host_ops, count, tc, round, st->optin, L)) return rc;      // depends on the list: worked out on every call
+    void *kernel = kernel_for(round);
     int occ = 0;
     MGQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, (int)tc + 32, L.smem));
     if (occ < 1) return fail(MGQ_ERR_CUDA, "plan kernel does not fit on an SM");
@@ -962,8 +1055,8 @@ extern "C" int mgq_plan_run_static(const mgq_plan_op *ops, size_t count, void *s
     MGQ_CUDA(cudaMemsetAsync(d_done, 0, kStaticDoneBytes + 256, stream));
     ChainArgs a{};
     a.ops = reinterpret_cast<const ChainOp *>(d_ops);
-    a.n_ops = (uint32_t)count; a.n_cached = L.n_cached;
-    a.slots = L.slots; a.slot_bytes = L.slot_bytes; a.window = L.window; a.xchg_bytes = L.xchg_bytes;
+    a.n_ops = (uint32_t)count;
+    a.slot_bytes = L.slot_bytes; a.xchg_bytes = L.xchg_bytes;
     a.done = reinterpret_cast<unsigned long long *>(d_done);
     a.epoch = reinterpret_cast<unsigned long long *>(d_state);
     a.error = reinterpret_cast<unsigned int *>(d_state + 8);

@@ -73,9 +73,9 @@ def test_static_plan_rejects_long_lists():
     x = torch.zeros((1, 256), device="cuda")
     y = torch.zeros((1, 64), device="cuda")
     w = torch.zeros(256 * 64 // 32 * 20, dtype=torch.uint8, device="cuda")
-    arr = _ops_array([(O.FMT_Q4, x, w, None, y, 256, 64, 0)] * 257)
-    status = _lib.lib.mgq_plan_run_static(arr, 257, torch.cuda.current_stream().cuda_stream)
+    arr = _ops_array([(O.FMT_Q4, x, w, None, y, 256, 64, 0)] * 129)
+    status = _lib.lib.mgq_plan_run_static(arr, 129, torch.cuda.current_stream().cuda_stream)
     assert status == 6                                      # MGQ_ERR_SIZE
-    assert "at most 256" in _lib.last_error()
+    assert "at most 128" in _lib.last_error()
     with pytest.raises(mg.MgqError):
         _lib.check(_lib.lib.mgq_plan_run_static(None, 1, None))

@@ -159,10 +159,11 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, const C
 {
     if (!mbar_try(bar, parity)) mbar_wait_slow(bar, parity, a);
 }
-__device__ __forceinline__ void mbar_arrive_if(uint32_t bar, bool yes)
+// Arrival by lane 0 only, as one predicated instruction (no branch).
+__device__ __forceinline__ void mbar_arrive_lane0(uint32_t bar, uint32_t lane)
 {
-    asm volatile("{\n .reg .pred p;\n setp.ne.u32 p, %1, 0;\n @p mbarrier.arrive.shared::cta.b64 _, [%0];\n}\n"
-                 ::"r"(bar), "r"((uint32_t)yes) : "memory");
+    asm volatile("{\n .reg .pred p;\n setp.eq.u32 p, %1, 0;\n @p mbarrier.arrive.shared::cta.b64 _, [%0];\n}\n"
+                 ::"r"(bar), "r"(lane) : "memory");
 }
 // Shared-memory loads by 32-bit shared address; volatile so that they stay between the barrier wait
 // before them and the arrival after them.
@@ -434,7 +435,6 @@ __global__ void __launch_bounds__(kConsumers + 32, 1) chain_kernel(const __grid_
     } else {
         // ------------------------------------------------------------------ consumers
         const uint32_t lane = t & 31u;
-        const bool elected = lane == 0;
         uint32_t round = 0;
         for (uint32_t op = 0; op < a.n_ops; op++) {
             const ChainOp &o = s_ops[op];
@@ -497,7 +497,7 @@ __global__ void __launch_bounds__(kConsumers + 32, 1) chain_kernel(const __grid_
                                 const uint32_t tile = tile0 + (uint32_t)u * a.slot_bytes;
                                 const uint4 q = lds128(tile + off_a);
                                 const uint32_t h = lds32(tile + off_h);
-                                mbar_arrive_if(empty_g + 8u * u, elected);
+                                mbar_arrive_lane0(empty_g + 8u * u, lane);
                                 const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&h));
                                 part[u * TC] = fmaf(dm.x * xb.inv, dot_q4_exact(q, xb), dm.y * xb.sum);
                             }
@@ -509,7 +509,7 @@ __global__ void __launch_bounds__(kConsumers + 32, 1) chain_kernel(const __grid_
                                 uint32_t c[9];
 #pragma unroll
                                 for (int i = 0; i < 9; i++) c[i] = lds32(tile + 4u * i);
-                                mbar_arrive_if(empty_g + 8u * u, elected);
+                                mbar_arrive_lane0(empty_g + 8u * u, lane);
                                 const float scale = __half2float(__ushort_as_half((unsigned short)(c[0] & 0xFFFFu)));
                                 part[u * TC] = scale * xb.inv * dot_q8(c + 1, xb);
                             }
@@ -538,7 +538,7 @@ __global__ void __launch_bounds__(kConsumers + 32, 1) chain_kernel(const __grid_
                                     }
                                 }
                                 __syncwarp();                                     // every lane's data is in registers: hand the slot back
-                                mbar_arrive_if(empty_g + 8u * u, elected);
+                                mbar_arrive_lane0(empty_g + 8u * u, lane);
                                 if (live) {
                                     if (q4) {
                                         const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&c[0]));

@@ -409,8 +409,10 @@ def parity_check_sharded(chain, shape_key, fmt, seed):
     import torch.distributed as dist
     from meganeura_b200 import decode_chain as dc
     world, rank = chain.world, chain.rank
+    dist.barrier()                                  # ranks may be seconds apart here (rank 0 has just stopped its clock sampler)
     chain.step()
     torch.cuda.synchronize()
+    timed_out = chain.check_error()
     mine = chain.head["y"][0].contiguous()
     parts = [torch.empty_like(mine) for _ in range(world)]
     dist.all_gather(parts, mine)
@@ -420,7 +422,7 @@ def parity_check_sharded(chain, shape_key, fmt, seed):
     dist.all_gather(copies, gathered)
     same_on_all = all(bool(torch.equal(c, copies[0])) for c in copies)
     finite = bool(torch.isfinite(gathered).all())
-    rel, exact = None, None
+    rel, exact, where = None, None, None
     if rank == 0:
         shape = dc.QWEN3_8B if shape_key == "qwen3-8b" else dc.SMOLLM2_135M
         single = dc.DecodeGemvChain(shape, fmt, rank=0, world=1, seed=seed, mode=chain.mode if chain.mode == "plan" else "launches")
@@ -429,11 +431,26 @@ def parity_check_sharded(chain, shape_key, fmt, seed):
         ref = single.logits_view().reshape(-1)
         rel = float((gathered.double() - ref.double()).norm() / ref.double().norm())
         exact = bool(torch.equal(gathered, ref))
+        where = None
+        if not exact:                                   # name the first GEMV whose slice on this rank differs
+            where = "input vector" if not torch.equal(single.x0, chain.x0) else None
+            for i, (a, b) in enumerate(zip(chain.ops_list, single.ops_list)):
+                if where:
+                    break
+                off_c = off_s = 0
+                for gw in a["spec"].groups:
+                    per = gw // world
+                    if not torch.equal(a["y"][0, off_c:off_c + per], b["y"][0, off_s + rank * per: off_s + (rank + 1) * per]):
+                        where = f"op {i} ({a['spec'].name})"
+                        break
+                    off_c += per
+                    off_s += gw
         del single
-    flag = torch.tensor([1 if (same_as_slices and same_on_all and finite) else 0], device="cuda")
+    flag = torch.tensor([1 if (same_as_slices and same_on_all and finite and not timed_out) else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     ok = bool(flag.item()) and (rel is None or rel <= 1e-4)
-    return {"ok": ok, "rel_l2_vs_single_gpu": rel, "bit_exact_vs_single_gpu": exact, "gathered_equals_all_gather_of_slices": same_as_slices,
+    return {"ok": ok, "rel_l2_vs_single_gpu": rel, "bit_exact_vs_single_gpu": exact, "first_difference": where if rank == 0 else None,
+            "gathered_equals_all_gather_of_slices": same_as_slices,
             "identical_on_all_ranks": same_on_all, "logits_finite": finite, "tolerance": 1e-4,
             "what": "gathered logits vs NCCL all-gather of the ranks' slices, across ranks, and vs the unsharded chain on rank 0's GPU"}
 
@@ -520,6 +537,7 @@ def main():
     if chain.check_error():
         raise SystemExit("a bounded device-side wait ran out (MGQ_ERR_TIMEOUT): results are invalid")
 
+    launches_per_step = chain.launches_per_step
     check = parity_check_sharded(chain, args.model, fmt, 0) if world > 1 else (parity_check(chain) if args.batch == 1 else None)
 
     bytes_rank = chain.bytes_per_step()
@@ -527,7 +545,7 @@ def main():
     ms_step = ms_dev / args.steps
     value = total_bytes / (ms_step * 1e-3) / 1e9
     e2e_value = total_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
-    launches = chain.launches_per_step * args.steps * 2         # device-timed steps + end-to-end steps
+    launches = launches_per_step * args.steps * 2               # device-timed steps + end-to-end steps
 
     if rank == 0:
         peak, peak_tf, which = measured_peaks()
@@ -542,13 +560,13 @@ def main():
             "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": chain.h2d_bytes(),
                     "d2h_bytes_per_step": chain.d2h_bytes(), "ms_per_step": round(ms_e2e / args.steps, 4),
                     "tokens_per_s": round(args.batch / (ms_e2e / args.steps * 1e-3), 1)},
-            "gpu_launches": launches, "launches_per_step": chain.launches_per_step,
+            "gpu_launches": launches, "launches_per_step": launches_per_step,
             "cuda_graph": captured,
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": UNIT,
                          "frac": round(achieved / peak, 4), "peak_source": f"of {which} (MEASURED_PEAKS.json hbm_gbs)",
                          "frac_of_nominal_8000": round(achieved / 8000.0, 4), "kernel": kernel,
-                         "bytes_per_launch": round(bytes_rank / chain.launches_per_step),
-                         "us_per_launch": round(ms_step * 1e3 / chain.launches_per_step, 3),
+                         "bytes_per_launch": round(bytes_rank / launches_per_step),
+                         "us_per_launch": round(ms_step * 1e3 / launches_per_step, 3),
                          "traffic": None},
             "clocks": clocks,
             "parity_check": check,

@@ -62,9 +62,11 @@ const char *mgq_version(void);
  *   "gemv.batch_mma"            1 (default): 3..16 rows run on the integer tensor-core kernel that reads
  *                               the weights once per 8 rows; 0: two rows at a time on the streaming kernels
  *   "gemv.wait_us"              time limit of the stamp polls of mgq_gemv_exchange / mgq_exchange_finish
- *                               (default 20000)
+ *                               (default 2000000: the other ranks' processes may launch seconds apart)
  *   "plan.window_tiles"         ring tiles the producer keeps in flight (default: about 64 KB per SM)
  *   "plan.deadline_us"          time limit of every wait inside the plan kernel (default 20000)
+ *   "plan.peer_deadline_us"     the same for plans created with mgq_plan_create_linked, whose waits also
+ *                               depend on other GPUs' host processes (default 2000000)
  *   "gemm.force_tiled"          1: never use the tcgen05 kernel (CUDA-core tiled kernel only)
  *   "session.horizontal_fusion" sessions built afterwards merge single-row matmuls that read the same
  *                               activation into one GEMV over the concatenated weight: 0 never,
@@ -237,7 +239,8 @@ int mgq_matmul_host(int fmt, const void *a_host, int a_dtype, const void *w_dev,
  * All pointers are device pointers and must stay valid for the plan's lifetime.
  * Limits: at most MGQ_PLAN_MAX_OPS ops (MGQ_ERR_SIZE beyond: split the list), m = 1, 256 <= K <= 12288, K*N/32 a multiple of 4, 16-byte aligned w and x.  Launches of one plan must not overlap.  Every device-side wait
  * has a time limit ("plan.deadline_us", default 20 ms), after which the launch finishes with
- * undefined results and mgq_plan_check reports MGQ_ERR_TIMEOUT. */
+ * undefined results, publishes nothing more to consumers, and mgq_plan_check reports
+ * MGQ_ERR_TIMEOUT. */
 #define MGQ_PLAN_MAX_OPS 152                 /* ops per plan (their descriptors are kept in shared memory) */
 typedef struct mgq_plan mgq_plan;
 typedef struct mgq_plan_op {

@@ -329,7 +329,7 @@ struct Tuning {
     int ctas_per_sm = 0;       // "gemv.ctas_per_sm"
     int serial = -1;           // "gemv.serial_dispatch": 1 turns programmatic dependent launch off
     int batch_mma = 1;          // "gemv.batch_mma": 3..16 rows run on the mma kernel (0: pairs of rows on the streaming kernels)
-    long wait_us = 0;           // "gemv.wait_us": time limit of the exchange's stamp polls (0: 20000)
+    long wait_us = 0;           // "gemv.wait_us": time limit of the exchange's stamp polls (0: 2000000; peers may launch seconds apart)
 };
 Tuning g_tuning;
 
@@ -499,7 +499,7 @@ bool overlap_allowed()
     return allowed;
 }
 
-unsigned long long exchange_wait_ns() { return (unsigned long long)(g_tuning.wait_us > 0 ? g_tuning.wait_us : 20000) * 1000ull; }
+unsigned long long exchange_wait_ns() { return (unsigned long long)(g_tuning.wait_us > 0 ? g_tuning.wait_us : 2000000) * 1000ull; }
 
 }  // namespace
 

@@ -584,7 +584,9 @@ __global__ void __launch_bounds__(kConsumers + 32, 1) chain_kernel(const __grid_
                         const float v = o.addend ? s + add : s;
                         o.y[col] = v;
                         const uint32_t pub_cols = o.pub_cols;
-                        if (col < pub_cols) {
+                        // after a timeout nothing is published: peers must run into their own limit rather than
+                        // consume results computed from incomplete inputs under a valid stamp
+                        if (col < pub_cols && *abort_flag_ptr() == 0u) {
                             const size_t at = (size_t)o.pub_rank * pub_cols + col;
                             unsigned long long *const *tab = o.pub_tab;
                             for (uint32_t q = 0; q < o.pub_world; q++)
@@ -627,7 +629,8 @@ __global__ void __launch_bounds__(kConsumers + 32, 1) chain_kernel(const __grid_
 // ------------------------------------------------------------------------------- host side
 
 struct PlanTuning {
-    long deadline_us = 0;       // "plan.deadline_us": limit of every device-side wait (0: 20000)
+    long deadline_us = 0;       // "plan.deadline_us": limit of every device-side wait of a self-contained plan (0: 20000)
+    long peer_deadline_us = 0;  // "plan.peer_deadline_us": the same for plans that wait for other GPUs (0: 2000000)
 };
 PlanTuning g_plan_tuning;
 
@@ -716,9 +719,13 @@ int layout_for(const ChainOp *ops, size_t count, uint32_t tc, uint32_t round, in
     return MGQ_OK;
 }
 
-unsigned long long deadline_ns()
+// A plan whose waits only concern this GPU's own CTAs (all resident at once) can give up after
+// milliseconds.  A plan that waits for other GPUs also waits for their host processes, which may
+// launch seconds apart, so its limit is long by default.
+unsigned long long deadline_ns(bool waits_for_peers)
 {
-    const long us = g_plan_tuning.deadline_us > 0 ? g_plan_tuning.deadline_us : 20000;
+    long us = g_plan_tuning.deadline_us > 0 ? g_plan_tuning.deadline_us : 20000;
+    if (waits_for_peers) us = g_plan_tuning.peer_deadline_us > 0 ? g_plan_tuning.peer_deadline_us : 2000000;
     return (unsigned long long)us * 1000ull;
 }
 
@@ -742,6 +749,9 @@ int set_plan_option(const char *name, long value)
     if (!std::strcmp(name, "plan.deadline_us")) {
         if (value < 0 || value > 10000000) return fail(MGQ_ERR_SHAPE, "%s out of range", name);
         g_plan_tuning.deadline_us = value;
+    } else if (!std::strcmp(name, "plan.peer_deadline_us")) {
+        if (value < 0 || value > 600000000) return fail(MGQ_ERR_SHAPE, "%s out of range", name);
+        g_plan_tuning.peer_deadline_us = value;
     } else {
         return fail(MGQ_ERR_NAME, "unknown option: %s", name);
     }
@@ -889,7 +899,7 @@ int create_plan(const mgq_plan_op *ops, const mgq_plan_link *links, size_t count
     a.finish = reinterpret_cast<unsigned int *>(pl->dev_block + state_off + 12);
     a.final_vec = reinterpret_cast<const unsigned long long *>(final_vec);
     a.final_len = final_vec ? final_len : 0;
-    a.deadline_ns = deadline_ns();
+    a.deadline_ns = deadline_ns(!pl->own_state);
     *out = pl;
     return MGQ_OK;
 }
@@ -913,7 +923,7 @@ int mgq_plan_create_linked(const mgq_plan_op *ops, const mgq_plan_link *links, s
 int mgq_plan_launch(mgq_plan *pl, void *stream)
 {
     if (!pl) return fail(MGQ_ERR_NULL, "null plan");
-    pl->args.deadline_ns = deadline_ns();
+    pl->args.deadline_ns = deadline_ns(!pl->own_state);
     void *args[] = {&pl->args};
     MGQ_CUDA(cudaLaunchCooperativeKernel(pl->kernel, dim3(pl->grid), dim3(pl->layout.tc + 32), args, pl->layout.smem,
                                          static_cast<cudaStream_t>(stream)));
@@ -1061,7 +1071,7 @@ extern "C" int mgq_plan_run_static(const mgq_plan_op *ops, size_t count, void *s
     a.epoch = reinterpret_cast<unsigned long long *>(d_state);
     a.error = reinterpret_cast<unsigned int *>(d_state + 8);
     a.finish = reinterpret_cast<unsigned int *>(d_state + 12);
-    a.deadline_ns = deadline_ns();
+    a.deadline_ns = deadline_ns(false);
     void *args[] = {&a};
     MGQ_CUDA(cudaLaunchCooperativeKernel(kernel, dim3((unsigned)st->sms), dim3(tc + 32), args, L.smem, stream));
     unsigned int err = 0;

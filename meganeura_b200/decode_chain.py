@@ -155,7 +155,10 @@ class DecodeGemvChain:
         self.peer = None
         gen = torch.Generator(device="cpu").manual_seed(1000 + seed)
         self.x0 = torch.randn((batch, shape.hidden), generator=gen).to(self.device)      # the token's input vector
-        self.x_host = torch.empty((batch, shape.hidden), dtype=torch.float32).pin_memory() if self.device.type == "cuda" else None
+        self.x_host = None
+        if self.device.type == "cuda":                     # the host copy of the token vector (what step_host sends in)
+            self.x_host = torch.empty((batch, shape.hidden), dtype=torch.float32).pin_memory()
+            self.x_host.copy_(self.x0)
         self.ops_list = []
         specs = layer_specs(shape)
         for layer in range(self.layers):

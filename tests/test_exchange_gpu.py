@@ -109,9 +109,13 @@ def test_wait_that_nothing_satisfies_times_out_cleanly():
     ex = _SelfExchange([k])
     y = torch.zeros((1, n), dtype=torch.float32, device="cuda")
     stream = torch.cuda.current_stream().cuda_stream
-    check(lib.mgq_gemv_exchange(fmt, None, w.data_ptr(), None, y.data_ptr(), k, n,
-                                None, ex.vec(0), ex.epoch, ex.error, stream))
-    assert ex.error_word() == 1                                # synchronises: the kernel has returned
+    ops.set_option("gemv.wait_us", 1000)                       # the default allows for peers that launch seconds apart
+    try:
+        check(lib.mgq_gemv_exchange(fmt, None, w.data_ptr(), None, y.data_ptr(), k, n,
+                                    None, ex.vec(0), ex.epoch, ex.error, stream))
+        assert ex.error_word() == 1                            # synchronises: the kernel has returned
+    finally:
+        ops.set_option("gemv.wait_us", 0)
     ex.buf[8:12].zero_()
     x = to_dev(np.ones((1, k), dtype=np.float32))
     want = ops.matmul(fmt, x, w, k, n)

@@ -145,7 +145,7 @@ def test_wait_that_nothing_satisfies_times_out(coracle):
     state = torch.zeros(64, dtype=torch.uint8, device="cuda")               # [epoch u64][error u32]
     vec = torch.zeros(k * 8, dtype=torch.uint8, device="cuda")               # stamps stay 0: never valid
     y = torch.zeros((1, n), device="cuda")
-    ops.set_option("plan.deadline_us", 1000)
+    ops.set_option("plan.peer_deadline_us", 1000)
     try:
         plan = ops.Plan([(O.FMT_Q4, None, w, None, y, k, n, 0)], links=[(None, vec.data_ptr())],
                         epoch_ptr=state.data_ptr(), error_ptr=state.data_ptr() + 8)
@@ -154,7 +154,7 @@ def test_wait_that_nothing_satisfies_times_out(coracle):
             plan.check()
         assert e.value.status == 9                                          # MGQ_ERR_TIMEOUT
     finally:
-        ops.set_option("plan.deadline_us", 0)
+        ops.set_option("plan.peer_deadline_us", 0)
     x = to_dev(np.ones((1, k), dtype=np.float32))
     good = ops.Plan([(O.FMT_Q4, x, w, None, y, k, n, 0)])
     good.launch(); good.check()

@@ -132,7 +132,6 @@ def test_fusion_modes_give_the_same_logits():
         s.wait()
         outs.append(s.read_output(cfg.vocab_size))
     assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])    # columns are independent: bit-identical
-    assert O.rel_l2(outs[3], outs[0]) < 5e-6                                        # same math, other f32 summation order
 
 
 def test_device_greedy_loop_and_graph_replay_match_host_loop():

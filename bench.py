@@ -390,15 +390,28 @@ def parity_check(chain, coracle_threads=8):
     logits_plan = chain.logits_view().clone()
     finite = bool(torch.isfinite(logits_plan).all())
     mode, graph = chain.mode, chain.graph
-    chain.mode, chain.graph = "launches", None
+    chain.mode, chain.graph = ("launches" if mode == "plan" else "plan"), None
     chain.step()
     torch.cuda.synchronize()
     logits_launch = chain.logits_view().clone()
     chain.mode, chain.graph = mode, graph
+    chain.step()                                            # leave the measured mode's results in the buffers
+    torch.cuda.synchronize()
     rel = float((logits_plan.double() - logits_launch.double()).norm() / logits_launch.double().norm())
-    ok = finite and worst <= 1e-4 and rel <= 1e-4
-    return {"ok": ok, "rel_l2_vs_oracle": float(f"{worst:.3e}"), "rel_l2_vs_per_gemv_launches": float(f"{rel:.3e}"),
-            "tolerance": 1e-4, "logits_finite": finite,
+    # every GEMV of the chain on its own: the stand-alone GEMV kernel fed with the activations the measured run used
+    from meganeura_b200 import ops
+    per_op = 0.0
+    for i, op in enumerate(chain.ops_list):
+        sp = op["spec"]
+        x_in = chain.x0 if i == 0 else chain.ops_list[i - 1]["y"][:, : sp.k]
+        ref = ops.matmul(fmt, x_in, op["w"], sp.k, op["n_loc"], addend=op["addend"], route="gemv")
+        per_op = max(per_op, float((op["y"].double() - ref.double()).norm() / ref.double().norm()))
+    # per-op results are held to 1e-4; the whole chain of 145 dependent GEMVs multiplies rounding differences
+    # between the two kernels (f32 summation order), so its end-to-end figure is held to 1e-3
+    ok = finite and worst <= 1e-4 and per_op <= 1e-4 and rel <= 1e-3
+    return {"ok": ok, "rel_l2_vs_oracle": float(f"{worst:.3e}"), "max_rel_l2_per_op_vs_gemv_kernel": float(f"{per_op:.3e}"),
+            "rel_l2_chain_vs_other_mode": float(f"{rel:.3e}"),
+            "tolerance": 1e-4, "chain_tolerance": 1e-3, "logits_finite": finite,
             "what": "layer 0 op by op and a 4096-column strip of lm_head vs the f64 CPU oracle; final logits vs one launch per GEMV"}
 
 
@@ -464,8 +477,9 @@ def main():
     ap.add_argument("--fmt", choices=["q4", "q8"], default="q4")
     ap.add_argument("--model", choices=["qwen3-8b", "smollm2-135m"], default="qwen3-8b")
     ap.add_argument("--impl", choices=["mgq", "reference"], default="mgq")
-    ap.add_argument("--mode", choices=["plan", "launches"], default="plan",
-                    help="plan: one persistent kernel per token (default); launches: one kernel per GEMV")
+    ap.add_argument("--mode", choices=["auto", "plan", "launches"], default="auto",
+                    help="plan: one persistent kernel per token; launches: one kernel per GEMV; auto (default): on one GPU "
+                         "whichever of the two is faster in a short calibration, on several GPUs the persistent kernel")
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                     help="launches mode on several GPUs: slices pushed over NVLink by the GEMV kernels (default) or NCCL all-gather")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -496,11 +510,25 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     mode = args.mode if args.batch == 1 else "launches"
+    calibration = None
+    if mode == "auto":
+        mode = "plan"
     exchange = args.exchange if mode == "launches" else "peer"
     if world > 1 and args.batch != 1:
         exchange = "nccl"
     chain = dc.DecodeGemvChain(shape, fmt, batch=args.batch, rank=rank, world=world, seed=0, mode=mode, exchange=exchange)
     captured = chain.capture()
+    if args.mode == "auto" and world == 1 and args.batch == 1:
+        # both ways of running the token, a few steps each; the faster one is what gets measured
+        ms_plan = cuda_timed(chain.step, 8, warmup=3)
+        chain.mode, chain.graph = "launches", None
+        chain.capture()
+        ms_launch = cuda_timed(chain.step, 8, warmup=3)
+        calibration = {"plan_ms": round(ms_plan, 4), "launches_ms": round(ms_launch, 4)}
+        if ms_plan <= ms_launch:
+            chain.mode, chain.graph = "plan", None
+            captured = chain.capture()
+        mode = chain.mode
 
     def barrier():
         if world > 1:
@@ -560,7 +588,7 @@ def main():
             "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": chain.h2d_bytes(),
                     "d2h_bytes_per_step": chain.d2h_bytes(), "ms_per_step": round(ms_e2e / args.steps, 4),
                     "tokens_per_s": round(args.batch / (ms_e2e / args.steps * 1e-3), 1)},
-            "gpu_launches": launches, "launches_per_step": launches_per_step,
+            "gpu_launches": launches, "launches_per_step": launches_per_step, "mode": mode, "mode_calibration": calibration,
             "cuda_graph": captured,
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": UNIT,
                          "frac": round(achieved / peak, 4), "peak_source": f"of {which} (MEASURED_PEAKS.json hbm_gbs)",
@@ -574,13 +602,15 @@ def main():
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(shape_t, fmt)
-        if world == 1 and args.batch == 1 and mode == "plan" and not args.no_extras:
-            # the same chain as one launch per GEMV (programmatic dependent launch, CUDA graph)
-            chain.mode, chain.graph = "launches", None
+        if world == 1 and args.batch == 1 and not args.no_extras:
+            # the same chain run the other way (one launch per GEMV with programmatic dependent launch, or the
+            # persistent plan kernel), CUDA graph, same weights
+            other = "launches" if mode == "plan" else "plan"
+            chain.mode, chain.graph = other, None
             chain.capture()
             ms_l = cuda_timed(chain.step, args.steps, warmup=args.warmup)
-            line["per_gemv_launches"] = {"ms_per_step": round(ms_l, 4), "gbs": round(bytes_rank / ms_l / 1e6, 1),
-                                         "frac": round(bytes_rank / ms_l / 1e6 / peak, 4), "launches_per_step": chain.launches_per_step}
+            line["other_mode"] = {"mode": other, "ms_per_step": round(ms_l, 4), "gbs": round(bytes_rank / ms_l / 1e6, 1),
+                                  "frac": round(bytes_rank / ms_l / 1e6 / peak, 4), "launches_per_step": chain.launches_per_step}
             chain.graph = None
             del chain
             torch.cuda.empty_cache()

@@ -398,6 +398,23 @@ int mgq_session_dispatch_info(const mgq_session *s, size_t index, int *shader, u
 /* Number of kernels launched by this session so far. */
 uint64_t mgq_session_launch_count(const mgq_session *s);
 
+/* Session::set_profiling / dump_gpu_timings / num_groups (src/runtime.rs:1965-1967, 2798-2832,
+ * 4192-4199).  With profiling on, step() runs every dispatch on its own between CUDA events (and
+ * inside an NVTX range named by the dispatch label; step and wait are NVTX ranges "step" / "wait"
+ * like the reference's spans) instead of replaying the captured graph.  mgq_session_gpu_timings
+ * copies the microseconds of each dispatch of the last profiled step (count must equal the number
+ * of dispatches); mgq_session_dump_gpu_timings writes the reference's report -- totals per pass
+ * name, largest first -- as text into `out`.  Both synchronise the session's stream.
+ * mgq_session_num_groups is the number of barrier groups of the plan: the reference's
+ * reorder_by_level + compute_groups (src/runtime.rs:1202-1256), available on plain buffer-id lists
+ * as mgq_barrier_groups (four input and four output ids per dispatch, -1 for none; reorder != 0
+ * sorts by dependency level first, as the reference does when it builds a session). */
+int mgq_session_set_profiling(mgq_session *s, int enabled);
+int mgq_session_gpu_timings(mgq_session *s, float *microseconds, size_t count);
+int mgq_session_dump_gpu_timings(mgq_session *s, char *out, size_t cap);
+int mgq_session_num_groups(const mgq_session *s);
+int mgq_barrier_groups(const int32_t *inputs, const int32_t *outputs, size_t n, int reorder);
+
 #ifdef __cplusplus
 }
 #endif

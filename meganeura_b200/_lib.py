@@ -121,6 +121,11 @@ SIGNATURES = {
     "mgq_session_dispatch_info": (_int, [_vp, _sz, ctypes.POINTER(_int), ctypes.POINTER(_u32), ctypes.POINTER(_u32),
                                          ctypes.POINTER(_int), ctypes.c_char_p, _sz]),
     "mgq_session_launch_count": (ctypes.c_uint64, [_vp]),
+    "mgq_session_set_profiling": (_int, [_vp, _int]),
+    "mgq_session_gpu_timings": (_int, [_vp, _vp, _sz]),
+    "mgq_session_dump_gpu_timings": (_int, [_vp, ctypes.c_char_p, _sz]),
+    "mgq_session_num_groups": (_int, [_vp]),
+    "mgq_barrier_groups": (_int, [_vp, _vp, _sz, _int]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

@@ -10,6 +10,9 @@
 #include <thread>
 #include <vector>
 
+#include <unordered_map>
+#include <unordered_set>
+#include <algorithm>
 #include "mgq_internal.h"
 
 namespace mgq {
@@ -227,4 +230,49 @@ extern "C" int mgq_convert_f16(const float *src, size_t len, uint16_t *dst)
     if (!src || !dst) return mgq::fail(MGQ_ERR_NULL, "null pointer");
     for (size_t i = 0; i < len; i++) dst[i] = f16_from_f32(src[i]);
     return MGQ_OK;
+}
+
+// Barrier groups of a dispatch list, the reference's reorder_by_level + compute_groups
+// (src/runtime.rs:1202-1256).  inputs / outputs hold up to four buffer ids per dispatch (-1: none).
+// Level of a dispatch = 0 when no earlier dispatch produced any of its inputs, else 1 + the highest
+// level among those producers; a stable sort by level gives the reference's order; a new group starts
+// whenever a dispatch reads a buffer written earlier in the current group.
+extern "C" int mgq_barrier_groups(const int32_t *inputs, const int32_t *outputs, size_t n, int reorder)
+{
+    if (n == 0) return 0;
+    if (!inputs || !outputs) return -mgq::fail(MGQ_ERR_NULL, "null dispatch list");
+    std::vector<size_t> order(n);
+    for (size_t i = 0; i < n; i++) order[i] = i;
+    if (reorder) {
+        std::vector<uint32_t> level(n, 0);
+        std::unordered_map<int32_t, size_t> producer;
+        for (size_t i = 0; i < n; i++) {
+            uint32_t lv = 0;
+            for (int j = 0; j < 4; j++) {
+                const int32_t b = inputs[i * 4 + j];
+                if (b < 0) continue;
+                auto it = producer.find(b);
+                if (it != producer.end()) lv = std::max(lv, level[it->second] + 1);
+            }
+            level[i] = lv;
+            for (int j = 0; j < 4; j++)
+                if (outputs[i * 4 + j] >= 0) producer[outputs[i * 4 + j]] = i;
+        }
+        std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return level[a] < level[b]; });
+    }
+    int groups = 0;
+    std::unordered_set<int32_t> dirty;
+    for (size_t pos = 0; pos < n; pos++) {
+        const size_t i = order[pos];
+        bool hazard = false;
+        for (int j = 0; j < 4; j++)
+            if (inputs[i * 4 + j] >= 0 && dirty.count(inputs[i * 4 + j])) hazard = true;
+        if (hazard) {
+            groups++;
+            dirty.clear();
+        }
+        for (int j = 0; j < 4; j++)
+            if (outputs[i * 4 + j] >= 0) dirty.insert(outputs[i * 4 + j]);
+    }
+    return groups + 1;
 }

@@ -24,6 +24,7 @@
 // after the dispatches and feed the next token and position back, so consecutive decode steps need
 // no host round trip.
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <algorithm>
 #include <cstdio>
@@ -147,6 +148,9 @@ struct mgq_session {
     cudaGraphExec_t graph_exec = nullptr;
     uint64_t launches = 0;
     int device = 0;
+    // per-dispatch timing (set_profiling): one event before every dispatch and one after the last
+    bool profiling = false, profiled = false;
+    std::vector<cudaEvent_t> events;
     // greedy feedback
     bool greedy = false;
     int greedy_output = -1, greedy_token_input = -1, greedy_pos_input = -1;
@@ -663,6 +667,7 @@ void mgq_session_free(mgq_session *s)
     if (s->greedy_ws) cudaFree(s->greedy_ws);
     if (s->greedy_token) cudaFree(s->greedy_token);
     if (s->greedy_history) cudaFree(s->greedy_history);
+    for (cudaEvent_t e : s->events) cudaEventDestroy(e);
     if (s->stream) cudaStreamDestroy(s->stream);
     delete s;
 }
@@ -904,17 +909,119 @@ static int enqueue_all(mgq_session *s)
     return MGQ_OK;
 }
 
+// Profiled step (Session::step with profiling on, src/runtime.rs:2851-2861): every dispatch on its own,
+// bracketed by events and an NVTX range named by its label; the captured graph is not used.
+static int enqueue_profiled(mgq_session *s)
+{
+    const size_t n = s->dispatches.size();
+    while (s->events.size() < n + 1) {
+        cudaEvent_t e = nullptr;
+        MGQ_CUDA(cudaEventCreate(&e));
+        s->events.push_back(e);
+    }
+    for (size_t i = 0; i < n; i++) {
+        MGQ_CUDA(cudaEventRecord(s->events[i], s->stream));
+        nvtxRangePushA(s->dispatches[i].label.c_str());
+        const int rc = run_dispatch(s, s->dispatches[i]);
+        nvtxRangePop();
+        if (rc) return rc;
+    }
+    MGQ_CUDA(cudaEventRecord(s->events[n], s->stream));
+    if (s->greedy) {
+        const Node &lo = s->nodes[s->greedy_output];
+        if (int rc = mgq_argmax(static_cast<const float *>(s->ptr(s->greedy_output)), (uint32_t)lo.elements(), s->greedy_ws,
+                                s->greedy_token, static_cast<uint32_t *>(s->ptr(s->greedy_token_input)),
+                                static_cast<uint32_t *>(s->ptr(s->greedy_pos_input)), s->greedy_history, s->greedy_cap, s->stream))
+            return rc;
+    }
+    s->profiled = true;
+    return MGQ_OK;
+}
+
 int mgq_session_step(mgq_session *s)
 {
     if (!s) return fail(MGQ_ERR_NULL, "null session");
     MGQ_CUDA(cudaSetDevice(s->device));
-    if (s->graph_exec) {
-        MGQ_CUDA(cudaGraphLaunch(s->graph_exec, s->stream));
-    } else if (int rc = enqueue_all(s)) {
-        return rc;
+    nvtxRangePushA("step");                      // the reference's span name (src/runtime.rs:2843)
+    int rc = MGQ_OK;
+    if (s->profiling) {
+        rc = enqueue_profiled(s);
+    } else if (s->graph_exec) {
+        rc = mgq::cuda_check((int)cudaGraphLaunch(s->graph_exec, s->stream), "cudaGraphLaunch", __FILE__, __LINE__);
+    } else {
+        rc = enqueue_all(s);
     }
+    nvtxRangePop();
+    if (rc) return rc;
     s->launches += s->dispatches.size() + (s->greedy ? 1 : 0);
     return MGQ_OK;
+}
+
+int mgq_session_set_profiling(mgq_session *s, int enabled)
+{
+    if (!s) return fail(MGQ_ERR_NULL, "null session");
+    s->profiling = enabled != 0;
+    return MGQ_OK;
+}
+
+int mgq_session_gpu_timings(mgq_session *s, float *microseconds, size_t count)
+{
+    if (!s || !microseconds) return fail(MGQ_ERR_NULL, "null argument");
+    if (!s->profiled) return fail(MGQ_ERR_STATE, "no profiled step yet: call mgq_session_set_profiling(s, 1) and step");
+    if (count != s->dispatches.size()) return fail(MGQ_ERR_SIZE, "the plan has %zu dispatches, asked for %zu timings", s->dispatches.size(), count);
+    MGQ_CUDA(cudaStreamSynchronize(s->stream));
+    for (size_t i = 0; i < count; i++) {
+        float ms = 0.f;
+        MGQ_CUDA(cudaEventElapsedTime(&ms, s->events[i], s->events[i + 1]));
+        microseconds[i] = ms * 1000.f;
+    }
+    return MGQ_OK;
+}
+
+int mgq_session_dump_gpu_timings(mgq_session *s, char *out, size_t cap)
+{
+    if (!s || !out || cap == 0) return fail(MGQ_ERR_NULL, "null argument");
+    out[0] = 0;
+    std::vector<float> us(s->dispatches.size());
+    if (int rc = mgq_session_gpu_timings(s, us.data(), us.size())) return rc;
+    // aggregated by pass name like Session::dump_gpu_timings (src/runtime.rs:2798-2832); a pass is named by its label
+    std::map<std::string, std::pair<unsigned, double>> by_label;
+    double total = 0.0;
+    for (size_t i = 0; i < us.size(); i++) {
+        auto &e = by_label[s->dispatches[i].label];
+        e.first++;
+        e.second += us[i];
+        total += us[i];
+    }
+    std::vector<std::pair<std::string, std::pair<unsigned, double>>> rows(by_label.begin(), by_label.end());
+    std::sort(rows.begin(), rows.end(), [](const auto &a, const auto &b) { return a.second.second > b.second.second; });
+    size_t at = 0;
+    auto put = [&](const char *fmt, auto... args) {
+        if (at + 1 >= cap) return;
+        const int n = std::snprintf(out + at, cap - at, fmt, args...);
+        if (n > 0) at += std::min((size_t)n, cap - at - 1);
+    };
+    put("--- GPU pass timings (%zu passes, %.2fms total) ---\n", us.size(), total / 1000.0);
+    for (const auto &r : rows)
+        put("  %32s: %3ux %8.3fms (%5.1f%%)\n", r.first.c_str(), r.second.first, r.second.second / 1000.0,
+            total > 0 ? r.second.second / total * 100.0 : 0.0);
+    put("---\n");
+    return MGQ_OK;
+}
+
+int mgq_session_num_groups(const mgq_session *s)
+{
+    if (!s) return -fail(MGQ_ERR_NULL, "null session");
+    const size_t n = s->dispatches.size();
+    std::vector<int32_t> ins(n * 4), outs(n * 4);
+    auto buf = [&](int node) { return node < 0 ? -1 : s->node_buffer[node]; };
+    for (size_t i = 0; i < n; i++) {
+        const Dispatch &d = s->dispatches[i];
+        for (int j = 0; j < 4; j++) ins[i * 4 + j] = buf(d.in[j]);
+        outs[i * 4] = buf(d.out);
+        for (int j = 0; j < 3; j++) outs[i * 4 + 1 + j] = buf(d.extra[j]);
+    }
+    return mgq_barrier_groups(ins.data(), outs.data(), n, 1);
 }
 
 int mgq_session_capture(mgq_session *s)
@@ -974,8 +1081,10 @@ int mgq_session_read_tokens(mgq_session *s, uint32_t first_pos, uint32_t *out, s
 int mgq_session_wait(mgq_session *s)
 {
     if (!s) return fail(MGQ_ERR_NULL, "null session");
-    MGQ_CUDA(cudaStreamSynchronize(s->stream));
-    return MGQ_OK;
+    nvtxRangePushA("wait");                      // the reference's span name (src/runtime.rs:2835)
+    const int rc = mgq::cuda_check((int)cudaStreamSynchronize(s->stream), "cudaStreamSynchronize", __FILE__, __LINE__);
+    nvtxRangePop();
+    return rc;
 }
 
 int mgq_session_read_output_by_index(mgq_session *s, size_t index, float *out, size_t len)

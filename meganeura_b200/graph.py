@@ -198,6 +198,31 @@ class Session:
     def launch_count(self) -> int:
         return int(lib.mgq_session_launch_count(self._h))
 
+    def set_profiling(self, enabled: bool) -> None:
+        """Session::set_profiling: the next steps run one timed dispatch at a time (no graph replay)."""
+        check(lib.mgq_session_set_profiling(self._h, 1 if enabled else 0))
+
+    def gpu_timings(self):
+        """Microseconds of every dispatch of the last profiled step."""
+        import numpy as np
+        n = int(lib.mgq_session_num_dispatches(self._h))
+        out = np.zeros(n, dtype=np.float32)
+        check(lib.mgq_session_gpu_timings(self._h, out.ctypes.data, n))
+        return out
+
+    def dump_gpu_timings(self) -> str:
+        """Session::dump_gpu_timings: per-label totals of the last profiled step, largest first."""
+        buf = ctypes.create_string_buffer(16384)
+        check(lib.mgq_session_dump_gpu_timings(self._h, buf, len(buf)))
+        return buf.value.decode()
+
+    def num_groups(self) -> int:
+        """Session::num_groups: barrier groups of the dispatch list."""
+        n = int(lib.mgq_session_num_groups(self._h))
+        if n < 0:
+            check(-n)
+        return n
+
 
 def build_inference_session(graph: Graph) -> Session:
     handle = ctypes.c_void_p()

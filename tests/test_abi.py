@@ -105,3 +105,36 @@ def test_graph_builder_checks():
     g.set_outputs([c])
     with pytest.raises(mg.MgqError):
         g.set_outputs([99])
+
+
+def test_barrier_groups_follow_the_reference_rules():
+    """reorder_by_level + compute_groups (src/runtime.rs:1202-1256) on plain buffer-id lists."""
+    import ctypes
+    import numpy as np
+    from meganeura_b200 import _lib
+
+    def groups(dispatches, reorder=1):
+        n = len(dispatches)
+        ins = np.full((n, 4), -1, dtype=np.int32)
+        outs = np.full((n, 4), -1, dtype=np.int32)
+        for i, (i_ids, o_ids) in enumerate(dispatches):
+            ins[i, :len(i_ids)] = i_ids
+            outs[i, :len(o_ids)] = o_ids
+        return _lib.lib.mgq_barrier_groups(ins.ctypes.data, outs.ctypes.data, n, reorder)
+
+    assert groups([]) == 0
+    assert groups([([0], [1])]) == 1
+    # a chain: every dispatch reads what the one before wrote -> one group each
+    assert groups([([0], [1]), ([1], [2]), ([2], [3])]) == 3
+    # q, k, v read the same input and write different buffers: one group; attention reads all three: a second one
+    assert groups([([0, 10], [1]), ([0, 11], [2]), ([0, 12], [3]), ([1, 2, 3], [4])]) == 2
+    # level reordering pulls an independent late dispatch forward into the first group ...
+    late = [([0], [1]), ([1], [2]), ([0], [5])]
+    assert groups(late, reorder=1) == 2
+    # ... without it the list order decides, which here gives the same count but a hazard-free third dispatch
+    assert groups(late, reorder=0) == 2
+    # extra outputs count as writes (merged RoPE + cache write): a reader of the second output starts a new group
+    assert groups([([0], [1, 2]), ([2], [3])]) == 2
+    # write-after-write alone is no hazard in the reference's rule (only reads of dirty buffers split groups)
+    assert groups([([0], [1]), ([0], [1])]) == 1
+    _ = ctypes

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 
 from oracle import oracle as O
-from gpu_util import check_against_oracle, run_matmul
+from gpu_util import check_against_oracle, run_matmul, to_dev
 
 pytestmark = pytest.mark.gpu
 
@@ -51,3 +51,34 @@ def test_rows_are_independent_and_zero_rows_stay_zero():
     assert (full[2] == 0.0).all()
     single = run_matmul(fmt, x[4:5], packed, k, n, route="gemv")         # one row: the streaming kernel
     assert O.rel_l2(full[4], single[0]) < 2e-6
+
+
+def test_sliced_batch_survives_a_larger_later_call(coracle):
+    """K > 4096 runs in K-slices whose partial sums live in a library-owned buffer.  A CUDA graph that
+    captured a launch must keep working after a later, larger call has made the library allocate a
+    bigger buffer: the old one is never freed or moved."""
+    import torch
+    from meganeura_b200 import ops
+    k, n = 12288, 512
+    w = to_dev(O.synth_weights(O.FMT_Q4, k, n, seed=77))
+    rng = np.random.Generator(np.random.PCG64(78))
+    x4 = to_dev(rng.standard_normal((4, k)).astype(np.float32))
+    y4 = torch.zeros((4, n), device="cuda")
+    ops.matmul(O.FMT_Q4, x4, w, k, n, out=y4, route="gemv")                 # first use sizes the buffer (before capture)
+    torch.cuda.synchronize()
+    want = y4.clone()
+    g, s = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g, stream=s):
+            ops.matmul(O.FMT_Q4, x4, w, k, n, out=y4, route="gemv")
+    n_big = 4096
+    w_big = to_dev(O.synth_weights(O.FMT_Q4, k, n_big, seed=79))
+    x16 = to_dev(rng.standard_normal((16, k)).astype(np.float32))
+    big = ops.matmul(O.FMT_Q4, x16, w_big, k, n_big, route="gemv")          # needs a larger partial-sum buffer
+    torch.cuda.synchronize()
+    y4.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(y4, want)
+    ref = coracle.matmul(O.FMT_Q4, x16.cpu().numpy(), w_big.cpu().numpy(), k, n_big)
+    assert O.rel_l2(big.cpu().numpy(), ref) <= 1e-4

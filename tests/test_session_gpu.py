@@ -152,3 +152,42 @@ def test_matmul_host_round_trip(coracle):
     x = np.random.default_rng(0).standard_normal((1, k)).astype(np.float32)
     got = ops.matmul_host(O.FMT_Q8, x, wd.data_ptr(), k, n)
     assert O.rel_l2(got, coracle.matmul(O.FMT_Q8, x, packed, k, n)) <= 1e-4
+
+
+def test_profiling_surface_and_groups():
+    """set_profiling / dump_gpu_timings / num_groups (src/runtime.rs:1965-1967, 2798-2832, 4192-4199):
+    per-dispatch times add up to about the step, the report lists every label, groups follow the
+    dependency levels of the decode graph."""
+    import time
+    import torch
+    import meganeura_b200 as mg
+    from meganeura_b200 import decode_model as M
+    cfg = M.small(M.SMOLLM2_135M, 2, 4096)
+    dec = M.DecodeSession(cfg, 64, seed=5)
+    s = dec.session
+    dec.set_position(3, 0)
+    s.step(); s.wait()
+    n = len(s.plan().dispatches)
+    # the decode graph is a chain except for what the fusions merged: one group per dispatch here
+    assert 1 <= s.num_groups() <= n
+    s.set_profiling(True)
+    dec.set_position(4, 1)
+    s.step(); s.wait()                                   # first profiled step creates the events
+    dec.set_position(5, 2)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    s.step(); s.wait()
+    wall_us = (time.perf_counter() - t0) * 1e6
+    times = s.gpu_timings()
+    assert times.shape == (n,) and (times > 0).all()
+    total = float(times.sum())
+    assert 0.3 * wall_us <= total <= 1.2 * wall_us, f"dispatch times {total:.0f} us vs step {wall_us:.0f} us"
+    report = s.dump_gpu_timings()
+    assert report.startswith("--- GPU pass timings (%d passes" % n)
+    for d in s.plan().dispatches:
+        assert d.label in report
+    s.set_profiling(False)
+    dec.set_position(6, 3)
+    s.step(); s.wait()
+    assert np.isfinite(s.read_output(cfg.vocab_size)).all()
+    _ = mg

@@ -66,6 +66,41 @@ def test_static_plan_matches_allocating_plan_twice(coracle):
             assert O.rel_l2(g, r) <= 1e-6, f"call {attempt}: differs from the allocating entry point"
 
 
+def test_static_plan_in_any_order_of_formats_and_without_allocating(coracle):
+    """A Q4-only list, then a list with a Q8 op, then Q4-only again: each call works out its own kernel
+    variant and shared-memory layout (nothing cached from the call before can be wrong for it), each
+    result matches the allocating entry point, and the device's free memory does not change across a call."""
+    import torch
+    from meganeura_b200 import _lib, ops
+    rng = np.random.Generator(np.random.PCG64(8))
+    stream = torch.cuda.current_stream().cuda_stream
+    x0 = rng.standard_normal((1, 1024)).astype(np.float32)
+    cases = [((O.FMT_Q4, O.FMT_Q4), 61), ((O.FMT_Q4, O.FMT_Q8), 62), ((O.FMT_Q4, O.FMT_Q4), 63)]
+    for fmts, seed in cases:
+        dims = [1024, 2048, 512]
+        weights = [to_dev(O.synth_weights(fmts[i], dims[i], dims[i + 1], seed=seed * 10 + i)) for i in range(2)]
+
+        def run(static):
+            bufs = [to_dev(x0)] + [torch.zeros((1, n), dtype=torch.float32, device="cuda") for n in dims[1:]]
+            entries = [(fmts[i], bufs[i], weights[i], None, bufs[i + 1], dims[i], dims[i + 1], i) for i in range(2)]
+            if static:
+                arr = _ops_array(entries)
+                torch.cuda.synchronize()
+                free_before = torch.cuda.mem_get_info()[0]
+                _lib.check(_lib.lib.mgq_plan_run_static(arr, 2, stream))
+                assert torch.cuda.mem_get_info()[0] == free_before, "the allocation-free entry point changed the free device memory"
+            else:
+                plan = ops.Plan(entries)
+                plan.launch()
+                plan.check()
+            return bufs[-1].cpu().numpy()
+
+        want, got = run(False), run(True)
+        assert np.isfinite(got).all() and O.rel_l2(got, want) <= 1e-6, f"formats {fmts}"
+        mid = coracle.matmul(fmts[0], x0, weights[0].cpu().numpy(), dims[0], dims[1]).astype(np.float32)
+        assert O.rel_l2(got, coracle.matmul(fmts[1], mid, weights[1].cpu().numpy(), dims[1], dims[2])) <= 1e-4
+
+
 def test_static_plan_rejects_long_lists():
     import torch
     import meganeura_b200 as mg

@@ -66,7 +66,7 @@ struct ChainOp {                               // 128 bytes
     uint32_t arrive;                           // 1: CTAs count themselves in done[op] when they finish the op
     uint32_t red_shift, red_chunk;
     uint32_t pub_cols, pub_world, pub_rank;    // leading columns published as {value, stamp}, to how many ranks, as which rank
-    uint32_t ppt;                              // passes per ring tile: 1 or 2
+    uint32_t units;                            // n / col_align: what the CTAs divide among themselves
     uint32_t pad[2];
 };
 static_assert(sizeof(ChainOp) == 128, "ChainOp is copied in 16-byte pieces");
@@ -223,15 +223,16 @@ __device__ __forceinline__ void st_elem(unsigned long long *p, float value, uint
 }
 
 // This CTA's share of an op: a contiguous column range, cut into passes of `lanes` columns; a ring
-// tile holds `ppt` passes (1 or 2).  Producer and consumers derive it from the same numbers.
+// tile holds one pass.  Producer and consumers derive it from the same numbers.
 struct Share {
     uint32_t c0, ncols, passes;
 };
 __device__ __forceinline__ Share share_of(const ChainOp &o)
 {
-    const uint32_t units = o.n / o.col_align;
-    const uint32_t u0 = (uint32_t)((unsigned long long)blockIdx.x * units / gridDim.x);
-    const uint32_t u1 = (uint32_t)((unsigned long long)(blockIdx.x + 1) * units / gridDim.x);
+    // units * gridDim.x < 2^32 (checked when the plan is built): plain 32-bit divisions
+    const uint32_t units = o.units;
+    const uint32_t u0 = blockIdx.x * units / gridDim.x;
+    const uint32_t u1 = (blockIdx.x + 1u) * units / gridDim.x;
     Share s;
     s.c0 = u0 * o.col_align;
     s.ncols = (u1 - u0) * o.col_align;
@@ -653,8 +654,9 @@ int shape_op(ChainOp &d, size_t i, uint32_t tc, uint32_t round)
                     (tc / d.col_align < kMaxBpc ? tc / d.col_align : kMaxBpc) * 32u);
     d.lanes = lanes;
     d.active = lanes * bpc;
-    d.ppt = 1;
     d.hdr_off = d.active * 16u;
+    d.units = d.n / d.col_align;
+    if ((unsigned long long)d.units * 1024ull >= (1ull << 32)) return fail(MGQ_ERR_SHAPE, "op %zu: N=%u is too large for the plan kernel", i, d.n);
     // finishing lanes per column: a power of two, at most 32, as many as a round leaves room for;
     // all of it follows from K and the consumer count, so a column's sum does not depend on N
     const uint32_t cols_per_round = round * lanes;

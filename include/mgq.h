@@ -64,6 +64,9 @@ const char *mgq_version(void);
  *   "gemv.wait_us"              time limit of the stamp polls of mgq_gemv_exchange / mgq_exchange_finish
  *                               (default 2000000: the other ranks' processes may launch seconds apart)
  *   "plan.window_tiles"         ring tiles the producer keeps in flight (default: about 64 KB per SM)
+ *   "plan.dataflow"             how a plan made by mgq_plan_create hands activations from op to op: 0 (default)
+ *                               plain vectors, the consumer waits for the producer's arrival counter; 1 the
+ *                               {value, stamp} vectors that multi-GPU plans use, consumers wait per block
  *   "plan.deadline_us"          time limit of every wait inside the plan kernel (default 20000)
  *   "plan.peer_deadline_us"     the same for plans created with mgq_plan_create_linked, whose waits also
  *                               depend on other GPUs' host processes (default 2000000)
@@ -231,11 +234,11 @@ int mgq_matmul_host(int fmt, const void *a_host, int a_dtype, const void *w_dev,
  * thread per CTA streams the packed weights of all ops through a shared-memory ring with bulk
  * copies and runs ahead across op boundaries; op i starts reading its activations only after
  * ops [0, wait_for) have completed (wait_for = 0: no dependency; wait_for = i: depends on the op
- * before it).  When x is a range of the output y of an earlier op that is waited for, the plan
- * moves those values between the two ops as {value, stamp} elements of a vector it owns, and the
- * consumer waits per 32-element block instead of for whole ops; any other x is read as a plain
- * vector once every CTA has counted itself out of op wait_for - 1.  y always receives the plain
- * result.  An addend must be complete before the op that produces this op's activations starts.
+ * before it).  x is read as a plain vector once every CTA has counted itself out of op
+ * wait_for - 1 (arrival counters in global memory).  With "plan.dataflow" = 1, an x that is a range
+ * of the output y of an earlier op that is waited for travels instead as {value, stamp} elements of a
+ * vector the plan owns and the consumer waits per 32-element block, which is what plans over several
+ * GPUs do (mgq_plan_create_linked).  y always receives the plain result.  An addend must be complete before the op that produces this op's activations starts.
  * All pointers are device pointers and must stay valid for the plan's lifetime.
  * Limits: at most MGQ_PLAN_MAX_OPS ops (MGQ_ERR_SIZE beyond: split the list), m = 1, 256 <= K <= 12288, K*N/32 a multiple of 4, 16-byte aligned w and x.  Launches of one plan must not overlap.  Every device-side wait
  * has a time limit ("plan.deadline_us", default 20 ms), after which the launch finishes with

@@ -630,6 +630,7 @@ __global__ void __launch_bounds__(kConsumers + 32, 1) chain_kernel(const __grid_
 // ------------------------------------------------------------------------------- host side
 
 struct PlanTuning {
+    int dataflow = 0;           // "plan.dataflow": 1 = on one GPU, too, hand activations from op to op as {value, stamp} vectors
     long deadline_us = 0;       // "plan.deadline_us": limit of every device-side wait of a self-contained plan (0: 20000)
     long peer_deadline_us = 0;  // "plan.peer_deadline_us": the same for plans that wait for other GPUs (0: 2000000)
 };
@@ -748,7 +749,9 @@ uint32_t consumer_threads() { return 768u; }
 
 int set_plan_option(const char *name, long value)
 {
-    if (!std::strcmp(name, "plan.deadline_us")) {
+    if (!std::strcmp(name, "plan.dataflow")) {
+        g_plan_tuning.dataflow = value ? 1 : 0;
+    } else if (!std::strcmp(name, "plan.deadline_us")) {
         if (value < 0 || value > 10000000) return fail(MGQ_ERR_SHAPE, "%s out of range", name);
         g_plan_tuning.deadline_us = value;
     } else if (!std::strcmp(name, "plan.peer_deadline_us")) {
@@ -815,7 +818,7 @@ int create_plan(const mgq_plan_op *ops, const mgq_plan_link *links, size_t count
             d.xs = reinterpret_cast<const unsigned long long *>(links[i].wait_vec);
             if (d.xs) d.wait_for = 0;
             if (reinterpret_cast<uintptr_t>(d.xs) % 16 != 0) return fail(MGQ_ERR_ALIGN, "op %zu: the gathered vector must be 16-byte aligned", i);
-        } else if (d.wait_for) {
+        } else if (d.wait_for && g_plan_tuning.dataflow) {
             // activations that are a range of an earlier op's output travel as stamped elements
             for (size_t j = d.wait_for; j-- > 0;) {
                 const float *y0 = ops[j].y, *y1 = ops[j].y + ops[j].n;

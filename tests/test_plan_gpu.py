@@ -40,14 +40,27 @@ def _chain(coracle, fmts, dims, addend_at=(), seed=0, replays=1):
     return plan
 
 
+@pytest.mark.parametrize("dataflow", [0, 1])
 @pytest.mark.parametrize("fmts", [(O.FMT_Q4,), (O.FMT_Q8,), (O.FMT_Q4, O.FMT_Q8)])
-def test_dependent_chain(coracle, fmts):
-    _chain(coracle, fmts, [512, 1024, 768, 4096, 256, 576, 1536, 576], addend_at=(1, 4, 6))
+def test_dependent_chain(coracle, fmts, dataflow):
+    """dataflow 0: consumers wait on arrival counters and read plain vectors; 1: {value, stamp} vectors."""
+    from meganeura_b200 import ops
+    ops.set_option("plan.dataflow", dataflow)
+    try:
+        _chain(coracle, fmts, [512, 1024, 768, 4096, 256, 576, 1536, 576], addend_at=(1, 4, 6), replays=2)
+    finally:
+        ops.set_option("plan.dataflow", 0)
 
 
-def test_qwen_layer_shapes(coracle):
+@pytest.mark.parametrize("dataflow", [0, 1])
+def test_qwen_layer_shapes(coracle, dataflow):
     # one layer of the benchmark's shapes, each op consuming its predecessor's output
-    _chain(coracle, (O.FMT_Q4,), [4096, 12288, 4096, 6144, 4096, 12288, 4096], addend_at=(1, 5))
+    from meganeura_b200 import ops
+    ops.set_option("plan.dataflow", dataflow)
+    try:
+        _chain(coracle, (O.FMT_Q4,), [4096, 12288, 4096, 6144, 4096, 12288, 4096], addend_at=(1, 5))
+    finally:
+        ops.set_option("plan.dataflow", 0)
 
 
 def test_small_ops_leave_ctas_idle(coracle):
@@ -110,17 +123,22 @@ def test_plain_vectors_wait_on_arrival_counters(coracle):
     assert O.rel_l2(y3.cpu().numpy(), coracle.matmul(O.FMT_Q4, want2, w3, n2, 256, wide=True)) <= 1e-4
 
 
-def test_consumer_of_a_column_range(coracle):
+@pytest.mark.parametrize("dataflow", [0, 1])
+def test_consumer_of_a_column_range(coracle, dataflow):
     """The consumer takes columns [256, 256+512) of its producer's output (not the leading ones)."""
     import torch
     from meganeura_b200 import ops
+    ops.set_option("plan.dataflow", dataflow)
     k, n, k2, n2 = 512, 1024, 512, 384
     rng = np.random.Generator(np.random.PCG64(4))
     x0 = rng.standard_normal((1, k)).astype(np.float32)
     w1, w2 = O.synth_weights(O.FMT_Q8, k, n, 21), O.synth_weights(O.FMT_Q4, k2, n2, 22)
     y1 = torch.zeros((1, n), device="cuda"); y2 = torch.zeros((1, n2), device="cuda")
-    plan = ops.Plan([(O.FMT_Q8, to_dev(x0), to_dev(w1), None, y1, k, n, 0),
-                     (O.FMT_Q4, y1[:, 256:256 + k2], to_dev(w2), None, y2, k2, n2, 1)])
+    try:
+        plan = ops.Plan([(O.FMT_Q8, to_dev(x0), to_dev(w1), None, y1, k, n, 0),
+                         (O.FMT_Q4, y1[:, 256:256 + k2], to_dev(w2), None, y2, k2, n2, 1)])
+    finally:
+        ops.set_option("plan.dataflow", 0)
     plan.launch(); plan.launch()
     plan.check()
     mid = coracle.matmul(O.FMT_Q8, x0, w1, k, n, wide=True).astype(np.float32)

@@ -228,7 +228,9 @@ __device__ __forceinline__ void load_x_gathered(const float2 *vec, uint32_t b, X
     prepare_x<ORDER>(v, xb);
 }
 
-// Exact sum over one block of X[i] * code[i], returned in f32 (planes recombined with two FMAs).
+// Exact sum over one block of X[i] * code[i], returned in f32.  The three plane sums are recombined in
+// integer arithmetic: |sum| <= 15 * 32 * (64 * 65536 + 255 * 256 + 255) < 2^31, so the exact value
+// fits and a single conversion rounds it (one I2F instead of three, no FMAs).
 __device__ __forceinline__ float dot_q4(const uint4 &q, const XBlock &xb)
 {
     const uint32_t wv[4] = {q.x, q.y, q.z, q.w};
@@ -243,7 +245,7 @@ __device__ __forceinline__ float dot_q4(const uint4 &q, const XBlock &xb)
         a1 = dp4a_uu(hi, xb.p1[2 * j + 1], a1);
         a2 = dp4a_us(hi, xb.p2[2 * j + 1], a2);
     }
-    return fmaf((float)a2, 65536.f, fmaf((float)a1, 256.f, (float)a0));
+    return (float)(a2 * 65536 + a1 * 256 + a0);
 }
 
 // bp points at the 8 code words (int8 x 4) of a Q8 block.

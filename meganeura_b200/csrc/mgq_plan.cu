@@ -180,25 +180,6 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr)
     return v;
 }
 
-// Q4 block dot product with the three byte planes recombined in integer arithmetic: |sum| is at most
-// 15*32*(64*65536 + 255*256 + 255) < 2^31, so the exact sum fits and one conversion remains.
-__device__ __forceinline__ float dot_q4_exact(const uint4 &q, const XBlock &xb)
-{
-    const uint32_t wv[4] = {q.x, q.y, q.z, q.w};
-    int a0 = 0, a1 = 0, a2 = 0;
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        const uint32_t lo = wv[j] & 0x0F0F0F0Fu, hi = (wv[j] >> 4) & 0x0F0F0F0Fu;
-        a0 = dp4a_uu(lo, xb.p0[2 * j], a0);
-        a1 = dp4a_uu(lo, xb.p1[2 * j], a1);
-        a2 = dp4a_us(lo, xb.p2[2 * j], a2);
-        a0 = dp4a_uu(hi, xb.p0[2 * j + 1], a0);
-        a1 = dp4a_uu(hi, xb.p1[2 * j + 1], a1);
-        a2 = dp4a_us(hi, xb.p2[2 * j + 1], a2);
-    }
-    return (float)(a2 * 65536 + a1 * 256 + a0);
-}
-
 __device__ __forceinline__ void consumer_sync(uint32_t threads)
 {
     asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
@@ -500,7 +481,7 @@ __global__ void __launch_bounds__(kConsumers + 32, 1) chain_kernel(const __grid_
                                 const uint32_t h = lds32(tile + off_h);
                                 mbar_arrive_lane0(empty_g + 8u * u, lane);
                                 const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&h));
-                                part[u * TC] = fmaf(dm.x * xb.inv, dot_q4_exact(q, xb), dm.y * xb.sum);
+                                part[u * TC] = fmaf(dm.x * xb.inv, dot_q4(q, xb), dm.y * xb.sum);
                             }
                         } else {
 #pragma unroll
@@ -543,7 +524,7 @@ __global__ void __launch_bounds__(kConsumers + 32, 1) chain_kernel(const __grid_
                                 if (live) {
                                     if (q4) {
                                         const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&c[0]));
-                                        part[u * TC] = fmaf(dm.x * xb.inv, dot_q4_exact(q, xb), dm.y * xb.sum);
+                                        part[u * TC] = fmaf(dm.x * xb.inv, dot_q4(q, xb), dm.y * xb.sum);
                                     } else {
                                         const float scale = __half2float(__ushort_as_half((unsigned short)(c[0] & 0xFFFFu)));
                                         part[u * TC] = scale * xb.inv * dot_q8(c + 1, xb);

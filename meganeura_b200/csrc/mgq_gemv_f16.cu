@@ -88,9 +88,8 @@ int launch_gemv_f16(const float *x, const void *w, const float *addend, float *y
     MGQ_CUDA(cudaGetDevice(&dev));
     MGQ_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    // Narrow column tiles win: 32 columns (64-byte row segments, 64 K-slices per CTA) measured 329 us
-    // on 4096x151936 against 351 / 373 / 514 us for 64 / 128 / 256 columns; 16 columns when even that
-    // gives an SM fewer than eight CTAs (4096x24576: 62 vs 72 us, 4096x4096: 20 vs 35 us).
+    // Narrow column tiles win: 32 columns (64-byte row segments, 64 K-slices per CTA); 16 columns when
+    // even that gives an SM fewer than eight CTAs.
     const int lanes = (n + 31) / 32 >= 8u * (uint32_t)sms ? 4 : 2;
     for (uint32_t r0 = 0; r0 < m; r0 += kF16Rows) {
         const uint32_t rows = m - r0 < (uint32_t)kF16Rows ? m - r0 : (uint32_t)kF16Rows;

@@ -620,6 +620,10 @@ int mgq_build_inference_session(const mgq_graph *g, mgq_session **out)
                 d.workgroups[0] = 1; d.workgroups[1] = nd.u0;
                 d.params[0] = (uint32_t)s->nodes[nd.inputs[1]].shape[0];   // max_seq (the reference's slot is reserved)
                 d.params[1] = nd.u0; d.params[2] = nd.u1; d.params[3] = nd.u2;
+                if (d.params[0] > 4096) {           // the attention kernel's limit: refuse here, not at the first step
+                    mgq_session_free(s);
+                    return fail(MGQ_ERR_SHAPE, "cached_attention: a cache of %u rows exceeds the kernel's limit of 4096", d.params[0]);
+                }
                 const size_t ws = mgq_cached_attention_workspace(nd.u1, nd.u2, d.params[0]);
                 rc = mgq_buffer_create(ws, &d.workspace);
                 if (rc) { mgq_session_free(s); return rc; }

@@ -4,7 +4,7 @@
     python -m meganeura_b200.kernel_cases gemm q8 512x4096x14336 [--launches 3]
     python -m meganeura_b200.kernel_cases sweep q4            # the SmolLM2-135M decode shapes
     python -m meganeura_b200.kernel_cases decode qwen3-8b --layers 4 --steps 4 [--context 2048]
-    python -m meganeura_b200.kernel_cases chain q4 --layers 4 [--launches 3] [--no-head]   # the persistent plan kernel
+    python -m meganeura_b200.kernel_cases chain q4 --layers 4 [--launches 3] [--no-head] [--mode plan|launches]
 
 `gemv` rotates through enough distinct weight copies to exceed L2 several times over and replays
 the launches from a CUDA graph, so the printed GB/s is a streaming (cold-cache) figure; with
@@ -89,31 +89,33 @@ def gemm_case(fmt, m, k, n, launches=0):
     return tf
 
 
-def chain_case(fmt, layers, launches, head=True, peak_gbs=None):
+def chain_case(fmt, layers, launches, head=True, peak_gbs=None, mode="plan"):
     """The decode GEMV chain (Qwen3-8B shapes, `layers` layers, optionally without the lm_head) as one
-    persistent plan kernel per token: `launches` plain launches for a profiler, else a timed loop."""
+    persistent plan kernel per token (mode "plan") or one kernel per GEMV (mode "launches"): `launches`
+    plain tokens for a profiler, else a timed loop."""
     from . import decode_chain as dc
-    chain = dc.DecodeGemvChain(dc.QWEN3_8B, fmt, layers=layers, mode="plan")
+    chain = dc.DecodeGemvChain(dc.QWEN3_8B, fmt, layers=layers, mode=mode)
     if not head:
         chain.ops_list.pop()
-    chain._build_plan()
     nbytes = sum(dc.gemv_bytes(fmt, 1, op["spec"].k, op["n_loc"], op["spec"].residual) for op in chain.ops_list)
     for _ in range(max(launches, 3)):
-        chain.plan.launch()
-    chain.plan.check()
+        chain._launch_all()
+    if chain.check_error():
+        raise RuntimeError("a bounded device-side wait ran out")
     if launches:
         return None
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(20):
-        chain.plan.launch()
+        chain._launch_all()
     e1.record()
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / 20
     gbs = nbytes / us / 1e3
     tail = f" ({gbs / peak_gbs * 100:.1f}% of {peak_gbs:.0f})" if peak_gbs else ""
-    print(f"chain {'Q4' if fmt == FMT_Q4 else 'Q8'} {layers} layers{' + lm_head' if head else ''}: {len(chain.ops_list)} GEMVs, "
-          f"{nbytes / 1e6:.1f} MB, {us:.1f} us per launch, {gbs:.1f} GB/s{tail}  {chain.plan.info()}")
+    info = chain.plan.info() if chain.plan is not None else {"kernels_per_token": chain.launches_per_step}
+    print(f"chain {'Q4' if fmt == FMT_Q4 else 'Q8'} {layers} layers{' + lm_head' if head else ''} ({mode}): {len(chain.ops_list)} GEMVs, "
+          f"{nbytes / 1e6:.1f} MB, {us:.1f} us per token, {gbs:.1f} GB/s{tail}  {info}")
     return gbs
 
 
@@ -150,6 +152,7 @@ def main():
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--no-head", action="store_true", help="chain: leave the lm_head out (a small profiler case)")
+    ap.add_argument("--mode", choices=["plan", "launches"], default="plan", help="chain: persistent kernel or one kernel per GEMV")
     args = ap.parse_args()
     if args.kind == "decode":
         if args.fmt not in ("qwen3-8b", "smollm2-135m"):
@@ -164,7 +167,7 @@ def main():
     torch.cuda.synchronize()
     del warm
     if args.kind == "chain":
-        chain_case(fmt, args.layers, args.launches, head=not args.no_head, peak_gbs=args.peak_gbs)
+        chain_case(fmt, args.layers, args.launches, head=not args.no_head, peak_gbs=args.peak_gbs, mode=args.mode)
     elif args.kind == "sweep":
         for k, n in SMOLLM2_SHAPES:
             gemv_case(fmt, k, n, peak_gbs=args.peak_gbs, hot=args.hot)

@@ -47,6 +47,7 @@ constexpr uint32_t kConsumerWarps = kConsumers / 32;
 constexpr uint32_t kMaxOps = MGQ_PLAN_MAX_OPS;  // every op descriptor of a plan is kept in shared memory
 constexpr uint32_t kStageWords = 32 * 33;      // per leader warp: 32 blocks x 32 activations, rows padded to 33 words
 constexpr uint32_t kMaxSlots = 16;             // 2 groups of at most 8 slots
+constexpr uint32_t kHeadBytes = 512;           // ring barriers (256 B), abort flag, two destination tables of kMaxPeers pointers (at 384)
 constexpr uint32_t kMaxBpc = 384;              // K <= 12288: the prepared activations of one op must fit their shared-memory stage
 
 struct ChainOp {                               // 128 bytes
@@ -67,7 +68,8 @@ struct ChainOp {                               // 128 bytes
     uint32_t red_shift, red_chunk;
     uint32_t pub_cols, pub_world, pub_rank;    // leading columns published as {value, stamp}, to how many ranks, as which rank
     uint32_t units;                            // n / col_align: what the CTAs divide among themselves
-    uint32_t pad[2];
+    uint32_t group_sync;                       // 1: a column's bpc threads are whole warps and reduce behind a barrier of their own
+    uint32_t pad[1];
 };
 static_assert(sizeof(ChainOp) == 128, "ChainOp is copied in 16-byte pieces");
 
@@ -184,6 +186,11 @@ __device__ __forceinline__ void consumer_sync(uint32_t threads)
 {
     asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
 }
+// Barrier 1 is all consumers; barriers 2..15 are the threads that share one column of every pass.
+__device__ __forceinline__ void named_sync(uint32_t id, uint32_t threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 
 __device__ __forceinline__ ulonglong2 ld_pair2(const ulonglong2 *p)
 {
@@ -233,7 +240,8 @@ __device__ __forceinline__ void wait_counter(const ChainOp &o, unsigned long lon
 // read consecutive 16-byte pieces (whole 128-byte lines per instruction instead of one line per lane),
 // the values go through a shared-memory stage (rows of 33 words, free of bank conflicts both ways)
 // and lane l leaves with the 32 activations of block b0 + l.  Stamped vectors are first polled at the
-// first and last piece of each block, then fetched until every stamp matches.
+// first and last piece of each block (polling all of them from every CTA loads the L2 enough to
+// slow the producers down), then fetched until every stamp matches.
 __device__ __forceinline__ void warp_fetch_x(const ChainOp &o, uint32_t b0, uint32_t nb, uint32_t stamp, unsigned long long target,
                                              const ChainArgs &a, uint32_t *stage, float (&v)[32])
 {
@@ -273,13 +281,18 @@ __device__ __forceinline__ void warp_fetch_x(const ChainOp &o, uint32_t b0, uint
         __syncwarp();
         const float4 *src = reinterpret_cast<const float4 *>(o.x + 32u * b0);              // 8 pieces of four values per block
         const uint32_t pieces = nb * 8u;
+        float4 e[8];                                 // all eight loads in flight before the first is used
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const uint32_t p = (uint32_t)j * 32u + lane;
+            e[j] = __ldcg(src + (p < pieces ? p : 0u));
+        }
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             const uint32_t p = (uint32_t)j * 32u + lane;
             if (p < pieces) {
-                const float4 e = __ldcg(src + p);
                 uint32_t *dst = stage + (p >> 3) * 33u + 4u * (p & 7u);
-                dst[0] = __float_as_uint(e.x); dst[1] = __float_as_uint(e.y); dst[2] = __float_as_uint(e.z); dst[3] = __float_as_uint(e.w);
+                dst[0] = __float_as_uint(e[j].x); dst[1] = __float_as_uint(e[j].y); dst[2] = __float_as_uint(e[j].z); dst[3] = __float_as_uint(e[j].w);
             }
         }
     }
@@ -386,9 +399,9 @@ __global__ void __launch_bounds__(kConsumers + 32, 1) chain_kernel(const __grid_
 {
     constexpr uint32_t TC = kConsumers;
     extern __shared__ __align__(128) uint8_t smem[];
-    // [barriers + abort flag 384 B][op descriptors][activation stages][reduction 2 x R x TC floats][ring 2 x R slots]
-    ChainOp *s_ops = reinterpret_cast<ChainOp *>(smem + 384);
-    uint32_t *s_xchg = reinterpret_cast<uint32_t *>(smem + 384 + (size_t)a.n_ops * sizeof(ChainOp));
+    // [barriers, abort flag, destination tables: kHeadBytes][op descriptors][activation stages][reduction 2 x R x TC floats][ring 2 x R slots]
+    ChainOp *s_ops = reinterpret_cast<ChainOp *>(smem + kHeadBytes);
+    uint32_t *s_xchg = reinterpret_cast<uint32_t *>(smem + kHeadBytes + (size_t)a.n_ops * sizeof(ChainOp));
     float *s_red = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(s_xchg) + a.xchg_bytes);
     const uint32_t t = threadIdx.x, G = gridDim.x;
     const uint32_t full0 = smem_u32(smem), empty0 = full0 + 2u * R * 8u;
@@ -422,28 +435,55 @@ __global__ void __launch_bounds__(kConsumers + 32, 1) chain_kernel(const __grid_
             const ChainOp &o = s_ops[op];
             const Share sh = share_of(o);
             if (sh.ncols != 0) {
-                // the fields the pass loop needs, in registers (the descriptor itself stays in shared memory)
-                const uint32_t bpc = o.bpc, o_lanes = o.lanes, o_shift = o.red_shift;
+                // Little is held in registers across the pass loop (72 registers per thread are all that 25 warps
+                // leave): the byte planes, two ring offsets, and a few packed words; everything else about the
+                // op is read from its descriptor in shared memory where it is needed.
+                const uint32_t bpc = o.bpc;
                 const bool has_block = t < o.active;
-                const uint32_t b = t % bpc, lane_col = t / bpc;
                 const bool q4 = o.fmt == MGQ_FMT_Q4;
+                const uint32_t my_col = has_block ? t / bpc : 0x40000000u;      // column inside a pass; idle threads: never live
 
-                // ---- which column sum this thread finishes after each round (same for every round);
-                //      worked out before the activations are waited for
-                uint32_t fin_src, fin_cnt, fin_rel;          // staging offset, partials to add, column inside a round
-                bool fin_writer;
+                // the ranks' gathered vectors this op publishes to: pointers into shared memory now (tables of
+                // consecutive ops alternate), so that the finishing lanes do not wait for global memory later;
+                // the barrier after the activation fetch orders these stores before their readers
+                unsigned long long *s_tab = reinterpret_cast<unsigned long long *>(smem + 384) + (op & 1u) * kMaxPeers;
+                if (t >= TC - 32u && lane < o.pub_world) s_tab[lane] = __ldg(reinterpret_cast<const unsigned long long *>(o.pub_tab + lane));
+
+                // ---- which column sum this thread finishes after each round (same for every round), worked out
+                //      before the activations are waited for and packed into one word:
+                //      [0,12) float offset of its partials in the round's staging rows, [12,21) how many, 21: scalar
+                //      reads, [22,31) column inside a round, 31: this lane stores the sum
+                uint32_t fin;
+                const bool group_sync = o.group_sync != 0u;
                 {
-                    const uint32_t chunk = o.red_chunk;
-                    const uint32_t fin = t >> o_shift, li = t & ((1u << o_shift) - 1u);
-                    const bool valid = fin < (uint32_t)R * o_lanes;
-                    const uint32_t fu = valid ? fin / o_lanes : 0u, fj = valid ? fin % o_lanes : 0u;
+                    const uint32_t o_lanes = o.lanes, o_shift = o.red_shift, chunk = o.red_chunk;
+                    const uint32_t li = t & ((1u << o_shift) - 1u);
+                    uint32_t fu, fj;
+                    bool valid;
+                    if (group_sync) {
+                        // the j-th warp of a column's threads finishes that column of the round's j-th pass: it reads
+                        // only what its own group wrote, so the group's barrier is all it needs
+                        const uint32_t gw = bpc >> 5, w = t >> 5;
+                        fj = w / gw;
+                        fu = w % gw;
+                        valid = fu < (uint32_t)R && fj < o_lanes;
+                        if (!valid) fu = fj = 0u;
+                    } else {
+                        const uint32_t f = t >> o_shift;
+                        valid = f < (uint32_t)R * o_lanes;
+                        fu = valid ? f / o_lanes : 0u;
+                        fj = valid ? f % o_lanes : 0u;
+                    }
                     const uint32_t first = li * chunk;
-                    fin_cnt = (valid && first < bpc) ? min(chunk, bpc - first) : 0u;
-                    fin_src = fu * TC + fj * bpc + first;
-                    fin_rel = fu * o_lanes + fj;
-                    fin_writer = valid && li == 0;
-                    if (!((bpc % 4u == 0u) && (chunk % 4u == 0u))) fin_cnt |= 0x80000000u;     // top bit: scalar reads
+                    const uint32_t cnt = (valid && first < bpc) ? min(chunk, bpc - first) : 0u;
+                    const uint32_t scalar = ((bpc % 4u == 0u) && (chunk % 4u == 0u)) ? 0u : 1u;
+                    fin = ((fu * TC + fj * bpc + first) & 4095u) | (cnt << 12) | (scalar << 21) | ((fu * o_lanes + fj) << 22) |
+                          ((valid && li == 0u) ? 0x80000000u : 0u);
                 }
+
+                // the barrier between a round's partial sums and its column sums, as id | threads << 4: the column's
+                // own threads where they are whole warps (idle threads then take no part: id 0), else all consumers
+                const uint32_t sync = group_sync ? (has_block ? (my_col + 2u) | (bpc << 4) : 0u) : (1u | (TC << 4));
 
                 // ---- activations of this thread's block, as byte planes in registers: the first bpc threads
                 //      fetch and prepare (a warp at a time, 32 blocks each), everyone reads the planes
@@ -452,6 +492,7 @@ __global__ void __launch_bounds__(kConsumers + 32, 1) chain_kernel(const __grid_
                     const uint32_t w0 = (t >> 5) * 32u;
                     if (w0 < bpc) fetch_prepare_shared(o, w0, stamp, (unsigned long long)G * stamp, a, s_xchg + (t >> 5) * kStageWords);
                     consumer_sync(TC);
+                    const uint32_t b = t % bpc;
                     const uint32_t *src = s_xchg + (b >> 5) * kStageWords + (b & 31u);
 #pragma unroll
                     for (int i = 0; i < 8; i++) { xb.p0[i] = src[i * 32]; xb.p1[i] = src[(8 + i) * 32]; xb.p2[i] = src[(16 + i) * 32]; }
@@ -463,13 +504,14 @@ __global__ void __launch_bounds__(kConsumers + 32, 1) chain_kernel(const __grid_
                 // shadow the last active thread in full rounds (nothing reads what they produce)
                 const uint32_t tt = has_block ? t : o.active - 1u;
                 const uint32_t off_a = q4 ? tt * 16u : tt * 36u, off_h = o.hdr_off + tt * 4u;
+                const uint32_t cpr = (uint32_t)R * o.lanes;                     // columns per round
 
-                for (uint32_t pass0 = 0; pass0 < sh.passes; pass0 += R, round++) {
+                for (uint32_t col0 = 0; col0 < sh.ncols; col0 += cpr, round++) {
                     const uint32_t group = (round & 1u) * R, parity = (round >> 1) & 1u;
                     const uint32_t tile0 = ring0 + group * a.slot_bytes, full_g = full0 + 8u * group, empty_g = empty0 + 8u * group;
                     // partial sums go straight to the staging buffer of this round (nothing is held across passes)
                     float *part = s_red + (size_t)(round & 1u) * R * TC + t;
-                    if ((pass0 + R) * o_lanes <= sh.ncols) {
+                    if (col0 + cpr <= sh.ncols) {
                         // full round: R whole passes, no predicates.  The warp is converged, so the loads of all its
                         // lanes are one instruction that precedes the elected lane's arrival in program order.
                         if (q4) {
@@ -498,14 +540,15 @@ __global__ void __launch_bounds__(kConsumers + 32, 1) chain_kernel(const __grid_
                         }
                     } else {
                         // last round of the op: fewer than R passes, or a last pass with fewer columns
+                        const uint32_t o_lanes = o.lanes;
 #pragma unroll
                         for (int u = 0; u < R; u++) {
                             part[u * TC] = 0.f;
-                            const uint32_t pass = pass0 + u;
-                            if (pass < sh.passes) {                               // CTA-uniform
+                            const uint32_t first_col = col0 + (uint32_t)u * o_lanes;
+                            if (first_col < sh.ncols) {                           // CTA-uniform: the pass exists
                                 mbar_wait(full_g + 8u * u, parity, a);
                                 const uint32_t tile = tile0 + (uint32_t)u * a.slot_bytes;
-                                const bool live = has_block && pass * o_lanes + lane_col < sh.ncols;
+                                const bool live = first_col + my_col < sh.ncols;
                                 uint4 q = make_uint4(0, 0, 0, 0);
                                 uint32_t c[9];
 #pragma unroll
@@ -534,21 +577,23 @@ __global__ void __launch_bounds__(kConsumers + 32, 1) chain_kernel(const __grid_
                         }
                     }
                     // ---- finish the round's columns
-                    consumer_sync(TC);
-                    const uint32_t rel = pass0 * o_lanes + fin_rel;                          // column inside this CTA's range
-                    const bool store = fin_writer && rel < sh.ncols;
+                    if (sync) named_sync(sync & 15u, sync >> 4);
+                    const uint32_t rel = col0 + ((fin >> 22) & 511u);                        // column inside this CTA's range
+                    const bool store = (fin >> 31) != 0u && rel < sh.ncols;
                     float add = 0.f;
                     if (store && o.addend) add = __ldcg(o.addend + sh.c0 + rel);             // in flight during the sums below
                     float s = 0.f;
-                    const float *src = s_red + (size_t)(round & 1u) * R * TC + fin_src;
-                    if (!(fin_cnt & 0x80000000u)) {
-                        for (uint32_t j = 0; j < fin_cnt; j += 4) {
+                    const float *src = s_red + (size_t)(round & 1u) * R * TC + (fin & 4095u);
+                    const uint32_t cnt = (fin >> 12) & 511u;
+                    if (!(fin & (1u << 21))) {
+                        for (uint32_t j = 0; j < cnt; j += 4) {
                             const float4 q = *reinterpret_cast<const float4 *>(src + j);
                             s += (q.x + q.y) + (q.z + q.w);
                         }
                     } else {
-                        for (uint32_t j = 0; j < (fin_cnt & 0x7FFFFFFFu); j++) s += src[j];
+                        for (uint32_t j = 0; j < cnt; j++) s += src[j];
                     }
+                    const uint32_t o_shift = o.red_shift;
                     if (o_shift == 5) {                       // a whole warp per column
                         s += __shfl_xor_sync(0xffffffffu, s, 16);
                         s += __shfl_xor_sync(0xffffffffu, s, 8);
@@ -570,18 +615,21 @@ __global__ void __launch_bounds__(kConsumers + 32, 1) chain_kernel(const __grid_
                         // consume results computed from incomplete inputs under a valid stamp
                         if (col < pub_cols && *abort_flag_ptr() == 0u) {
                             const size_t at = (size_t)o.pub_rank * pub_cols + col;
-                            unsigned long long *const *tab = o.pub_tab;
+                            const unsigned long long *tab = reinterpret_cast<const unsigned long long *>(smem + 384) + (op & 1u) * kMaxPeers;
                             for (uint32_t q = 0; q < o.pub_world; q++)
-                                st_elem(reinterpret_cast<unsigned long long *>(__ldg(reinterpret_cast<const unsigned long long *>(tab + q))) + at, v, stamp);
+                                st_elem(reinterpret_cast<unsigned long long *>(tab[q]) + at, v, stamp);
                         }
                     }
                 }
             }
             if (o.arrive) {
-                // publish this CTA's part of the op to readers of the plain vector: results, then the arrival
-                __threadfence();
+                // publish this CTA's part of the op to readers of the plain vector: the barrier orders every
+                // consumer's stores before thread 0's fence, which is cumulative, then the arrival
                 consumer_sync(TC);
-                if (t == 0) atomicAdd(a.done + op, 1ull);
+                if (t == 0) {
+                    __threadfence();
+                    atomicAdd(a.done + op, 1ull);
+                }
             }
         }
         // ---- the token ends when the last gathered vector is complete on this GPU
@@ -644,6 +692,8 @@ int shape_op(ChainOp &d, size_t i, uint32_t tc, uint32_t round)
     const uint32_t cols_per_round = round * lanes;
     d.red_shift = 0;
     while (d.red_shift < 5 && (cols_per_round << (d.red_shift + 1)) <= tc && (2u << d.red_shift) <= bpc) d.red_shift++;
+    // whole warps per column and at least one of them per pass of a round: columns reduce on their own
+    d.group_sync = (bpc % 32u == 0u && bpc / 32u >= round && lanes <= 14u && d.red_shift == 5u) ? 1u : 0u;
     const uint32_t fl = 1u << d.red_shift;
     d.red_chunk = (bpc + fl - 1) / fl;
     if (d.red_chunk % 4 != 0 && bpc % 4 == 0 && d.red_chunk > 4) d.red_chunk = (d.red_chunk + 3u) & ~3u;
@@ -698,7 +748,7 @@ int layout_for(const ChainOp *ops, size_t count, uint32_t tc, uint32_t round, in
     L.round = round;
     L.slot_bytes = (slot + 127u) & ~127u;
     L.xchg_bytes = (xchg + 127u) & ~127u;
-    L.smem = 384 + count * sizeof(ChainOp) + L.xchg_bytes + (size_t)2 * round * tc * sizeof(float) + (size_t)2 * round * L.slot_bytes;
+    L.smem = kHeadBytes + count * sizeof(ChainOp) + L.xchg_bytes + (size_t)2 * round * tc * sizeof(float) + (size_t)2 * round * L.slot_bytes;
     if (L.smem > (size_t)optin) return fail(MGQ_ERR_SHAPE, "plan needs %zu B of shared memory, device allows %d", L.smem, optin);
     return MGQ_OK;
 }

@@ -158,6 +158,15 @@ int mgq_gemv_exchange(int fmt, const float *x, const void *w, const float *adden
 int mgq_exchange_finish(const mgq_exchange_elem *last_vec, uint32_t length, unsigned long long *epoch,
                         unsigned int *error, unsigned int *blocks_done, void *stream);
 
+/* The same exchange for the operators between the GEMVs of a sharded model: stores `slice`
+ * (slice_len plain floats: this rank's part, e.g. its heads' attention output) into every rank's
+ * gathered vector as {value, stamp} elements -- with slice == NULL nothing is stored, because the
+ * producing GEMV has pushed already -- then waits, bounded like mgq_gemv_exchange, until all `total`
+ * elements of the local gathered vector carry this token's stamp and writes their values to `out`
+ * as a plain vector.  The epoch is not changed (mgq_exchange_finish with last_vec == NULL adds one). */
+int mgq_exchange_all_gather(const float *slice, const mgq_exchange_push *push_dev, const mgq_exchange_elem *local_vec, float *out,
+                            uint32_t slice_len, uint32_t total, const unsigned long long *epoch, unsigned int *error, void *stream);
+
 /* c[m,n] = a[m,k] . dequant(w)[k,n] (+ addend[m,n]); a is f32 or bf16 row-major, c is f32.
  * Stands in for the MatMul / FusedMatMulAdd dispatches with a quantized weight_format
  * (src/compile.rs:1408-1419, 1511-1522; src/shaders/matmul.wgsl:28-109).
@@ -334,6 +343,7 @@ typedef struct mgq_session mgq_session;
 #define MGQ_SHADER_SWIGLU            10
 #define MGQ_SHADER_SWIGLU_CONCAT     11
 #define MGQ_SHADER_ROPE_CACHE_WRITE  12   /* RoPEDynamic x2 + CacheWrite x2 merged (no reference entry) */
+#define MGQ_SHADER_ALL_GATHER        13   /* column-sharded sessions: slice -> whole vector over peer memory (no reference entry) */
 
 mgq_graph *mgq_graph_new(void);
 void mgq_graph_free(mgq_graph *g);
@@ -359,6 +369,15 @@ int mgq_graph_cached_attention(mgq_graph *g, int q, int k_cache, int v_cache, in
                                uint32_t num_kv_heads, uint32_t head_dim);
 int mgq_graph_swiglu(mgq_graph *g, int gate, int up);
 int mgq_graph_swiglu_concat(mgq_graph *g, int input);
+/* No reference counterpart (the reference is single-device): x is this rank's [1, n] slice of a
+ * vector that every rank needs whole; the node is the [1, n * world] vector, rank-major.  A graph
+ * that holds such nodes is one rank's part of a column-sharded model: its weights are this rank's
+ * column slices, its attention works on this rank's heads, and every all_gather must be bound to
+ * peer-visible memory (mgq_session_bind_exchange) before the first step. */
+int mgq_graph_all_gather(mgq_graph *g, int x, uint32_t world);
+/* Columns [first, first + count) of a [1, n] f32 node, without a copy (first % 4 == 0): the part of
+ * a whole vector that belongs to this rank, e.g. the residual a sharded projection adds to. */
+int mgq_graph_slice_columns(mgq_graph *g, int x, uint32_t first, uint32_t count);
 int mgq_graph_set_outputs(mgq_graph *g, const int *ids, size_t count);
 
 /* build_inference_session (src/train.rs:380-389): fuse, lower, allocate zero-filled buffers. */
@@ -412,6 +431,22 @@ uint64_t mgq_session_launch_count(const mgq_session *s);
  * reorder_by_level + compute_groups (src/runtime.rs:1202-1256), available on plain buffer-id lists
  * as mgq_barrier_groups (four input and four output ids per dispatch, -1 for none; reorder != 0
  * sorts by dependency level first, as the reference does when it builds a session). */
+/* Column-sharded sessions.  mgq_session_num_exchanges counts the all_gather nodes (in execution
+ * order); mgq_session_exchange_info gives the floats this rank contributes and the number of ranks.
+ * mgq_session_bind_exchange hands exchange `index` its push record (device memory, gather_cols ==
+ * slice length) and this rank's gathered vector of slice_len * world elements, which every rank must
+ * be able to store into (symmetric or IPC memory).  mgq_session_bind_exchange_state gives the token
+ * index, the error word and a zeroed scratch word, all in local device memory; every rank must have
+ * made the same number of steps.  A single-row GEMV that feeds an all_gather pushes its columns
+ * itself ("session.fuse_exchange", default 1).  Every step ends by adding one to the token index.
+ * mgq_session_check_exchange synchronises the stream and returns MGQ_ERR_TIMEOUT if a bounded wait
+ * of an earlier step ran out (the word is cleared). */
+int mgq_session_num_exchanges(const mgq_session *s);
+int mgq_session_exchange_info(const mgq_session *s, size_t index, uint32_t *slice_len, uint32_t *world);
+int mgq_session_bind_exchange(mgq_session *s, size_t index, const mgq_exchange_push *push_dev, mgq_exchange_elem *local_vec);
+int mgq_session_bind_exchange_state(mgq_session *s, unsigned long long *epoch, unsigned int *error, unsigned int *blocks_done);
+int mgq_session_check_exchange(mgq_session *s);
+
 int mgq_session_set_profiling(mgq_session *s, int enabled);
 int mgq_session_gpu_timings(mgq_session *s, float *microseconds, size_t count);
 int mgq_session_dump_gpu_timings(mgq_session *s, char *out, size_t cap);

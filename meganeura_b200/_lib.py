@@ -75,6 +75,7 @@ SIGNATURES = {
     "mgq_argmax": (_int, [_vp, _u32, _vp, _vp, _vp, _vp, _vp, _u32, _vp]),
     "mgq_gemv_exchange": (_int, [_int, _vp, _vp, _vp, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
     "mgq_exchange_finish": (_int, [_vp, _u32, _vp, _vp, _vp, _vp]),
+    "mgq_exchange_all_gather": (_int, [_vp, _vp, _vp, _vp, _u32, _u32, _vp, _vp, _vp]),
     "mgq_gemm": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_matmul": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_matmul_host": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32]),
@@ -101,6 +102,8 @@ SIGNATURES = {
     "mgq_graph_cached_attention": (_int, [_vp, _int, _int, _int, _int, _u32, _u32, _u32]),
     "mgq_graph_swiglu": (_int, [_vp, _int, _int]),
     "mgq_graph_swiglu_concat": (_int, [_vp, _int]),
+    "mgq_graph_all_gather": (_int, [_vp, _int, _u32]),
+    "mgq_graph_slice_columns": (_int, [_vp, _int, _u32, _u32]),
     "mgq_graph_set_outputs": (_int, [_vp, ctypes.POINTER(_int), _sz]),
     "mgq_build_inference_session": (_int, [_vp, ctypes.POINTER(_vp)]),
     "mgq_session_free": (None, [_vp]),
@@ -125,6 +128,11 @@ SIGNATURES = {
     "mgq_session_gpu_timings": (_int, [_vp, _vp, _sz]),
     "mgq_session_dump_gpu_timings": (_int, [_vp, ctypes.c_char_p, _sz]),
     "mgq_session_num_groups": (_int, [_vp]),
+    "mgq_session_num_exchanges": (_int, [_vp]),
+    "mgq_session_exchange_info": (_int, [_vp, _sz, ctypes.POINTER(_u32), ctypes.POINTER(_u32)]),
+    "mgq_session_bind_exchange": (_int, [_vp, _sz, _vp, _vp]),
+    "mgq_session_bind_exchange_state": (_int, [_vp, _vp, _vp, _vp]),
+    "mgq_session_check_exchange": (_int, [_vp]),
     "mgq_barrier_groups": (_int, [_vp, _vp, _sz, _int]),
 }
 

@@ -569,6 +569,59 @@ int launch_exchange_finish(const void *last_vec, uint32_t length, unsigned long 
     return MGQ_OK;
 }
 
+// All-gather of a plain vector slice over peer memory, for the operators between the GEMVs of a
+// column-sharded model (attention output, SwiGLU output) and for turning a gathered vector back into
+// a plain one: every CTA first stores its part of this rank's slice as {value, stamp} elements into
+// every rank's gathered vector (skipped when the producing GEMV has already pushed it), then waits
+// -- bounded -- for its part of the whole local vector and writes the values out plain.  The waits
+// are for other GPUs' stores and for stores of this launch's own CTAs made before they wait, so the
+// grid is kept small enough to be resident at once.
+__global__ void __launch_bounds__(256) all_gather_kernel(const float *slice, const mgq_exchange_push *push, const float2 *local_vec,
+                                                         float *out, uint32_t slice_len, uint32_t total,
+                                                         const unsigned long long *epoch, unsigned int *error, unsigned long long wait_ns)
+{
+    const uint32_t stamp = dev::exchange_stamp(epoch);
+    const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x, nthreads = gridDim.x * blockDim.x;
+    if (slice) {
+        const uint32_t world = push->world;
+        const size_t at = (size_t)push->rank * push->gather_cols;
+        for (uint32_t i = tid; i < slice_len; i += nthreads) {
+            const float v = slice[i];
+            const unsigned long long e = (unsigned long long)__float_as_uint(v) | ((unsigned long long)stamp << 32);
+            for (uint32_t q = 0; q < world; q++)
+                asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(reinterpret_cast<unsigned long long *>(push->dst[q]) + at + i), "l"(e) : "memory");
+        }
+    }
+    for (uint32_t i = tid; i < total; i += nthreads) {
+        unsigned long long t0 = 0, e;
+        for (uint32_t spins = 0;; spins++) {
+            asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(e) : "l"(local_vec + i) : "memory");
+            if ((uint32_t)(e >> 32) == stamp) break;
+            if ((spins & 31u) == 31u) {
+                if (*reinterpret_cast<const volatile uint32_t *>(error) != 0u) break;
+                const unsigned long long now = dev::global_timer_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > wait_ns) { atomicExch(error, 1u); break; }
+            }
+        }
+        out[i] = __uint_as_float((uint32_t)e);
+    }
+}
+
+int launch_all_gather(const float *slice, const void *push_dev, const void *local_vec, float *out, uint32_t slice_len, uint32_t total,
+                      const unsigned long long *epoch, unsigned int *error, void *stream_v)
+{
+    const uint32_t threads = 256;
+    uint32_t grid = (total + threads - 1) / threads;
+    if (grid > 148) grid = 148;
+    if (grid < 1) grid = 1;
+    all_gather_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream_v)>>>(
+        slice, static_cast<const mgq_exchange_push *>(push_dev), static_cast<const float2 *>(local_vec), out, slice_len, total, epoch,
+        error, exchange_wait_ns());
+    MGQ_CUDA(cudaGetLastError());
+    return MGQ_OK;
+}
+
 bool gemv_streamable(const void *x, uint32_t k, uint32_t n)
 {
     const uint32_t bpc = k / 32;

@@ -41,7 +41,7 @@ constexpr int kU32 = 100;         // node dtype of input_u32 (not a weight forma
 
 enum class Op {
     Input, Parameter, MatMul, Add, FusedMatMulAdd, Embedding, RmsNorm, RoPE, CacheWrite, CachedAttention,
-    SwiGLU, SwiGLUConcat, View, Nop
+    SwiGLU, SwiGLUConcat, AllGather, View, Nop
 };
 
 struct Node {
@@ -65,6 +65,8 @@ struct Dispatch {
     int weight_format;
     float f0;
     void *workspace;
+    int exchange = -1;            // all_gather: which exchange; GEMV: the exchange it pushes its columns to (-1: none)
+    bool push_done = false;       // all_gather: the producing GEMV has pushed the slice already
     std::string label;
 };
 
@@ -102,12 +104,21 @@ const char *shader_name(int s)
         case MGQ_SHADER_SWIGLU: return "SwiGLU";
         case MGQ_SHADER_SWIGLU_CONCAT: return "SwiGLUConcat";
         case MGQ_SHADER_ROPE_CACHE_WRITE: return "RoPEDynamic+CacheWrite";
+        case MGQ_SHADER_ALL_GATHER: return "AllGather";
     }
     return "?";
 }
 
 int g_fuse_rope_cache = 1;        // "session.fuse_rope_cache"
 int g_horizontal_fusion = 2;      // "session.horizontal_fusion": 0 none, 1 gate|up only (the reference's), 2 every same-input GEMV group
+int g_fuse_exchange = 1;          // "session.fuse_exchange": a GEMV that feeds an all_gather pushes its columns itself
+
+// One all_gather of a column-sharded session: what the caller bound to it.
+struct Exchange {
+    uint32_t slice_len = 0, world = 0;
+    const mgq_exchange_push *push_dev = nullptr;
+    mgq_exchange_elem *local_vec = nullptr;
+};
 
 }  // namespace
 
@@ -121,6 +132,10 @@ int set_session_option(const char *name, long value)
     }
     if (!std::strcmp(name, "session.fuse_rope_cache")) {
         g_fuse_rope_cache = value ? 1 : 0;
+        return MGQ_OK;
+    }
+    if (!std::strcmp(name, "session.fuse_exchange")) {
+        g_fuse_exchange = value ? 1 : 0;
         return MGQ_OK;
     }
     return fail(MGQ_ERR_NAME, "unknown option: %s", name);
@@ -157,6 +172,10 @@ struct mgq_session {
     void *greedy_ws = nullptr;
     uint32_t *greedy_token = nullptr, *greedy_history = nullptr;
     uint32_t greedy_cap = 0;
+    // column-sharded sessions: the all_gathers and the words of the exchange protocol
+    std::vector<Exchange> exchanges;
+    unsigned long long *xchg_epoch = nullptr;
+    unsigned int *xchg_error = nullptr, *xchg_blocks = nullptr;
 
     void *ptr(int node) const
     {
@@ -325,6 +344,33 @@ int mgq_graph_swiglu_concat(mgq_graph *g, int input)
     if (ni.shape.size() != 2) return -fail(MGQ_ERR_SHAPE, "swiglu_concat requires 2D input");
     if (ni.shape[1] % 2 != 0) return -fail(MGQ_ERR_SHAPE, "SwiGLUConcat requires even N");
     return push_node(g, Node{Op::SwiGLUConcat, "", {ni.shape[0], ni.shape[1] / 2}, MGQ_FMT_F32, {input}});
+}
+
+int mgq_graph_slice_columns(mgq_graph *g, int x, uint32_t first, uint32_t count)
+{
+    if (!g) return -fail(MGQ_ERR_NULL, "null graph");
+    if (!valid(g, x)) return -fail(MGQ_ERR_NAME, "slice_columns: node id out of range");
+    const Node &nx = g->nodes[x];
+    if (nx.dtype != MGQ_FMT_F32 || nx.shape.size() != 2 || nx.shape[0] != 1)
+        return -fail(MGQ_ERR_SHAPE, "slice_columns: the source must be a [1, n] f32 tensor");
+    if (count == 0 || (size_t)first + count > nx.shape[1] || first % 4 != 0)
+        return -fail(MGQ_ERR_SHAPE, "slice_columns: [%u, %u) is not a 16-byte aligned range of %zu columns", first, first + count, nx.shape[1]);
+    Node nd{Op::View, "", {1, count}, MGQ_FMT_F32, {x}};
+    nd.u0 = first;
+    return push_node(g, std::move(nd));
+}
+
+int mgq_graph_all_gather(mgq_graph *g, int x, uint32_t world)
+{
+    if (!g) return -fail(MGQ_ERR_NULL, "null graph");
+    if (!valid(g, x)) return -fail(MGQ_ERR_NAME, "all_gather: node id out of range");
+    const Node &nx = g->nodes[x];
+    if (nx.dtype != MGQ_FMT_F32 || nx.shape.size() != 2 || nx.shape[0] != 1)
+        return -fail(MGQ_ERR_SHAPE, "all_gather: the slice must be a [1, n] f32 tensor");
+    if (world < 1 || world > MGQ_MAX_PEERS) return -fail(MGQ_ERR_SHAPE, "all_gather: world must be 1..%d", MGQ_MAX_PEERS);
+    Node nd{Op::AllGather, "", {1, nx.shape[1] * world}, MGQ_FMT_F32, {x}};
+    nd.u0 = world;
+    return push_node(g, std::move(nd));
 }
 
 int mgq_graph_set_outputs(mgq_graph *g, const int *ids, size_t count)
@@ -651,6 +697,29 @@ int mgq_build_inference_session(const mgq_graph *g, mgq_session **out)
                 set_label(d, "SwiGLUConcat[%u]", len);
                 break;
             }
+            case Op::AllGather: {
+                d.shader = MGQ_SHADER_ALL_GATHER;
+                Exchange ex;
+                ex.slice_len = (uint32_t)s->nodes[nd.inputs[0]].elements();
+                ex.world = nd.u0;
+                d.exchange = (int)s->exchanges.size();
+                s->exchanges.push_back(ex);
+                d.params[0] = ex.slice_len; d.params[1] = ex.world; d.params[2] = ex.slice_len * ex.world;
+                d.workgroups[0] = (d.params[2] + 255) / 256;
+                set_label(d, "AllGather[%ux%u]", ex.world, ex.slice_len);
+                // a single-row GEMV whose whole output is the slice stores its columns into the ranks'
+                // gathered vectors itself; the all_gather then only waits and unpacks
+                if (g_fuse_exchange && !s->dispatches.empty()) {
+                    Dispatch &prev = s->dispatches.back();
+                    const bool gemv = prev.shader == MGQ_SHADER_MATMUL_GEMV || prev.shader == MGQ_SHADER_MATMUL_GEMV_ADD;
+                    if (gemv && prev.out == nd.inputs[0] && prev.params[0] == 1 && prev.params[2] == ex.slice_len &&
+                        mgq::is_quant(prev.weight_format) && prev.exchange < 0) {
+                        prev.exchange = d.exchange;
+                        d.push_done = true;
+                    }
+                }
+                break;
+            }
             default: continue;           // Input, Parameter, View, Nop: nothing to run
         }
         s->dispatches.push_back(d);
@@ -889,14 +958,41 @@ static int run_dispatch(mgq_session *s, const Dispatch &d)
         case MGQ_SHADER_SWIGLU_CONCAT:
             if (d.in[1] >= 0) return mgq_swiglu(f(0), f(1), outp, d.params[0] / d.params[1], d.params[1], d.params[2], s->stream);
             return mgq_swiglu(f(0), f(0) + d.params[1], outp, d.params[0] / d.params[1], d.params[1], d.params[2], s->stream);
+        case MGQ_SHADER_ALL_GATHER: {
+            const Exchange &ex = s->exchanges[d.exchange];
+            return mgq_exchange_all_gather(d.push_done ? nullptr : f(0), ex.push_dev, ex.local_vec, outp, ex.slice_len,
+                                           ex.slice_len * ex.world, s->xchg_epoch, s->xchg_error, s->stream);
+        }
         default: {
             const float *addend = d.in[2] >= 0 ? f(2) : nullptr;
+            if (d.exchange >= 0) {
+                const Exchange &ex = s->exchanges[d.exchange];
+                return mgq_gemv_exchange(d.weight_format, f(0), s->ptr(d.in[1]), addend, outp, d.params[1], d.params[2], ex.push_dev,
+                                         nullptr, s->xchg_epoch, s->xchg_error, s->stream);
+            }
             if (d.weight_format == MGQ_FMT_F16)
                 return mgq_gemv_f16(f(0), s->ptr(d.in[1]), addend, outp, d.params[0], d.params[1], d.params[2], s->stream);
             return mgq_matmul(d.weight_format, s->ptr(d.in[0]), MGQ_A_F32, s->ptr(d.in[1]), addend, outp, d.params[0], d.params[1],
                               d.params[2], s->stream);
         }
     }
+}
+
+// A sharded step ends by adding one to the token index (every gathered vector of the step has been
+// waited for by its all_gather, so nothing is left to poll).
+static int end_token(mgq_session *s)
+{
+    if (s->exchanges.empty()) return MGQ_OK;
+    return mgq_exchange_finish(nullptr, 0, s->xchg_epoch, s->xchg_error, s->xchg_blocks, s->stream);
+}
+
+static int exchanges_bound(const mgq_session *s)
+{
+    if (s->exchanges.empty()) return MGQ_OK;
+    if (!s->xchg_epoch || !s->xchg_error || !s->xchg_blocks) return fail(MGQ_ERR_STATE, "sharded session: bind the exchange state before the first step");
+    for (size_t i = 0; i < s->exchanges.size(); i++)
+        if (!s->exchanges[i].push_dev || !s->exchanges[i].local_vec) return fail(MGQ_ERR_STATE, "sharded session: exchange %zu is not bound", i);
+    return MGQ_OK;
 }
 
 static int enqueue_all(mgq_session *s)
@@ -910,7 +1006,7 @@ static int enqueue_all(mgq_session *s)
                                   static_cast<uint32_t *>(s->ptr(s->greedy_pos_input)), s->greedy_history, s->greedy_cap, s->stream);
         if (rc) return rc;
     }
-    return MGQ_OK;
+    return end_token(s);
 }
 
 // Profiled step (Session::step with profiling on, src/runtime.rs:2851-2861): every dispatch on its own,
@@ -939,13 +1035,14 @@ static int enqueue_profiled(mgq_session *s)
             return rc;
     }
     s->profiled = true;
-    return MGQ_OK;
+    return end_token(s);
 }
 
 int mgq_session_step(mgq_session *s)
 {
     if (!s) return fail(MGQ_ERR_NULL, "null session");
     MGQ_CUDA(cudaSetDevice(s->device));
+    if (int rc = exchanges_bound(s)) return rc;
     nvtxRangePushA("step");                      // the reference's span name (src/runtime.rs:2843)
     int rc = MGQ_OK;
     if (s->profiling) {
@@ -957,8 +1054,56 @@ int mgq_session_step(mgq_session *s)
     }
     nvtxRangePop();
     if (rc) return rc;
-    s->launches += s->dispatches.size() + (s->greedy ? 1 : 0);
+    s->launches += s->dispatches.size() + (s->greedy ? 1 : 0) + (s->exchanges.empty() ? 0 : 1);
     return MGQ_OK;
+}
+
+int mgq_session_num_exchanges(const mgq_session *s) { return s ? (int)s->exchanges.size() : -fail(MGQ_ERR_NULL, "null session"); }
+
+int mgq_session_exchange_info(const mgq_session *s, size_t index, uint32_t *slice_len, uint32_t *world)
+{
+    if (!s) return fail(MGQ_ERR_NULL, "null session");
+    if (index >= s->exchanges.size()) return fail(MGQ_ERR_NAME, "exchange index %zu out of range", index);
+    if (slice_len) *slice_len = s->exchanges[index].slice_len;
+    if (world) *world = s->exchanges[index].world;
+    return MGQ_OK;
+}
+
+int mgq_session_bind_exchange(mgq_session *s, size_t index, const mgq_exchange_push *push_dev, mgq_exchange_elem *local_vec)
+{
+    if (!s || !push_dev || !local_vec) return fail(MGQ_ERR_NULL, "null argument");
+    if (index >= s->exchanges.size()) return fail(MGQ_ERR_NAME, "exchange index %zu out of range", index);
+    if (s->graph_exec) return fail(MGQ_ERR_STATE, "bind exchanges before mgq_session_capture");
+    if (reinterpret_cast<uintptr_t>(local_vec) % 16 != 0) return fail(MGQ_ERR_ALIGN, "the gathered vector must be 16-byte aligned");
+    mgq_exchange_push rec;
+    MGQ_CUDA(cudaMemcpy(&rec, push_dev, sizeof rec, cudaMemcpyDeviceToHost));
+    const Exchange &ex = s->exchanges[index];
+    if (rec.world != ex.world || rec.rank >= rec.world || rec.gather_cols != ex.slice_len)
+        return fail(MGQ_ERR_SHAPE, "exchange %zu: the push record (world %u, rank %u, %u columns) does not fit the all_gather (world %u, %u columns)",
+                    index, rec.world, rec.rank, rec.gather_cols, ex.world, ex.slice_len);
+    s->exchanges[index].push_dev = push_dev;
+    s->exchanges[index].local_vec = local_vec;
+    return MGQ_OK;
+}
+
+int mgq_session_bind_exchange_state(mgq_session *s, unsigned long long *epoch, unsigned int *error, unsigned int *blocks_done)
+{
+    if (!s || !epoch || !error || !blocks_done) return fail(MGQ_ERR_NULL, "null argument");
+    if (s->graph_exec) return fail(MGQ_ERR_STATE, "bind exchanges before mgq_session_capture");
+    s->xchg_epoch = epoch; s->xchg_error = error; s->xchg_blocks = blocks_done;
+    return MGQ_OK;
+}
+
+int mgq_session_check_exchange(mgq_session *s)
+{
+    if (!s) return fail(MGQ_ERR_NULL, "null session");
+    if (s->exchanges.empty() || !s->xchg_error) return MGQ_OK;
+    MGQ_CUDA(cudaStreamSynchronize(s->stream));
+    unsigned int err = 0;
+    MGQ_CUDA(cudaMemcpy(&err, s->xchg_error, sizeof err, cudaMemcpyDeviceToHost));
+    if (!err) return MGQ_OK;
+    MGQ_CUDA(cudaMemset(s->xchg_error, 0, sizeof err));
+    return fail(MGQ_ERR_TIMEOUT, "a wait for another rank's part of a gathered vector ran out");
 }
 
 int mgq_session_set_profiling(mgq_session *s, int enabled)

@@ -8,6 +8,14 @@ quantized parameters.
     swiglu, down matmul + residual] -> rms_norm -> lm_head matmul
 
 The session fuses o/down with their residual adds, q|k|v and gate|up into single GEMVs.
+
+With world > 1 the same builder makes ONE RANK'S part of the column-sharded model (no reference
+counterpart, the reference is single-device): every projection holds this rank's column range,
+attention works on this rank's query heads and their KV heads, and four all_gathers per layer
+(attention output, hidden state after o, SwiGLU output, hidden state after down) plus one for the
+logits put the slices together over peer memory.  Columns never share a quantization block, each
+head is local to one rank and the gathers are rank-major, so every rank computes, bit for bit, the
+logits of the unsharded model.
 """
 from __future__ import annotations
 
@@ -60,9 +68,32 @@ def _qparam(g: Graph, fmt: int, name: str, shape):
     return g.parameter_q4(name, shape) if fmt == FMT_Q4 else g.parameter_q8(name, shape)
 
 
-def build_decode_graph(g: Graph, cfg: DecoderConfig, max_seq_len: int):
-    """Returns (logits, k_cache_params, v_cache_params), like the reference's build_decode_graph."""
-    hidden, kv_dim, ffn = cfg.hidden_size, cfg.kv_dim, cfg.intermediate_size
+def check_world(cfg: DecoderConfig, world: int) -> None:
+    for what, n in (("KV heads", cfg.num_key_value_heads), ("query heads", cfg.num_attention_heads)):
+        if n % world != 0:
+            raise ValueError(f"{n} {what} do not divide over {world} ranks")
+    for what, n in (("hidden size", cfg.hidden_size), ("intermediate size", cfg.intermediate_size), ("vocabulary", cfg.vocab_size)):
+        if n % (4 * world) != 0:
+            raise ValueError(f"{what} {n}: each rank's slice must be a multiple of 4 columns ({world} ranks)")
+
+
+def build_decode_graph(g: Graph, cfg: DecoderConfig, max_seq_len: int, rank: int = 0, world: int = 1, gather_always: bool = False):
+    """Returns (logits, k_cache_params, v_cache_params), like the reference's build_decode_graph.
+    world > 1: this rank's part of the column-sharded model (gather_always builds the same graph,
+    all_gathers included, for a single rank)."""
+    check_world(cfg, world)
+    sharded = world > 1 or gather_always
+    hidden, ffn = cfg.hidden_size, cfg.intermediate_size
+    q_loc, kv_loc, ffn_loc, hid_loc, vocab_loc = (cfg.q_dim // world, cfg.kv_dim // world, ffn // world, hidden // world,
+                                                  cfg.vocab_size // world)
+    heads_loc, kv_heads_loc = cfg.num_attention_heads // world, cfg.num_key_value_heads // world
+
+    def gather(x):
+        return g.all_gather(x, world) if sharded else x
+
+    def mine(x):                     # this rank's columns of a whole hidden-state vector
+        return g.slice_columns(x, rank * hid_loc, hid_loc) if sharded else x
+
     token_ids = g.input_u32("token_ids", [1])
     kv_pos = g.input_u32("kv_pos", [1])
     embed = g.parameter("model.embed_tokens.weight", [cfg.vocab_size, hidden])
@@ -71,29 +102,29 @@ def build_decode_graph(g: Graph, cfg: DecoderConfig, max_seq_len: int):
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}"
         h = g.rms_norm(x, g.parameter(f"{p}.input_layernorm.weight", [hidden]), cfg.rms_norm_eps)
-        wq = _qparam(g, cfg.attn_fmt, f"{p}.self_attn.q_proj.weight", [hidden, cfg.q_dim])
-        wk = _qparam(g, cfg.attn_fmt, f"{p}.self_attn.k_proj.weight", [hidden, kv_dim])
-        wv = _qparam(g, cfg.attn_fmt, f"{p}.self_attn.v_proj.weight", [hidden, kv_dim])
+        wq = _qparam(g, cfg.attn_fmt, f"{p}.self_attn.q_proj.weight", [hidden, q_loc])
+        wk = _qparam(g, cfg.attn_fmt, f"{p}.self_attn.k_proj.weight", [hidden, kv_loc])
+        wv = _qparam(g, cfg.attn_fmt, f"{p}.self_attn.v_proj.weight", [hidden, kv_loc])
         q, k, v = g.matmul(h, wq), g.matmul(h, wk), g.matmul(h, wv)
         q = g.rope_dynamic_offset(q, cfg.rope_theta, kv_pos, cfg.head_dim)
         k = g.rope_dynamic_offset(k, cfg.rope_theta, kv_pos, cfg.head_dim)
-        k_cache = g.parameter(f"kv_cache.layer.{i}.k", [max_seq_len, kv_dim])
-        v_cache = g.parameter(f"kv_cache.layer.{i}.v", [max_seq_len, kv_dim])
+        k_cache = g.parameter(f"kv_cache.layer.{i}.k", [max_seq_len, kv_loc])
+        v_cache = g.parameter(f"kv_cache.layer.{i}.v", [max_seq_len, kv_loc])
         k_caches.append(k_cache)
         v_caches.append(v_cache)
         g.cache_write(k, k_cache, kv_pos)
         g.cache_write(v, v_cache, kv_pos)
-        attn = g.cached_attention(q, k_cache, v_cache, kv_pos, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
-        wo = _qparam(g, cfg.attn_fmt, f"{p}.self_attn.o_proj.weight", [cfg.q_dim, hidden])
-        x = g.add(x, g.matmul(attn, wo))
+        attn = gather(g.cached_attention(q, k_cache, v_cache, kv_pos, heads_loc, kv_heads_loc, cfg.head_dim))
+        wo = _qparam(g, cfg.attn_fmt, f"{p}.self_attn.o_proj.weight", [cfg.q_dim, hid_loc])
+        x = gather(g.add(mine(x), g.matmul(attn, wo)))
         h = g.rms_norm(x, g.parameter(f"{p}.post_attention_layernorm.weight", [hidden]), cfg.rms_norm_eps)
-        w_gate = _qparam(g, cfg.mlp_fmt, f"{p}.mlp.gate_proj.weight", [hidden, ffn])
-        w_up = _qparam(g, cfg.mlp_fmt, f"{p}.mlp.up_proj.weight", [hidden, ffn])
-        w_down = _qparam(g, cfg.mlp_fmt, f"{p}.mlp.down_proj.weight", [ffn, hidden])
-        ffn_out = g.swiglu(g.matmul(h, w_gate), g.matmul(h, w_up))
-        x = g.add(x, g.matmul(ffn_out, w_down))
+        w_gate = _qparam(g, cfg.mlp_fmt, f"{p}.mlp.gate_proj.weight", [hidden, ffn_loc])
+        w_up = _qparam(g, cfg.mlp_fmt, f"{p}.mlp.up_proj.weight", [hidden, ffn_loc])
+        w_down = _qparam(g, cfg.mlp_fmt, f"{p}.mlp.down_proj.weight", [ffn, hid_loc])
+        ffn_out = gather(g.swiglu(g.matmul(h, w_gate), g.matmul(h, w_up)))
+        x = gather(g.add(mine(x), g.matmul(ffn_out, w_down)))
     x = g.rms_norm(x, g.parameter("model.norm.weight", [hidden]), cfg.rms_norm_eps)
-    logits = g.matmul(x, _qparam(g, cfg.head_fmt, "lm_head.weight", [hidden, cfg.vocab_size]))
+    logits = gather(g.matmul(x, _qparam(g, cfg.head_fmt, "lm_head.weight", [hidden, vocab_loc])))
     return logits, k_caches, v_caches
 
 
@@ -133,14 +164,28 @@ class DecodeSession:
     (the lm_head of an eighth of the vocabulary), so the 30 GB of f32 an 8B-parameter model would
     need are never materialised and start-up stays in seconds."""
 
-    def __init__(self, cfg: DecoderConfig, max_seq_len: int, seed: int = 0, greedy_history: int = 0, base_cols: int = 256):
+    def __init__(self, cfg: DecoderConfig, max_seq_len: int, seed: int = 0, greedy_history: int = 0, base_cols: int = 256,
+                 rank: int = 0, world: int = 1, group=None, gather_always: bool = False):
+        """world > 1 (under torch.distributed, one process per GPU): this rank's part of the sharded
+        model, holding its column range of the very same weights, with the all_gathers bound to a
+        symmetric-memory PeerExchange.  gather_always: the sharded graph for a single rank."""
         from . import ops
-        self.cfg, self.max_seq_len = cfg, max_seq_len
+        self.cfg, self.max_seq_len, self.rank, self.world = cfg, max_seq_len, rank, world
         g = Graph()
-        logits, self.k_caches, self.v_caches = build_decode_graph(g, cfg, max_seq_len)
+        logits, self.k_caches, self.v_caches = build_decode_graph(g, cfg, max_seq_len, rank, world, gather_always)
         g.set_outputs([logits])
         self.session: Session = build_inference_session(g)
         s = self.session
+        self.exchange = None
+        slices = s.exchange_slices()
+        if slices:
+            if world > 1:
+                from .exchange import PeerExchange
+                self.exchange = PeerExchange(slices, rank, world, group)
+            else:
+                from .exchange import LocalExchange
+                self.exchange = LocalExchange(slices)
+            s.bind_exchanges(self.exchange)
         rng = np.random.Generator(np.random.PCG64(seed))
         table = rng.standard_normal((cfg.vocab_size, cfg.hidden_size), dtype=np.float32)
         s.set_parameter("model.embed_tokens.weight", table)
@@ -157,18 +202,25 @@ class DecodeSession:
                     cols //= 2
             wrng = np.random.Generator(np.random.PCG64(seed * 1000003 + 17 * idx + 1))
             w = wrng.standard_normal((k, cols), dtype=np.float32) * np.float32(0.02)
-            s.upload_param(name, synth.tile_columns(fmt, ops.quantize(fmt, w), k, cols, n // cols))
+            packed = synth.tile_columns(fmt, ops.quantize(fmt, w), k, cols, n // cols)
+            if world > 1:
+                per = n // world
+                packed = ops.shard_columns(fmt, packed, k, n, rank * per, (rank + 1) * per)
+            s.upload_param(name, packed)
         if greedy_history:
             s.enable_greedy(0, "token_ids", "kv_pos", greedy_history)
 
     def fill_caches(self, upto: int, seed: int = 1, scale: float = 0.1) -> None:
-        """Pretend `upto` tokens were already decoded: cache rows [0, upto) get N(0,1)*scale."""
+        """Pretend `upto` tokens were already decoded: cache rows [0, upto) get N(0,1)*scale (a sharded
+        rank keeps the columns of its own KV heads of the same rows)."""
         rng = np.random.Generator(np.random.PCG64(seed))
+        kv_loc = self.cfg.kv_dim // self.world
         for i in range(self.cfg.num_hidden_layers):
             for kind in ("k", "v"):
                 rows = np.zeros((self.max_seq_len, self.cfg.kv_dim), dtype=np.float32)
                 rows[:upto] = rng.standard_normal((upto, self.cfg.kv_dim), dtype=np.float32) * scale
-                self.session.set_parameter(f"kv_cache.layer.{i}.{kind}", rows)
+                mine = np.ascontiguousarray(rows[:, self.rank * kv_loc:(self.rank + 1) * kv_loc])
+                self.session.set_parameter(f"kv_cache.layer.{i}.{kind}", mine)
 
     def set_position(self, token: int, pos: int) -> None:
         self.session.set_input_u32("token_ids", [token])
@@ -180,3 +232,7 @@ class DecodeSession:
     def logits(self) -> np.ndarray:
         self.session.wait()
         return self.session.read_output(self.cfg.vocab_size)
+
+    def check_exchange(self) -> None:
+        """Raises if a wait for another rank ran out in an earlier step (sharded sessions)."""
+        self.session.check_exchange()

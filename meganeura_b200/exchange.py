@@ -99,3 +99,43 @@ class PeerExchange:
         import torch
         torch.cuda.synchronize()
         return int(self.buf[self.off_error: self.off_error + 4].view(torch.int32).item())
+
+
+class LocalExchange:
+    """The same layout in ordinary device memory for a single rank (world 1): every all_gather then
+    stores into and reads from this GPU's own vectors.  Exercises the exchange path without peers."""
+
+    def __init__(self, gather_sizes):
+        import torch
+        self.rank, self.world = 0, 1
+        self.gather_sizes = list(gather_sizes)
+        self.n_ops = len(self.gather_sizes)
+        self.off_epoch, self.off_error, self.off_blocks = 0, 8, 12
+        off = 256
+        self.off_gather = []
+        for g in self.gather_sizes:
+            self.off_gather.append(off)
+            off += (8 * g + 255) // 256 * 256
+        self.buf = torch.zeros(off, dtype=torch.uint8, device="cuda")
+        self.local = self.buf.data_ptr()
+        descs = (_lib.ExchangePush * self.n_ops)()
+        for i, g in enumerate(self.gather_sizes):
+            descs[i].world, descs[i].rank, descs[i].gather_cols = 1, 0, g
+            descs[i].dst[0] = self.local + self.off_gather[i]
+        self.desc_dev = torch.from_numpy(np.frombuffer(bytes(descs), dtype=np.uint8).copy()).cuda()
+        self.desc_size = ctypes.sizeof(_lib.ExchangePush)
+        torch.cuda.synchronize()
+
+    def push_ptr(self, op: int):
+        return self.desc_dev.data_ptr() + op * self.desc_size
+
+    def vec_ptr(self, op: int) -> int:
+        return self.local + self.off_gather[op]
+
+    @property
+    def epoch_ptr(self) -> int:
+        return self.local + self.off_epoch
+
+    @property
+    def error_ptr(self) -> int:
+        return self.local + self.off_error

@@ -30,6 +30,7 @@ class ShaderEntry(IntEnum):
     SwiGLU = 10
     SwiGLUConcat = 11
     RoPECacheWrite = 12
+    AllGather = 13
 
 
 class WeightFormat(IntEnum):
@@ -118,6 +119,15 @@ class Graph:
 
     def swiglu_concat(self, x: int) -> int:
         return _node(lib.mgq_graph_swiglu_concat(self._h, x))
+
+    def all_gather(self, x: int, world: int) -> int:
+        """This rank's [1, n] slice -> the whole [1, n * world] vector, rank-major (column-sharded
+        models; no reference counterpart: the reference is single-device)."""
+        return _node(lib.mgq_graph_all_gather(self._h, x, world))
+
+    def slice_columns(self, x: int, first: int, count: int) -> int:
+        """Columns [first, first + count) of a [1, n] node, as a view."""
+        return _node(lib.mgq_graph_slice_columns(self._h, x, first, count))
 
     def set_outputs(self, ids) -> None:
         arr = (ctypes.c_int * len(ids))(*ids)
@@ -222,6 +232,29 @@ class Session:
         if n < 0:
             check(-n)
         return n
+
+    # ---- column-sharded sessions (graphs with all_gather nodes)
+    def exchange_slices(self):
+        """Floats this rank contributes to each all_gather, in execution order."""
+        n = int(lib.mgq_session_num_exchanges(self._h))
+        if n < 0:
+            check(-n)
+        out = []
+        for i in range(n):
+            slice_len, world = ctypes.c_uint32(), ctypes.c_uint32()
+            check(lib.mgq_session_exchange_info(self._h, i, ctypes.byref(slice_len), ctypes.byref(world)))
+            out.append(int(slice_len.value))
+        return out
+
+    def bind_exchanges(self, exchange) -> None:
+        """Binds every all_gather to a PeerExchange built from exchange_slices() (kept alive here)."""
+        for i in range(len(exchange.gather_sizes)):
+            check(lib.mgq_session_bind_exchange(self._h, i, exchange.push_ptr(i), exchange.vec_ptr(i)))
+        check(lib.mgq_session_bind_exchange_state(self._h, exchange.epoch_ptr, exchange.error_ptr, exchange.local + exchange.off_blocks))
+        self._exchange = exchange
+
+    def check_exchange(self) -> None:
+        check(lib.mgq_session_check_exchange(self._h))
 
 
 def build_inference_session(graph: Graph) -> Session:

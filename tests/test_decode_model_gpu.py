@@ -204,3 +204,52 @@ def test_checkpoint_round_trip_in_the_reference_file_layout(tmp_path):
     assert np.array_equal(s2.read_output(cfg.vocab_size), want)
     with pytest.raises(Exception):
         s2.load_checkpoint(tmp_path / "missing.safetensors")
+
+
+def test_all_gather_graph_on_one_rank_matches_the_plain_graph():
+    """The column-sharded graph built for a single rank (every all_gather stores into and waits on this
+    GPU's own vectors; o, down and the lm_head push their columns from inside the GEMV) gives the plain
+    graph's logits bit for bit, eagerly, after capture, and with the fused push switched off."""
+    from meganeura_b200 import decode_model as M, ops
+    from meganeura_b200.graph import ShaderEntry as S
+    cfg = _configs()["qwen3"]
+    plain = M.DecodeSession(cfg, MAX_SEQ, seed=3)
+    outs = {}
+    for fuse in (1, 0):
+        ops.set_option("session.fuse_exchange", fuse)
+        try:
+            sharded = M.DecodeSession(cfg, MAX_SEQ, seed=3, gather_always=True)
+        finally:
+            ops.set_option("session.fuse_exchange", 1)
+        shaders = [d.shader for d in sharded.session.plan().dispatches]
+        assert shaders.count(S.AllGather) == 4 * cfg.num_hidden_layers + 1
+        assert sharded.session.exchange_slices()[:4] == [cfg.q_dim, cfg.hidden_size, cfg.intermediate_size, cfg.hidden_size]
+        for dec in (plain, sharded):
+            dec.fill_caches(20, seed=9)
+        got = []
+        for step, (tok, pos) in enumerate([(5, 20), (77, 21), (901, 22), (3, 23)]):
+            if step == 2:
+                sharded.session.capture()
+            want = None
+            for dec in (plain, sharded):
+                dec.set_position(tok, pos)
+                dec.step()
+                if dec is plain:
+                    want = dec.logits()
+            sharded.check_exchange()
+            assert np.array_equal(sharded.logits(), want), f"fuse_exchange={fuse}, step {step}"
+            got.append(want)
+        outs[fuse] = got
+    assert np.isfinite(outs[1][-1]).all()
+
+
+def test_unbound_all_gather_is_refused():
+    import meganeura_b200 as mg
+    from meganeura_b200 import decode_model as M
+    cfg = _configs()["qwen3"]
+    g = mg.Graph()
+    logits, _, _ = M.build_decode_graph(g, cfg, 32, gather_always=True)
+    g.set_outputs([logits])
+    s = mg.build_inference_session(g)
+    with pytest.raises(Exception, match="bind"):
+        s.step()

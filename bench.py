@@ -290,6 +290,83 @@ def decode_tokens_per_s(model: str, steps: int = 128, context: int = 2048):
     return out
 
 
+def decode_sharded_tokens_per_s(model: str, rank: int, world: int, steps: int = 128, context: int = 2048):
+    """The same whole-model greedy decode column-sharded over `world` GPUs: every rank holds its
+    column range of every projection and its heads' KV cache and runs its own captured CUDA graph;
+    slices travel through all_gathers over peer memory (four per layer and the logits).  Timed by
+    the host clock on every rank (launch of `steps` tokens to the last token read), max over ranks.
+    Checked: every rank picked the same tokens, and they are the tokens the unsharded model picks
+    on rank 0's GPU (the logits are bit-identical by construction)."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from meganeura_b200 import decode_model as M
+    cfg = M.QWEN3_8B if model == "qwen3-8b" else M.SMOLLM2_135M
+    try:
+        M.check_world(cfg, world)
+    except ValueError as e:
+        return {"skipped": str(e)}
+    if cfg is M.SMOLLM2_135M:
+        context = 128
+    max_seq = context + steps + 8
+    dec = M.DecodeSession(cfg, max_seq, seed=3, greedy_history=max_seq, rank=rank, world=world)
+    dec.fill_caches(context)
+    s = dec.session
+    dist.barrier()
+    dec.set_position(1, context)
+    s.step()
+    s.wait()
+    s.capture()
+    dec.set_position(1, context)
+    for _ in range(3):
+        s.step()
+    s.wait()
+    dec.set_position(1, context)
+    dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        s.step()
+    s.wait()
+    tokens = np.asarray(s.read_tokens(context, steps), dtype=np.int64)
+    dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device="cuda")
+    dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+    dt = float(dt.item())
+    timeout = False
+    try:
+        dec.check_exchange()
+    except Exception:
+        timeout = True
+    finite = bool(np.isfinite(s.read_output(cfg.vocab_size)).all())
+    mine = torch.from_numpy(tokens).cuda()
+    everyone = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(everyone, mine)
+    same = all(bool(torch.equal(t, mine)) for t in everyone)
+    flag = torch.tensor([1 if timeout else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    launches = len(s.plan().dispatches) + 2
+    del dec, s
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    ref = M.DecodeSession(cfg, max_seq, seed=3, greedy_history=max_seq)
+    ref.fill_caches(context)
+    ref.set_position(1, context)
+    for _ in range(steps):
+        ref.step()
+    ref.session.wait()
+    want = np.asarray(ref.session.read_tokens(context, steps), dtype=np.int64)
+    distinct = int(len(set(int(t) for t in tokens)))
+    out = {"model": f"{cfg.name}-shaped, column-sharded over {world} GPUs", "tokens_per_s": round(steps / dt, 1),
+           "ms_per_token": round(dt / steps * 1e3, 4), "steps": steps, "kv_context": context, "batch": 1,
+           "launches_per_token": launches, "all_gathers_per_token": 4 * cfg.num_hidden_layers + 1,
+           "timing": "host wall clock, launch of the first token to the last token read, max over ranks",
+           "same_tokens_on_every_rank": same, "tokens_equal_unsharded_model": bool(np.array_equal(tokens, want)),
+           "distinct_tokens": distinct, "logits_finite": finite, "wait_ran_out": bool(flag.item())}
+    if not (same and out["tokens_equal_unsharded_model"] and finite) or out["wait_ran_out"] or distinct <= 1:
+        out["invalid"] = "sharded decode differs from the unsharded model, is degenerate, or a wait ran out"
+    return out
+
+
 def gemm_case(peak_tflops, which):
     """BASELINE config 3: Q8 prefill GEMM 512 x 4096 x 14336, bf16 activations, on the tcgen05 kernel."""
     import torch
@@ -628,6 +705,13 @@ def main():
                 line["decode"] = decode_tokens_per_s(args.model)
                 other = "smollm2-135m" if args.model == "qwen3-8b" else "qwen3-8b"
                 line["decode_" + other.split("-")[0]] = decode_tokens_per_s(other)
+    sharded = None
+    if world > 1 and args.batch == 1 and not args.no_extras and not args.no_decode:
+        chain.graph = None
+        sharded = decode_sharded_tokens_per_s(args.model, rank, world)
+    if rank == 0:
+        if sharded is not None:
+            line["decode_sharded"] = sharded
         print(json.dumps(line))
         if check is not None and not check["ok"]:
             sys.stdout.flush()

@@ -705,11 +705,28 @@ def main():
                 line["decode"] = decode_tokens_per_s(args.model)
                 other = "smollm2-135m" if args.model == "qwen3-8b" else "qwen3-8b"
                 line["decode_" + other.split("-")[0]] = decode_tokens_per_s(other)
-    sharded = None
-    if world > 1 and args.batch == 1 and not args.no_extras and not args.no_decode:
+    sharded, batch8 = None, None
+    if world > 1 and args.batch == 1 and not args.no_extras:
         chain.graph = None
-        sharded = decode_sharded_tokens_per_s(args.model, rank, world)
+        # eight tokens per step over the same column shards: the 8-row GEMV kernel with NCCL all-gathers between the
+        # ops (the peer exchange carries one row)
+        b8 = dc.DecodeGemvChain(shape, fmt, batch=8, rank=rank, world=world, seed=0, mode="launches", exchange="nccl")
+        b8.capture()
+        dist.barrier()
+        ms8 = torch.tensor([cuda_timed(b8.step, max(5, args.steps // 2), warmup=3)], device="cuda")
+        dist.all_reduce(ms8, op=dist.ReduceOp.MAX)
+        ms8 = float(ms8.item())
+        batch8 = {"ms_per_step": round(ms8, 4), "tokens_per_s": round(8 / (ms8 * 1e-3), 1),
+                  "weight_gbs": round(b8.bytes_per_step() * world / ms8 / 1e6, 1), "exchange": "nccl all_gather_into_tensor",
+                  "kernel": "gemv_mma_kernel (8 rows per pass over W)"}
+        b8.graph = None
+        del b8
+        torch.cuda.empty_cache()
+        if not args.no_decode:
+            sharded = decode_sharded_tokens_per_s(args.model, rank, world)
     if rank == 0:
+        if batch8 is not None:
+            line["batch8"] = batch8
         if sharded is not None:
             line["decode_sharded"] = sharded
         print(json.dumps(line))

@@ -76,7 +76,10 @@ const char *mgq_version(void);
  *                               1 gate|up under a SwiGLU only (the reference's rule,
  *                               src/optimize.rs:776-879), 2 every such group, e.g. q|k|v (default)
  *   "session.fuse_rope_cache"   1 (default): RoPE(q), RoPE(k), CacheWrite(k), CacheWrite(v) of a decode
- *                               layer run as one launch; 0: four dispatches like the reference */
+ *                               layer run as one launch; 0: four dispatches like the reference
+ *   "session.fuse_exchange"     1 (default): in a column-sharded session a single-row GEMV whose output
+ *                               feeds an all_gather stores its columns into the ranks' gathered vectors
+ *                               itself; 0: the all_gather does */
 int mgq_set_option(const char *name, long value);
 
 /* ---- format: TensorType::size_bytes for quantized dtypes (src/graph.rs:52-68) ---------- */
@@ -163,7 +166,8 @@ int mgq_exchange_finish(const mgq_exchange_elem *last_vec, uint32_t length, unsi
  * gathered vector as {value, stamp} elements -- with slice == NULL nothing is stored, because the
  * producing GEMV has pushed already -- then waits, bounded like mgq_gemv_exchange, until all `total`
  * elements of the local gathered vector carry this token's stamp and writes their values to `out`
- * as a plain vector.  The epoch is not changed (mgq_exchange_finish with last_vec == NULL adds one). */
+ * as a plain vector; with out == NULL it only stores (the reader, a GEMV given the vector as its
+ * wait_vec, waits itself).  The epoch is not changed (mgq_exchange_finish with last_vec == NULL adds one). */
 int mgq_exchange_all_gather(const float *slice, const mgq_exchange_push *push_dev, const mgq_exchange_elem *local_vec, float *out,
                             uint32_t slice_len, uint32_t total, const unsigned long long *epoch, unsigned int *error, void *stream);
 

@@ -187,7 +187,8 @@ int mgq_exchange_finish(const mgq_exchange_elem *last_vec, uint32_t length, unsi
 int mgq_exchange_all_gather(const float *slice, const mgq_exchange_push *push_dev, const mgq_exchange_elem *local_vec, float *out,
                             uint32_t slice_len, uint32_t total, const unsigned long long *epoch, unsigned int *error, void *stream)
 {
-    if (!local_vec || !out || !epoch || !error) return fail(MGQ_ERR_NULL, "all_gather needs the local gathered vector, the output and the epoch and error words");
+    if (!local_vec || !epoch || !error) return fail(MGQ_ERR_NULL, "all_gather needs the local gathered vector and the epoch and error words");
+    if (!out && !slice) return fail(MGQ_ERR_NULL, "all_gather: nothing to store and nothing to wait for");
     if (slice && !push_dev) return fail(MGQ_ERR_NULL, "all_gather: a slice to push needs its push record");
     if (total == 0 || slice_len > total) return fail(MGQ_ERR_SHAPE, "all_gather: bad lengths (slice %u, total %u)", slice_len, total);
     if (reinterpret_cast<uintptr_t>(local_vec) % 8 != 0) return fail(MGQ_ERR_ALIGN, "the gathered vector must be 8-byte aligned");

@@ -592,6 +592,7 @@ __global__ void __launch_bounds__(256) all_gather_kernel(const float *slice, con
                 asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(reinterpret_cast<unsigned long long *>(push->dst[q]) + at + i), "l"(e) : "memory");
         }
     }
+    if (!out) return;                                 // store only: the reader waits for the elements itself
     for (uint32_t i = tid; i < total; i += nthreads) {
         unsigned long long t0 = 0, e;
         for (uint32_t spins = 0;; spins++) {
@@ -612,7 +613,7 @@ int launch_all_gather(const float *slice, const void *push_dev, const void *loca
                       const unsigned long long *epoch, unsigned int *error, void *stream_v)
 {
     const uint32_t threads = 256;
-    uint32_t grid = (total + threads - 1) / threads;
+    uint32_t grid = ((out ? total : slice_len) + threads - 1) / threads;
     if (grid > 148) grid = 148;
     if (grid < 1) grid = 1;
     all_gather_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream_v)>>>(

@@ -489,7 +489,7 @@ def parity_check(chain, coracle_threads=8):
     return {"ok": ok, "rel_l2_vs_oracle": float(f"{worst:.3e}"), "max_rel_l2_per_op_vs_gemv_kernel": float(f"{per_op:.3e}"),
             "rel_l2_chain_vs_other_mode": float(f"{rel:.3e}"),
             "tolerance": 1e-4, "chain_tolerance": 1e-3, "logits_finite": finite,
-            "what": "layer 0 op by op and a 4096-column strip of lm_head vs the f64 CPU oracle; final logits vs one launch per GEMV"}
+            "what": "layer 0 op by op and a 4096-column strip of lm_head vs the f64 CPU oracle; every GEMV vs the stand-alone kernel on the same activations; final logits vs the other way of running the chain"}
 
 
 def parity_check_sharded(chain, shape_key, fmt, seed):

@@ -97,3 +97,31 @@ def test_all_gather_reassembles_columns_gloo(groups, m):
     for p in procs:
         p.join(timeout=60)
     assert sorted(results) == [(0, True), (1, True)]
+
+
+def test_sharded_decode_graph_builds_for_every_rank():
+    """Host side of the column-sharded session: every rank's graph builds with the sliced shapes, the
+    all_gather / slice_columns builders check their arguments, and a model whose heads or widths do
+    not divide over the ranks is refused before anything is built."""
+    from dataclasses import replace
+    import meganeura_b200 as mg
+    from meganeura_b200 import decode_model as M
+    cfg = replace(M.QWEN3_8B, name="t", vocab_size=4096, hidden_size=512, num_hidden_layers=2,
+                  num_attention_heads=4, num_key_value_heads=2, intermediate_size=1024)
+    for world in (1, 2):
+        for rank in range(world):
+            g = mg.Graph()
+            logits, k_caches, v_caches = M.build_decode_graph(g, cfg, 64, rank, world)
+            g.set_outputs([logits])
+            assert len(k_caches) == len(v_caches) == 2
+    with pytest.raises(ValueError, match="KV heads"):
+        M.build_decode_graph(mg.Graph(), cfg, 64, 0, 4)
+    with pytest.raises(ValueError, match="multiple of 4"):
+        M.build_decode_graph(mg.Graph(), replace(cfg, vocab_size=4100), 64, 0, 2)
+    g = mg.Graph()
+    x = g.input("x", [1, 64])
+    assert g.all_gather(x, 2) >= 0 and g.slice_columns(x, 32, 32) >= 0
+    for bad in (lambda: g.all_gather(x, 0), lambda: g.all_gather(x, 9), lambda: g.slice_columns(x, 48, 32),
+                lambda: g.slice_columns(x, 2, 8), lambda: g.all_gather(g.input("m", [2, 64]), 2)):
+        with pytest.raises(Exception):
+            bad()

@@ -123,6 +123,10 @@ int mgq_gemv(int fmt, const float *x, const void *w, const float *addend, float 
  * aligned.  mgq_convert_f16 is the host conversion (round to nearest even, like half::f16::from_f32). */
 int mgq_gemv_f16(const float *x, const void *w_f16, const float *addend, float *y, uint32_t m, uint32_t k, uint32_t n, void *stream);
 int mgq_convert_f16(const float *src, size_t len, uint16_t *dst);
+/* MatMulGemvBT (src/shaders/matmul_gemv_bt.wgsl:34-65; src/compile.rs:1447-1469): y[n] = sum_k x[k] * b[n, k]
+ * with b an f32 [N, K] row-major matrix -- the lm_head of a model with tied embeddings, b being the
+ * embedding table.  K % 4 == 0; x and b 16-byte aligned. */
+int mgq_gemv_bt(const float *x, const float *b, float *y, uint32_t k, uint32_t n, void *stream);
 
 /* ---- column-sharded GEMV with a fused all-gather over peer memory (no reference counterpart: the
  * reference is single-device, src/runtime.rs:1513-1531).
@@ -348,6 +352,7 @@ typedef struct mgq_session mgq_session;
 #define MGQ_SHADER_SWIGLU_CONCAT     11
 #define MGQ_SHADER_ROPE_CACHE_WRITE  12   /* RoPEDynamic x2 + CacheWrite x2 merged (no reference entry) */
 #define MGQ_SHADER_ALL_GATHER        13   /* column-sharded sessions: slice -> whole vector over peer memory (no reference entry) */
+#define MGQ_SHADER_MATMUL_GEMV_BT    14
 
 mgq_graph *mgq_graph_new(void);
 void mgq_graph_free(mgq_graph *g);
@@ -360,6 +365,9 @@ int mgq_graph_parameter_q8(mgq_graph *g, const char *name, const size_t *shape, 
  * right operand of a matmul with at most MGQ_GEMV_MAX_M rows and N % 8 == 0. */
 int mgq_graph_parameter_f16(mgq_graph *g, const char *name, const size_t *shape, size_t rank);
 int mgq_graph_matmul(mgq_graph *g, int a, int b);
+/* Graph::matmul_bt (src/graph.rs:809-817): a [M, K] times the transpose of an f32 parameter b [N, K].
+ * Only the single-row form (MatMulGemvBT) is lowered; m > 1 is refused when the session is built. */
+int mgq_graph_matmul_bt(mgq_graph *g, int a, int b);
 int mgq_graph_add(mgq_graph *g, int a, int b);
 /* decode-step nodes: Graph::{input_u32, embedding, rms_norm, rope_dynamic_offset, cache_write,
  * cached_attention, swiglu, swiglu_concat} (src/graph.rs:1003-1009, 1029-1040, 1062-1087, 1148-1170,

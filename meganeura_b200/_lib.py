@@ -62,6 +62,8 @@ SIGNATURES = {
     "mgq_gemv": (_int, [_int, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_gemv_f16": (_int, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_convert_f16": (_int, [_vp, _sz, _vp]),
+    "mgq_gemv_bt": (_int, [_vp, _vp, _vp, _u32, _u32, _vp]),
+    "mgq_graph_matmul_bt": (_int, [_vp, _int, _int]),
     "mgq_graph_parameter_f16": (_int, [_vp, ctypes.c_char_p, _szp, _sz]),
     "mgq_embedding": (_int, [_vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_rms_norm": (_int, [_vp, _vp, _vp, _u32, _u32, ctypes.c_float, _vp]),

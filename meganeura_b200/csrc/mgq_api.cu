@@ -165,6 +165,15 @@ int mgq_gemv_f16(const float *x, const void *w_f16, const float *addend, float *
     return launch_gemv_f16(x, w_f16, addend, y, m, k, n, stream);
 }
 
+int mgq_gemv_bt(const float *x, const float *b, float *y, uint32_t k, uint32_t n, void *stream)
+{
+    if (!x || !b || !y) return fail(MGQ_ERR_NULL, "null operand pointer");
+    if (k == 0 || n == 0 || k % 4 != 0) return fail(MGQ_ERR_SHAPE, "gemv_bt: K=%u must be a positive multiple of 4 (N=%u)", k, n);
+    if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || reinterpret_cast<uintptr_t>(b) % 16 != 0)
+        return fail(MGQ_ERR_ALIGN, "gemv_bt: activations and weights must be 16-byte aligned");
+    return launch_gemv_bt(x, b, y, k, n, stream);
+}
+
 int mgq_gemv_exchange(int fmt, const float *x, const void *w, const float *addend, float *y, uint32_t k, uint32_t n,
                       const mgq_exchange_push *push_dev, const mgq_exchange_elem *wait_vec,
                       const unsigned long long *epoch, unsigned int *error, void *stream)

@@ -113,3 +113,64 @@ int launch_gemv_f16(const float *x, const void *w, const float *addend, float *y
 }
 
 }  // namespace mgq
+
+// ---------------------------------------------------------------------------------------------
+// Transposed f32 GEMV: y[n] = sum_k x[k] * B[n, k], B row-major [N, K] -- the reference's
+// MatMulGemvBT (src/shaders/matmul_gemv_bt.wgsl:34-65; lowering src/compile.rs:1447-1469), which a
+// model with tied embeddings uses for its lm_head (B is the embedding table).  A row of B is
+// contiguous along K, so a warp owns a row at a time and its lanes read consecutive float4 pieces
+// (the reference's K-split); two rows are in flight per warp.  HBM-bound: 4*K*N + 4*(K+N) bytes.
+namespace mgq {
+namespace {
+
+__global__ void __launch_bounds__(256) gemv_bt_kernel(const float *x, const float *b, float *y, uint32_t k, uint32_t n)
+{
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), nwarps = gridDim.x * (blockDim.x >> 5);
+    const uint32_t k4 = k / 4;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x);
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    for (uint32_t row = 2u * warp; row < n; row += 2u * nwarps) {
+        const bool two = row + 1u < n;
+        const float4 *r0 = reinterpret_cast<const float4 *>(b + (size_t)row * k);
+        const float4 *r1 = reinterpret_cast<const float4 *>(b + (size_t)(two ? row + 1u : row) * k);
+        float a0 = 0.f, a1 = 0.f;
+        for (uint32_t i = lane; i < k4; i += 32u) {
+            const float4 xv = __ldg(x4 + i), p = __ldcs(r0 + i), q = __ldcs(r1 + i);
+            a0 += xv.x * p.x + xv.y * p.y + xv.z * p.z + xv.w * p.w;
+            a1 += xv.x * q.x + xv.y * q.y + xv.z * q.z + xv.w * q.w;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            a0 += __shfl_xor_sync(0xffffffffu, a0, o);
+            a1 += __shfl_xor_sync(0xffffffffu, a1, o);
+        }
+        if (lane == 0) {
+            y[row] = a0;
+            if (two) y[row + 1u] = a1;
+        }
+    }
+}
+
+}  // namespace
+
+int launch_gemv_bt(const float *x, const float *b, float *y, uint32_t k, uint32_t n, void *stream_v)
+{
+    const uint32_t warps_needed = (n + 1) / 2;
+    uint32_t grid = (warps_needed + 7) / 8;
+    if (grid > 148u * 8u) grid = 148u * 8u;
+    cudaLaunchConfig_t lc{};
+    lc.gridDim = dim3(grid);
+    lc.blockDim = dim3(256);
+    lc.stream = static_cast<cudaStream_t>(stream_v);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    MGQ_CUDA(cudaLaunchKernelEx(&lc, gemv_bt_kernel, x, b, y, k, n));
+    return MGQ_OK;
+}
+
+}  // namespace mgq

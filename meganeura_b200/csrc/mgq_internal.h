@@ -33,6 +33,7 @@ int launch_gemv_mma(int fmt, const float *x, const void *w, const float *addend,
                     uint32_t m, uint32_t k, uint32_t n, void *stream);
 // f16-weight GEMV (mgq_gemv_f16.cu).
 int launch_gemv_f16(const float *x, const void *w, const float *addend, float *y, uint32_t m, uint32_t k, uint32_t n, void *stream);
+int launch_gemv_bt(const float *x, const float *b, float *y, uint32_t k, uint32_t n, void *stream);
 bool gemv_streamable(const void *x, uint32_t k, uint32_t n);   // the streaming kernels take this shape (else the generic kernel runs)
 int launch_exchange_finish(const void *last_vec, uint32_t length, unsigned long long *epoch,
                            unsigned int *error, unsigned int *blocks_done, void *stream);

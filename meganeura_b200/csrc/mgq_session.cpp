@@ -41,7 +41,7 @@ constexpr int kU32 = 100;         // node dtype of input_u32 (not a weight forma
 
 enum class Op {
     Input, Parameter, MatMul, Add, FusedMatMulAdd, Embedding, RmsNorm, RoPE, CacheWrite, CachedAttention,
-    SwiGLU, SwiGLUConcat, AllGather, View, Nop
+    SwiGLU, SwiGLUConcat, AllGather, MatMulBT, View, Nop
 };
 
 struct Node {
@@ -105,6 +105,7 @@ const char *shader_name(int s)
         case MGQ_SHADER_SWIGLU_CONCAT: return "SwiGLUConcat";
         case MGQ_SHADER_ROPE_CACHE_WRITE: return "RoPEDynamic+CacheWrite";
         case MGQ_SHADER_ALL_GATHER: return "AllGather";
+        case MGQ_SHADER_MATMUL_GEMV_BT: return "MatMulGemvBT";
     }
     return "?";
 }
@@ -242,6 +243,17 @@ int mgq_graph_matmul(mgq_graph *g, int a, int b)
     if (na.shape[1] != nb.shape[0]) return -fail(MGQ_ERR_SHAPE, "matmul inner dimensions must match (%zu vs %zu)", na.shape[1], nb.shape[0]);
     if (na.dtype != MGQ_FMT_F32) return -fail(MGQ_ERR_FORMAT, "matmul: the left operand must be f32");
     return push_node(g, Node{Op::MatMul, "", {na.shape[0], nb.shape[1]}, MGQ_FMT_F32, {a, b}});
+}
+
+int mgq_graph_matmul_bt(mgq_graph *g, int a, int b)
+{
+    if (!g) return -fail(MGQ_ERR_NULL, "null graph");
+    if (!valid(g, a) || !valid(g, b)) return -fail(MGQ_ERR_NAME, "matmul_bt: node id out of range");
+    const Node &na = g->nodes[a], &nb = g->nodes[b];
+    if (na.shape.size() != 2 || nb.shape.size() != 2) return -fail(MGQ_ERR_SHAPE, "matmul_bt requires 2D tensors");
+    if (na.shape[1] != nb.shape[1]) return -fail(MGQ_ERR_SHAPE, "MatMulBT: K dimensions must match (%zu vs %zu)", na.shape[1], nb.shape[1]);
+    if (na.dtype != MGQ_FMT_F32 || nb.dtype != MGQ_FMT_F32) return -fail(MGQ_ERR_FORMAT, "matmul_bt: both operands must be f32");
+    return push_node(g, Node{Op::MatMulBT, "", {na.shape[0], nb.shape[0]}, MGQ_FMT_F32, {a, b}});
 }
 
 int mgq_graph_add(mgq_graph *g, int a, int b)
@@ -618,6 +630,19 @@ int mgq_build_inference_session(const mgq_graph *g, mgq_session **out)
                 set_label(d, "%s[%ux%ux%u]", shader_name(d.shader), m, n, k);
                 break;
             }
+            case Op::MatMulBT: {
+                const Node &na = s->nodes[nd.inputs[0]], &nb = s->nodes[nd.inputs[1]];
+                const uint32_t m = (uint32_t)na.shape[0], k = (uint32_t)na.shape[1], n = (uint32_t)nb.shape[0];
+                if (m != 1 || k % 4 != 0) {          // the reference's tiled MatMulBT (m > 1) is outside this library
+                    mgq_session_free(s);
+                    return fail(MGQ_ERR_SHAPE, "matmul_bt: only the single-row form with K %% 4 == 0 is lowered (got %ux%ux%u)", m, n, k);
+                }
+                d.shader = MGQ_SHADER_MATMUL_GEMV_BT;
+                d.workgroups[0] = n;
+                d.params[0] = m; d.params[1] = n; d.params[2] = k; d.params[3] = 0;      // [m, n, k, 0] like the reference
+                set_label(d, "MatMulGemvBT[%ux%ux%u]", m, n, k);
+                break;
+            }
             case Op::Add: {
                 d.shader = MGQ_SHADER_ADD;
                 const uint32_t len = (uint32_t)nd.elements();
@@ -958,6 +983,7 @@ static int run_dispatch(mgq_session *s, const Dispatch &d)
         case MGQ_SHADER_SWIGLU_CONCAT:
             if (d.in[1] >= 0) return mgq_swiglu(f(0), f(1), outp, d.params[0] / d.params[1], d.params[1], d.params[2], s->stream);
             return mgq_swiglu(f(0), f(0) + d.params[1], outp, d.params[0] / d.params[1], d.params[1], d.params[2], s->stream);
+        case MGQ_SHADER_MATMUL_GEMV_BT: return mgq_gemv_bt(f(0), f(1), outp, d.params[2], d.params[1], s->stream);
         case MGQ_SHADER_ALL_GATHER: {
             const Exchange &ex = s->exchanges[d.exchange];
             return mgq_exchange_all_gather(d.push_done ? nullptr : f(0), ex.push_dev, ex.local_vec, outp, ex.slice_len,

@@ -43,6 +43,7 @@ class DecoderConfig:
     attn_fmt: int
     mlp_fmt: int
     head_fmt: int
+    tie_word_embeddings: bool = False       # lm_head = embed_tokens^T through matmul_bt (src/models/smollm2.rs:29-30, 413-414)
 
     @property
     def kv_dim(self) -> int:
@@ -124,7 +125,12 @@ def build_decode_graph(g: Graph, cfg: DecoderConfig, max_seq_len: int, rank: int
         ffn_out = gather(g.swiglu(g.matmul(h, w_gate), g.matmul(h, w_up)))
         x = gather(g.add(mine(x), g.matmul(ffn_out, w_down)))
     x = g.rms_norm(x, g.parameter("model.norm.weight", [hidden]), cfg.rms_norm_eps)
-    logits = gather(g.matmul(x, _qparam(g, cfg.head_fmt, "lm_head.weight", [hidden, vocab_loc])))
+    if cfg.tie_word_embeddings:
+        if sharded:
+            raise ValueError("tied embeddings are not column-sharded (the table is indexed by rows)")
+        logits = g.matmul_bt(x, embed)
+    else:
+        logits = gather(g.matmul(x, _qparam(g, cfg.head_fmt, "lm_head.weight", [hidden, vocab_loc])))
     return logits, k_caches, v_caches
 
 
@@ -140,7 +146,8 @@ def quantized_weights(cfg: DecoderConfig):
                 (f"{p}.mlp.gate_proj.weight", cfg.mlp_fmt, cfg.hidden_size, cfg.intermediate_size),
                 (f"{p}.mlp.up_proj.weight", cfg.mlp_fmt, cfg.hidden_size, cfg.intermediate_size),
                 (f"{p}.mlp.down_proj.weight", cfg.mlp_fmt, cfg.intermediate_size, cfg.hidden_size)]
-    out.append(("lm_head.weight", cfg.head_fmt, cfg.hidden_size, cfg.vocab_size))
+    if not cfg.tie_word_embeddings:
+        out.append(("lm_head.weight", cfg.head_fmt, cfg.hidden_size, cfg.vocab_size))
     return out
 
 

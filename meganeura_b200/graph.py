@@ -31,6 +31,7 @@ class ShaderEntry(IntEnum):
     SwiGLUConcat = 11
     RoPECacheWrite = 12
     AllGather = 13
+    MatMulGemvBT = 14
 
 
 class WeightFormat(IntEnum):
@@ -119,6 +120,10 @@ class Graph:
 
     def swiglu_concat(self, x: int) -> int:
         return _node(lib.mgq_graph_swiglu_concat(self._h, x))
+
+    def matmul_bt(self, a: int, b: int) -> int:
+        """Graph::matmul_bt (src/graph.rs:809-817): a [M, K] @ b[N, K]^T, b an f32 parameter."""
+        return _node(lib.mgq_graph_matmul_bt(self._h, a, b))
 
     def all_gather(self, x: int, world: int) -> int:
         """This rank's [1, n] slice -> the whole [1, n * world] vector, rank-major (column-sharded

@@ -142,4 +142,7 @@ class DecodeOracle:
             ffn = swiglu(h @ self.w[f"{p}.mlp.gate_proj.weight"], h @ self.w[f"{p}.mlp.up_proj.weight"])
             x = x + ffn @ self.w[f"{p}.mlp.down_proj.weight"]
         x = rms_norm(x, self.w["model.norm.weight"], c.rms_norm_eps)
+        if "lm_head.weight" not in self.w:
+            # tied embeddings: logits = x . embed^T (g.matmul_bt(x, embed_weight), src/models/smollm2.rs:413-414)
+            return (x @ self.w["model.embed_tokens.weight"].T).reshape(-1)
         return (x @ self.w["lm_head.weight"]).reshape(-1)

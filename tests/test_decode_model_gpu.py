@@ -253,3 +253,42 @@ def test_unbound_all_gather_is_refused():
     s = mg.build_inference_session(g)
     with pytest.raises(Exception, match="bind"):
         s.step()
+
+
+def test_tied_embeddings_use_the_transposed_gemv():
+    """tie_word_embeddings (the reference's default for SmolLM2, src/models/smollm2.rs:45, 413-414): the
+    lm_head is matmul_bt(x, embed_tokens), lowered to MatMulGemvBT with params [m, n, k, 0]."""
+    from meganeura_b200.graph import ShaderEntry as S
+    cfg = replace(_configs()["smollm2"], tie_word_embeddings=True)
+    s, oracle = _build(cfg, seed=13)
+    last = s.plan().dispatches[-1]
+    assert last.shader == S.MatMulGemvBT and last.params == (1, cfg.vocab_size, cfg.hidden_size, 0)
+    assert last.label == f"MatMulGemvBT[1x{cfg.vocab_size}x{cfg.hidden_size}]" and last.workgroups == (cfg.vocab_size, 1, 1)
+    worst = 0.0
+    for pos, tok in enumerate([9, 1500, 77]):
+        s.set_input_u32("token_ids", [tok])
+        s.set_input_u32("kv_pos", [pos])
+        s.step()
+        s.wait()
+        got = s.read_output(cfg.vocab_size).astype(np.float64)
+        worst = max(worst, O.rel_l2(got, oracle.step(int(tok), pos)))
+    assert worst <= 1e-4, f"rel-L2 {worst:.3e}"
+
+
+@pytest.mark.parametrize("k,n", [(576, 49152), (4096, 1001), (64, 7), (2048, 2)])
+def test_gemv_bt_matches_float64(k, n):
+    import ctypes
+    import torch
+    from meganeura_b200._lib import check, lib
+    rng = np.random.Generator(np.random.PCG64(k + n))
+    x = rng.standard_normal(k).astype(np.float32)
+    b = rng.standard_normal((n, k)).astype(np.float32)
+    xd, bd = torch.from_numpy(x).cuda(), torch.from_numpy(b).cuda()
+    y = torch.full((n + 8,), 123.0, device="cuda")
+    check(lib.mgq_gemv_bt(xd.data_ptr(), bd.data_ptr(), y.data_ptr(), k, n, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    want = b.astype(np.float64) @ x.astype(np.float64)
+    assert O.rel_l2(y[:n].cpu().numpy().astype(np.float64), want) <= 1e-5
+    assert bool((y[n:] == 123.0).all())                       # nothing written past the end
+    with pytest.raises(Exception):
+        check(lib.mgq_gemv_bt(xd.data_ptr(), bd.data_ptr(), y.data_ptr(), 6, n, None))

@@ -591,8 +591,6 @@ def main():
     if mode == "auto":
         mode = "plan"
     exchange = args.exchange if mode == "launches" else "peer"
-    if world > 1 and args.batch != 1:
-        exchange = "nccl"
     chain = dc.DecodeGemvChain(shape, fmt, batch=args.batch, rank=rank, world=world, seed=0, mode=mode, exchange=exchange)
     captured = chain.capture()
     if args.mode == "auto" and world == 1 and args.batch == 1:
@@ -708,17 +706,34 @@ def main():
     sharded, batch8 = None, None
     if world > 1 and args.batch == 1 and not args.no_extras:
         chain.graph = None
-        # eight tokens per step over the same column shards: the 8-row GEMV kernel with NCCL all-gathers between the
-        # ops (the peer exchange carries one row)
-        b8 = dc.DecodeGemvChain(shape, fmt, batch=8, rank=rank, world=world, seed=0, mode="launches", exchange="nccl")
+        # eight tokens per step over the same column shards: the 8-row GEMV kernel, then an all-gather kernel that stores
+        # the rank's rows into every peer's gathered vector and unpacks the whole; NCCL all-gathers timed beside it
+        b8 = dc.DecodeGemvChain(shape, fmt, batch=8, rank=rank, world=world, seed=0, mode="launches", exchange="peer")
         b8.capture()
         dist.barrier()
         ms8 = torch.tensor([cuda_timed(b8.step, max(5, args.steps // 2), warmup=3)], device="cuda")
         dist.all_reduce(ms8, op=dist.ReduceOp.MAX)
         ms8 = float(ms8.item())
+        bad8 = torch.tensor([1 if b8.check_error() else 0], device="cuda")
+        dist.all_reduce(bad8, op=dist.ReduceOp.MAX)
+        peer_logits = b8.logits_view().clone()
+        bytes8 = b8.bytes_per_step()
+        b8.graph = None
+        del b8
+        torch.cuda.empty_cache()
+        b8 = dc.DecodeGemvChain(shape, fmt, batch=8, rank=rank, world=world, seed=0, mode="launches", exchange="nccl")
+        b8.capture()
+        dist.barrier()
+        ms8n = torch.tensor([cuda_timed(b8.step, max(5, args.steps // 2), warmup=3)], device="cuda")
+        dist.all_reduce(ms8n, op=dist.ReduceOp.MAX)
+        same8 = torch.tensor([1 if bool(torch.equal(peer_logits, b8.logits_view())) else 0], device="cuda")
+        dist.all_reduce(same8, op=dist.ReduceOp.MIN)
         batch8 = {"ms_per_step": round(ms8, 4), "tokens_per_s": round(8 / (ms8 * 1e-3), 1),
-                  "weight_gbs": round(b8.bytes_per_step() * world / ms8 / 1e6, 1), "exchange": "nccl all_gather_into_tensor",
-                  "kernel": "gemv_mma_kernel (8 rows per pass over W)"}
+                  "weight_gbs": round(bytes8 * world / ms8 / 1e6, 1), "exchange": "all-gather kernel over peer memory",
+                  "kernel": "gemv_mma_kernel (8 rows per pass over W)", "nccl_ms_per_step": round(float(ms8n.item()), 4),
+                  "logits_equal_nccl_path": bool(same8.item()), "wait_ran_out": bool(bad8.item())}
+        if not batch8["logits_equal_nccl_path"] or batch8["wait_ran_out"]:
+            batch8["invalid"] = "the two exchange paths disagree or a wait ran out"
         b8.graph = None
         del b8
         torch.cuda.empty_cache()

@@ -174,6 +174,12 @@ int mgq_exchange_finish(const mgq_exchange_elem *last_vec, uint32_t length, unsi
  * wait_vec, waits itself).  The epoch is not changed (mgq_exchange_finish with last_vec == NULL adds one). */
 int mgq_exchange_all_gather(const float *slice, const mgq_exchange_push *push_dev, const mgq_exchange_elem *local_vec, float *out,
                             uint32_t slice_len, uint32_t total, const unsigned long long *epoch, unsigned int *error, void *stream);
+/* The same for several rows (a batch of tokens): this rank's slice is `rows` rows of `cols` columns,
+ * `slice_pitch` floats apart (e.g. the leading columns of a wider GEMV output); the push record's
+ * gather_cols is rows * cols; `out` is the whole row-major [rows, world * cols] matrix. */
+int mgq_exchange_all_gather_rows(const float *slice, uint32_t slice_pitch, uint32_t rows, uint32_t cols, uint32_t world,
+                                 const mgq_exchange_push *push_dev, const mgq_exchange_elem *local_vec, float *out,
+                                 const unsigned long long *epoch, unsigned int *error, void *stream);
 
 /* c[m,n] = a[m,k] . dequant(w)[k,n] (+ addend[m,n]); a is f32 or bf16 row-major, c is f32.
  * Stands in for the MatMul / FusedMatMulAdd dispatches with a quantized weight_format

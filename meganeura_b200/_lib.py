@@ -78,6 +78,7 @@ SIGNATURES = {
     "mgq_gemv_exchange": (_int, [_int, _vp, _vp, _vp, _vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
     "mgq_exchange_finish": (_int, [_vp, _u32, _vp, _vp, _vp, _vp]),
     "mgq_exchange_all_gather": (_int, [_vp, _vp, _vp, _vp, _u32, _u32, _vp, _vp, _vp]),
+    "mgq_exchange_all_gather_rows": (_int, [_vp, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mgq_gemm": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_matmul": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mgq_matmul_host": (_int, [_int, _vp, _int, _vp, _vp, _vp, _u32, _u32, _u32]),

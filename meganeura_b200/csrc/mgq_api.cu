@@ -193,15 +193,25 @@ int mgq_exchange_finish(const mgq_exchange_elem *last_vec, uint32_t length, unsi
     return launch_exchange_finish(last_vec, length, epoch, error, blocks_done, stream);
 }
 
-int mgq_exchange_all_gather(const float *slice, const mgq_exchange_push *push_dev, const mgq_exchange_elem *local_vec, float *out,
-                            uint32_t slice_len, uint32_t total, const unsigned long long *epoch, unsigned int *error, void *stream)
+int mgq_exchange_all_gather_rows(const float *slice, uint32_t slice_pitch, uint32_t rows, uint32_t cols, uint32_t world,
+                                 const mgq_exchange_push *push_dev, const mgq_exchange_elem *local_vec, float *out,
+                                 const unsigned long long *epoch, unsigned int *error, void *stream)
 {
     if (!local_vec || !epoch || !error) return fail(MGQ_ERR_NULL, "all_gather needs the local gathered vector and the epoch and error words");
     if (!out && !slice) return fail(MGQ_ERR_NULL, "all_gather: nothing to store and nothing to wait for");
     if (slice && !push_dev) return fail(MGQ_ERR_NULL, "all_gather: a slice to push needs its push record");
-    if (total == 0 || slice_len > total) return fail(MGQ_ERR_SHAPE, "all_gather: bad lengths (slice %u, total %u)", slice_len, total);
+    if (rows == 0 || cols == 0 || world == 0 || world > MGQ_MAX_PEERS || (slice && slice_pitch < cols) ||
+        (unsigned long long)rows * cols * world >= (1ull << 31))
+        return fail(MGQ_ERR_SHAPE, "all_gather: bad shape (rows %u, cols %u, pitch %u, world %u)", rows, cols, slice_pitch, world);
     if (reinterpret_cast<uintptr_t>(local_vec) % 8 != 0) return fail(MGQ_ERR_ALIGN, "the gathered vector must be 8-byte aligned");
-    return launch_all_gather(slice, push_dev, local_vec, out, slice_len, total, epoch, error, stream);
+    return launch_all_gather(slice, push_dev, local_vec, out, rows, cols, slice_pitch, world, epoch, error, stream);
+}
+
+int mgq_exchange_all_gather(const float *slice, const mgq_exchange_push *push_dev, const mgq_exchange_elem *local_vec, float *out,
+                            uint32_t slice_len, uint32_t total, const unsigned long long *epoch, unsigned int *error, void *stream)
+{
+    if (slice_len == 0 || total % slice_len != 0) return fail(MGQ_ERR_SHAPE, "all_gather: bad lengths (slice %u, total %u)", slice_len, total);
+    return mgq_exchange_all_gather_rows(slice, slice_len, 1, slice_len, total / slice_len, push_dev, local_vec, out, epoch, error, stream);
 }
 
 int mgq_gemm(int fmt, const void *a, int a_dtype, const void *w, const float *addend, float *c,

@@ -577,22 +577,26 @@ int launch_exchange_finish(const void *last_vec, uint32_t length, unsigned long 
 // are for other GPUs' stores and for stores of this launch's own CTAs made before they wait, so the
 // grid is kept small enough to be resident at once.
 __global__ void __launch_bounds__(256) all_gather_kernel(const float *slice, const mgq_exchange_push *push, const float2 *local_vec,
-                                                         float *out, uint32_t slice_len, uint32_t total,
+                                                         float *out, uint32_t rows, uint32_t cols, uint32_t pitch, uint32_t world,
                                                          const unsigned long long *epoch, unsigned int *error, unsigned long long wait_ns)
 {
+    // A rank's slice is `rows` rows of `cols` columns (row stride `pitch`); in a gathered vector the
+    // slices stand rank after rank, each row-major; `out` is the whole [rows, world * cols] matrix.
     const uint32_t stamp = dev::exchange_stamp(epoch);
     const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x, nthreads = gridDim.x * blockDim.x;
+    const uint32_t slice_len = rows * cols;
     if (slice) {
-        const uint32_t world = push->world;
         const size_t at = (size_t)push->rank * push->gather_cols;
         for (uint32_t i = tid; i < slice_len; i += nthreads) {
-            const float v = slice[i];
+            const uint32_t r = i / cols, c = i - r * cols;
+            const float v = slice[(size_t)r * pitch + c];
             const unsigned long long e = (unsigned long long)__float_as_uint(v) | ((unsigned long long)stamp << 32);
             for (uint32_t q = 0; q < world; q++)
                 asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(reinterpret_cast<unsigned long long *>(push->dst[q]) + at + i), "l"(e) : "memory");
         }
     }
     if (!out) return;                                 // store only: the reader waits for the elements itself
+    const uint32_t total = world * slice_len;
     for (uint32_t i = tid; i < total; i += nthreads) {
         unsigned long long t0 = 0, e;
         for (uint32_t spins = 0;; spins++) {
@@ -605,20 +609,21 @@ __global__ void __launch_bounds__(256) all_gather_kernel(const float *slice, con
                 else if (now - t0 > wait_ns) { atomicExch(error, 1u); break; }
             }
         }
-        out[i] = __uint_as_float((uint32_t)e);
+        const uint32_t q = i / slice_len, rem = i - q * slice_len, r = rem / cols, c = rem - r * cols;
+        out[(size_t)r * world * cols + (size_t)q * cols + c] = __uint_as_float((uint32_t)e);
     }
 }
 
-int launch_all_gather(const float *slice, const void *push_dev, const void *local_vec, float *out, uint32_t slice_len, uint32_t total,
-                      const unsigned long long *epoch, unsigned int *error, void *stream_v)
+int launch_all_gather(const float *slice, const void *push_dev, const void *local_vec, float *out, uint32_t rows, uint32_t cols,
+                      uint32_t pitch, uint32_t world, const unsigned long long *epoch, unsigned int *error, void *stream_v)
 {
     const uint32_t threads = 256;
-    uint32_t grid = ((out ? total : slice_len) + threads - 1) / threads;
+    uint32_t grid = ((out ? world : 1u) * rows * cols + threads - 1) / threads;
     if (grid > 148) grid = 148;
     if (grid < 1) grid = 1;
     all_gather_kernel<<<grid, threads, 0, static_cast<cudaStream_t>(stream_v)>>>(
-        slice, static_cast<const mgq_exchange_push *>(push_dev), static_cast<const float2 *>(local_vec), out, slice_len, total, epoch,
-        error, exchange_wait_ns());
+        slice, static_cast<const mgq_exchange_push *>(push_dev), static_cast<const float2 *>(local_vec), out, rows, cols, pitch, world,
+        epoch, error, exchange_wait_ns());
     MGQ_CUDA(cudaGetLastError());
     return MGQ_OK;
 }

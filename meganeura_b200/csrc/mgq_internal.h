@@ -37,8 +37,8 @@ int launch_gemv_bt(const float *x, const float *b, float *y, uint32_t k, uint32_
 bool gemv_streamable(const void *x, uint32_t k, uint32_t n);   // the streaming kernels take this shape (else the generic kernel runs)
 int launch_exchange_finish(const void *last_vec, uint32_t length, unsigned long long *epoch,
                            unsigned int *error, unsigned int *blocks_done, void *stream);
-int launch_all_gather(const float *slice, const void *push_dev, const void *local_vec, float *out, uint32_t slice_len, uint32_t total,
-                      const unsigned long long *epoch, unsigned int *error, void *stream);
+int launch_all_gather(const float *slice, const void *push_dev, const void *local_vec, float *out, uint32_t rows, uint32_t cols,
+                      uint32_t pitch, uint32_t world, const unsigned long long *epoch, unsigned int *error, void *stream);
 int set_gemv_option(const char *name, long value);
 int set_plan_option(const char *name, long value);
 int set_gemm_option(const char *name, long value);

@@ -142,11 +142,10 @@ class DecodeGemvChain:
         if batch != 1 and mode == "plan":
             mode = "launches"                   # the persistent kernel takes single rows
         self.mode = mode
-        # exchange between ranks: "peer" = slices pushed over NVLink by the kernels themselves,
-        # "nccl" = all_gather_into_tensor after each GEMV (launches mode only)
+        # exchange between ranks: "peer" = slices stored over NVLink by the library's own kernels (inside the GEMV
+        # for one row, by an all-gather kernel behind the GEMV for a batch of rows), "nccl" =
+        # all_gather_into_tensor after each GEMV (launches mode only)
         self.exchange = exchange if world > 1 else "none"
-        if self.exchange == "peer" and batch != 1:
-            raise ValueError("the peer exchange takes batch 1; use exchange='nccl'")
         if self.exchange == "nccl" and mode == "plan":
             raise ValueError("the persistent kernel exchanges through peer memory; use mode='launches' with NCCL")
         self.launches_per_step = 0
@@ -168,9 +167,12 @@ class DecodeGemvChain:
         self.ops_list.append(self.head)
         if self.exchange == "peer":
             from .exchange import PeerExchange
-            self.peer = PeerExchange([op["gather_cols"] for op in self.ops_list], rank, world, group)
+            self.peer = PeerExchange([self.m * op["gather_cols"] for op in self.ops_list], rank, world, group)
             for i, op in enumerate(self.ops_list):
-                op["full"] = self.peer.gathered(i)
+                if self.m == 1:
+                    op["full"] = self.peer.gathered(i)
+                elif op["gather_cols"]:                              # a batch: the gathered rows, unpacked by the all-gather kernel
+                    op["full"] = torch.zeros((self.m, world * op["gather_cols"]), dtype=torch.float32, device=self.device)
         # what each op reads: the token input, then the gathered first group of the op before it
         for i, op in enumerate(self.ops_list):
             k = op["spec"].k
@@ -184,7 +186,7 @@ class DecodeGemvChain:
                     op["x"] = prev["y"][:, :k]                      # a view: rows are n_loc apart (batch 1: contiguous)
                     if self.m > 1:
                         op["x_buf"] = torch.zeros((self.m, k), dtype=torch.float32, device=self.device)
-                elif self.exchange == "nccl":
+                elif self.exchange == "nccl" or self.m > 1:
                     op["x"] = prev["full"]
                 else:
                     op["x"] = None                                   # taken from the gathered {value, stamp} vector
@@ -249,7 +251,7 @@ class DecodeGemvChain:
             self.launches_per_step = 1
             return 1
         if self.exchange == "peer":
-            return self._launch_all_peer()
+            return self._launch_all_peer() if self.m == 1 else self._launch_all_peer_rows()
         count = 0
         for op in self.ops_list:
             sp = op["spec"]
@@ -277,6 +279,23 @@ class DecodeGemvChain:
             self.peer.gemv(self.fmt, op["x"], op["w"], op["addend"], op["y"], sp.k, op["n_loc"], i, i - 1 if i > 0 else None, stream)
         self.peer.finish(len(self.ops_list) - 1, stream)
         self.launches_per_step = len(self.ops_list) + 1
+        return self.launches_per_step
+
+    def _launch_all_peer_rows(self):
+        """A batch of rows: the 8-row GEMV kernel on the column shard, then one all-gather kernel over peer memory."""
+        import torch
+        stream = torch.cuda.current_stream().cuda_stream
+        count = 0
+        for i, op in enumerate(self.ops_list):
+            sp = op["spec"]
+            ops.matmul(self.fmt, op["x"], op["w"], sp.k, op["n_loc"], addend=op["addend"], out=op["y"], route="gemv")
+            count += 1
+            g = op["gather_cols"]
+            if g:
+                self.peer.all_gather_rows(i, op["y"], self.m, g, op["full"], stream)
+                count += 1
+        self.peer.finish(None, stream)
+        self.launches_per_step = count + 1
         return self.launches_per_step
 
     def capture(self):

@@ -90,6 +90,14 @@ class PeerExchange:
                                     y.data_ptr(), k, n, self.push_ptr(op), wait_ptr,
                                     self.epoch_ptr, self.error_ptr, stream_ptr))
 
+    def all_gather_rows(self, op: int, slice_t, rows: int, cols: int, out_t, stream_ptr):
+        """Stores this rank's [rows, cols] slice (a view with any row stride) into every rank's gathered vector of
+        `op`, waits for the whole vector and writes the row-major [rows, world * cols] matrix to out_t."""
+        if rows * cols != self.gather_sizes[op]:
+            raise ValueError(f"op {op} gathers {self.gather_sizes[op]} values per rank, got {rows}x{cols}")
+        check(lib.mgq_exchange_all_gather_rows(slice_t.data_ptr(), slice_t.stride(0), rows, cols, self.world, self.push_ptr(op),
+                                               self.vec_ptr(op), out_t.data_ptr(), self.epoch_ptr, self.error_ptr, stream_ptr))
+
     def finish(self, last_op, stream_ptr):
         last = self.vec_ptr(last_op) if last_op is not None else None
         length = self.vec_len(last_op) if last_op is not None else 0

@@ -77,6 +77,35 @@ def main():
         del chain
         if failures:
             break
+    # a batch of 8 rows: the 8-row GEMV kernel with the all-gather kernel over peer memory, against the same chain
+    # with NCCL all-gathers (bit for bit: same GEMV kernel, different transport) and against the unsharded chain
+    if not failures:
+        single8 = dc.DecodeGemvChain(dc.QWEN3_8B, 2, batch=8, rank=0, world=1, layers=layers, mode="launches")
+        single8.step()
+        torch.cuda.synchronize()
+        want8 = single8.logits_view().clone()
+        del single8
+        got = {}
+        for exchange in ("peer", "nccl"):
+            chain = dc.DecodeGemvChain(dc.QWEN3_8B, 2, batch=8, rank=rank, world=world, layers=layers, mode="launches", exchange=exchange)
+            chain._launch_all()
+            chain._launch_all()
+            if exchange == "peer" and chain.capture():
+                chain.step()
+                chain.step()
+            torch.cuda.synchronize()
+            if chain.check_error():
+                failures.append(f"batch 8 / {exchange}: a bounded wait ran out")
+            got[exchange] = chain.logits_view().clone()
+            dist.barrier()
+            chain.graph = None
+            del chain
+        if not failures:
+            if not bool(torch.equal(got["peer"], got["nccl"])):
+                failures.append("batch 8: the peer all-gather and the NCCL all-gather give different logits")
+            rel = float((got["peer"].double() - want8.double()).norm() / want8.double().norm())
+            if rel > 1e-4:
+                failures.append(f"batch 8: logits differ from the unsharded chain by rel-L2 {rel:.3e}")
     dist.barrier()
     torch.cuda.synchronize()
     print(f"rank {rank}: {'OK' if not failures else 'FAIL ' + '; '.join(failures)}", flush=True)

@@ -138,3 +138,13 @@ def test_barrier_groups_follow_the_reference_rules():
     # write-after-write alone is no hazard in the reference's rule (only reads of dirty buffers split groups)
     assert groups([([0], [1]), ([0], [1])]) == 1
     _ = ctypes
+
+
+def test_new_entry_points_check_their_arguments_without_a_gpu():
+    """Argument errors are reported before any CUDA call."""
+    from meganeura_b200._lib import MgqError, check, lib
+    for call in (lambda: lib.mgq_gemv_bt(None, None, None, 64, 8, None),
+                 lambda: lib.mgq_exchange_all_gather(None, None, None, None, 4, 8, None, None, None),
+                 lambda: lib.mgq_exchange_all_gather_rows(None, 4, 1, 4, 2, None, None, None, None, None, None)):
+        with pytest.raises(MgqError):
+            check(call())

@@ -121,3 +121,56 @@ def test_wait_that_nothing_satisfies_times_out_cleanly():
     want = ops.matmul(fmt, x, w, k, n)
     torch.cuda.synchronize()
     assert torch.isfinite(want).all()
+
+
+def test_all_gather_rows_two_ranks_emulated_on_one_gpu():
+    """mgq_exchange_all_gather_rows with both ranks' gathered vectors on this GPU: rank 0 stores only,
+    then rank 1 stores and waits (nothing waits for a later launch).  Both vectors must hold the slices
+    rank-major, and the unpacked matrix must be the row-major [rows, world * cols] whole; then a second
+    token (stamps grow), and a wait for a slice that nobody stores, which must end in the error word."""
+    import torch
+    from meganeura_b200 import _lib, ops
+    from meganeura_b200._lib import check, lib
+    rows, cols, pitch, world = 8, 96, 160, 2
+    total = world * rows * cols
+    buf = torch.zeros(256 + 2 * 8 * total + 512, dtype=torch.uint8, device="cuda")
+    vec = [buf.data_ptr() + 256, buf.data_ptr() + 256 + 8 * total + 256]
+    descs = (_lib.ExchangePush * world)()
+    for r in range(world):
+        descs[r].world, descs[r].rank, descs[r].gather_cols = world, r, rows * cols
+        for q in range(world):
+            descs[r].dst[q] = vec[q]
+    dev_descs = torch.from_numpy(np.frombuffer(bytes(descs), dtype=np.uint8).copy()).cuda()
+    push = [dev_descs.data_ptr() + r * ctypes.sizeof(_lib.ExchangePush) for r in range(world)]
+    epoch, error, blocks = buf.data_ptr(), buf.data_ptr() + 8, buf.data_ptr() + 12
+    stream = torch.cuda.current_stream().cuda_stream
+    rng = torch.Generator(device="cpu").manual_seed(3)
+    for token in range(2):
+        slices = [torch.randn((rows, pitch), generator=rng).cuda() for _ in range(world)]
+        out = torch.full((rows, world * cols), -1.0, device="cuda")
+        check(lib.mgq_exchange_all_gather_rows(slices[0].data_ptr(), pitch, rows, cols, world, push[0], vec[0], None, epoch, error, stream))
+        check(lib.mgq_exchange_all_gather_rows(slices[1].data_ptr(), pitch, rows, cols, world, push[1], vec[1], out.data_ptr(),
+                                               epoch, error, stream))
+        check(lib.mgq_exchange_finish(None, 0, epoch, error, blocks, stream))
+        torch.cuda.synchronize()
+        want = torch.cat([s[:, :cols] for s in slices], dim=1)
+        assert torch.equal(out, want)
+        for q in range(world):                                   # both ranks' vectors hold the same gathered data
+            off = vec[q] - buf.data_ptr()
+            pairs = buf[off: off + 8 * total].view(torch.float32).view(world, rows, cols, 2)
+            assert torch.equal(pairs[..., 0], torch.stack([s[:, :cols] for s in slices]))
+            assert bool((buf[off: off + 8 * total].view(torch.int32).view(-1, 2)[:, 1] == token + 1).all())
+        assert int(buf[8:12].view(torch.int32).item()) == 0
+    # third token: rank 0 never stores; rank 1's wait must give up and say so
+    ops.set_option("gemv.wait_us", 2000)
+    try:
+        out = torch.zeros((rows, world * cols), device="cuda")
+        check(lib.mgq_exchange_all_gather_rows(slices[1].data_ptr(), pitch, rows, cols, world, push[1], vec[1], out.data_ptr(),
+                                               epoch, error, stream))
+        torch.cuda.synchronize()
+        assert int(buf[8:12].view(torch.int32).item()) == 1
+    finally:
+        ops.set_option("gemv.wait_us", 0)
+    with pytest.raises(Exception):
+        check(lib.mgq_exchange_all_gather_rows(slices[1].data_ptr(), cols - 1, rows, cols, world, push[1], vec[1], out.data_ptr(),
+                                               epoch, error, stream))

@@ -15,6 +15,14 @@ without an explicit flush.
 logits are copied out inside the timed region.  `--impl reference` times the CPU restatement of
 meganeura's own kernel math (oracle/) on the host cores; the reference itself needs a Rust
 toolchain and a Vulkan device, neither of which exists here.
+
+Every line carries `parity_check` (the measured results against the CPU oracle, the stand-alone
+kernels and, on several GPUs, the unsharded chain).  Further keys unless --no-extras: on one GPU
+`other_mode`, `batch8`, `gemm` (512x4096x14336 Q8 prefill GEMM), `gemv_cases`, `decode` /
+`decode_<model>` (whole-model greedy decode through Graph / Session); on several GPUs `batch8`
+(8 rows over the column shards, peer-memory all-gather with NCCL timed beside it) and
+`decode_sharded` (the whole model column-sharded over the ranks, tokens checked against the
+unsharded model).
 """
 from __future__ import annotations
 

@@ -125,3 +125,86 @@ def test_sharded_decode_graph_builds_for_every_rank():
                 lambda: g.slice_columns(x, 2, 8), lambda: g.all_gather(g.input("m", [2, 64]), 2)):
         with pytest.raises(Exception):
             bad()
+
+
+def _sharded_decode_worker(rank, world, port, q):
+    """One rank of the column-sharded decoder in numpy: its column range of every projection, its heads'
+    caches, and the five kinds of all-gather of decode_model.build_decode_graph, over gloo."""
+    from dataclasses import replace
+    import torch
+    import torch.distributed as dist
+    from oracle import decode_oracle as D
+    from meganeura_b200 import decode_model as M
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        cfg = replace(M.QWEN3_8B, name="t", vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=64, intermediate_size=512)
+        max_seq = 16
+        rng = np.random.Generator(np.random.PCG64(21))
+        weights = {"model.embed_tokens.weight": rng.standard_normal((cfg.vocab_size, cfg.hidden_size)).astype(np.float32)}
+        for name in M.norm_weights(cfg):
+            weights[name] = (1.0 + 0.1 * rng.standard_normal(cfg.hidden_size)).astype(np.float32)
+        dense = {}
+        for name, fmt, k, n in M.quantized_weights(cfg):
+            w = (rng.standard_normal((k, n)) * (1.5 / np.sqrt(k))).astype(np.float32)
+            packed = O.quantize_q4_np(w) if fmt == O.FMT_Q4 else O.quantize_q8_np(w)
+            weights[name] = (fmt, packed, k, n)
+            dense[name] = O.dequantize_np(fmt, packed, k, n).astype(np.float64)
+        whole = D.DecodeOracle(cfg, weights, max_seq)
+
+        def gather(local):                                   # rank-major concatenation, like the all_gather node
+            parts = [torch.empty_like(torch.from_numpy(local)) for _ in range(world)]
+            dist.all_gather(parts, torch.from_numpy(np.ascontiguousarray(local)))
+            return np.concatenate([p.numpy() for p in parts], axis=-1)
+
+        def mine(w):                                         # this rank's column range of a [k, n] weight
+            per = w.shape[1] // world
+            return w[:, rank * per:(rank + 1) * per]
+
+        heads, kv_heads = cfg.num_attention_heads // world, cfg.num_key_value_heads // world
+        kv_loc, hid_loc = cfg.kv_dim // world, cfg.hidden_size // world
+        k_cache = [np.zeros((max_seq, kv_loc)) for _ in range(cfg.num_hidden_layers)]
+        v_cache = [np.zeros((max_seq, kv_loc)) for _ in range(cfg.num_hidden_layers)]
+        ok = True
+        for pos, tok in enumerate([3, 200, 77]):
+            x = D.embedding([tok], weights["model.embed_tokens.weight"]).astype(np.float64)
+            for i in range(cfg.num_hidden_layers):
+                p = f"model.layers.{i}"
+                h = D.rms_norm(x, weights[f"{p}.input_layernorm.weight"].astype(np.float64), cfg.rms_norm_eps)
+                qv = D.rope(h @ mine(dense[f"{p}.self_attn.q_proj.weight"]), cfg.rope_theta, pos, cfg.head_dim)
+                kv = D.rope(h @ mine(dense[f"{p}.self_attn.k_proj.weight"]), cfg.rope_theta, pos, cfg.head_dim)
+                vv = h @ mine(dense[f"{p}.self_attn.v_proj.weight"])
+                D.cache_write(k_cache[i], kv, pos)
+                D.cache_write(v_cache[i], vv, pos)
+                attn = gather(D.cached_attention(qv, k_cache[i], v_cache[i], pos, heads, kv_heads, cfg.head_dim))
+                x_mine = x[:, rank * hid_loc:(rank + 1) * hid_loc]
+                x = gather(x_mine + attn @ mine(dense[f"{p}.self_attn.o_proj.weight"]))
+                h = D.rms_norm(x, weights[f"{p}.post_attention_layernorm.weight"].astype(np.float64), cfg.rms_norm_eps)
+                ffn = gather(D.swiglu(h @ mine(dense[f"{p}.mlp.gate_proj.weight"]), h @ mine(dense[f"{p}.mlp.up_proj.weight"])))
+                x_mine = x[:, rank * hid_loc:(rank + 1) * hid_loc]
+                x = gather(x_mine + ffn @ mine(dense[f"{p}.mlp.down_proj.weight"]))
+            x = D.rms_norm(x, weights["model.norm.weight"].astype(np.float64), cfg.rms_norm_eps)
+            logits = gather(x @ mine(dense["lm_head.weight"])).reshape(-1)
+            want = whole.step(tok, pos)
+            ok = ok and float(np.abs(logits - want).max()) <= 1e-9 * max(1.0, float(np.abs(want).max()))
+        q.put((rank, ok))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_decode_math_matches_the_whole_model_gloo():
+    """The sharding of decode_model.build_decode_graph (heads per rank, column ranges, rank-major gathers)
+    written out with the CPU oracle's operators on two gloo ranks reproduces the unsharded oracle."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_sharded_decode_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(results) == [(0, True), (1, True)]

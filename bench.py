@@ -686,72 +686,95 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(shape_t, fmt)
         if world == 1 and args.batch == 1 and not args.no_extras:
-            # the same chain run the other way (one launch per GEMV with programmatic dependent launch, or the
-            # persistent plan kernel), CUDA graph, same weights
-            other = "launches" if mode == "plan" else "plan"
-            chain.mode, chain.graph = other, None
-            chain.capture()
-            ms_l = cuda_timed(chain.step, args.steps, warmup=args.warmup)
-            line["other_mode"] = {"mode": other, "ms_per_step": round(ms_l, 4), "gbs": round(bytes_rank / ms_l / 1e6, 1),
-                                  "frac": round(bytes_rank / ms_l / 1e6 / peak, 4), "launches_per_step": chain.launches_per_step}
+            # The extra measurements must never cost the line above them: whatever goes wrong in one of them is
+            # recorded under "extras_error" and the line is printed with the extras measured so far.
+            try:
+                # the same chain run the other way (one launch per GEMV with programmatic dependent launch, or the
+                # persistent plan kernel), CUDA graph, same weights
+                other = "launches" if mode == "plan" else "plan"
+                chain.mode, chain.graph = other, None
+                chain.capture()
+                ms_l = cuda_timed(chain.step, args.steps, warmup=args.warmup)
+                line["other_mode"] = {"mode": other, "ms_per_step": round(ms_l, 4), "gbs": round(bytes_rank / ms_l / 1e6, 1),
+                                      "frac": round(bytes_rank / ms_l / 1e6 / peak, 4), "launches_per_step": chain.launches_per_step}
+                chain.graph = None
+                del chain
+                torch.cuda.empty_cache()
+                b8 = dc.DecodeGemvChain(shape, fmt, batch=8, seed=0, mode="launches")
+                b8.capture()
+                ms8 = cuda_timed(b8.step, max(5, args.steps // 2), warmup=3)
+                line["batch8"] = {"ms_per_step": round(ms8, 4), "tokens_per_s": round(8 / (ms8 * 1e-3), 1),
+                                  "weight_gbs": round(b8.bytes_per_step() / ms8 / 1e6, 1), "kernel": "gemv_mma_kernel (8 rows per pass over W)"}
+                b8.graph = None
+                del b8
+                torch.cuda.empty_cache()
+                line["gemm"] = gemm_case(peak_tf, which)
+                line["gemv_cases"] = gemv_cases(peak)
+                if not args.no_decode:
+                    line["decode"] = decode_tokens_per_s(args.model)
+                    other = "smollm2-135m" if args.model == "qwen3-8b" else "qwen3-8b"
+                    line["decode_" + other.split("-")[0]] = decode_tokens_per_s(other)
+            except Exception as exc:
+                line["extras_error"] = repr(exc)[:300]
+    sharded, batch8, extras_error = None, None, None
+    if world > 1 and args.batch == 1 and not args.no_extras:
+        # The extra measurements must never cost the line above them.  They hold collectives, so an error on one
+        # rank can leave the others waiting: rank 0 arms a timer that prints the line as it stands and ends the
+        # process if the extras have not come back in time; an exception is recorded and the line is printed.
+        def give_up():
+            line["extras_error"] = "the extra measurements did not finish in 420 s"
+            print(json.dumps(line), flush=True)
+            os._exit(0)
+        extras_timer = threading.Timer(420.0, give_up) if rank == 0 else None
+        if extras_timer is not None:
+            extras_timer.daemon = True
+            extras_timer.start()
+        try:
             chain.graph = None
-            del chain
-            torch.cuda.empty_cache()
-            b8 = dc.DecodeGemvChain(shape, fmt, batch=8, seed=0, mode="launches")
+            # eight tokens per step over the same column shards: the 8-row GEMV kernel, then an all-gather kernel that stores
+            # the rank's rows into every peer's gathered vector and unpacks the whole; NCCL all-gathers timed beside it
+            b8 = dc.DecodeGemvChain(shape, fmt, batch=8, rank=rank, world=world, seed=0, mode="launches", exchange="peer")
             b8.capture()
-            ms8 = cuda_timed(b8.step, max(5, args.steps // 2), warmup=3)
-            line["batch8"] = {"ms_per_step": round(ms8, 4), "tokens_per_s": round(8 / (ms8 * 1e-3), 1),
-                              "weight_gbs": round(b8.bytes_per_step() / ms8 / 1e6, 1), "kernel": "gemv_mma_kernel (8 rows per pass over W)"}
+            dist.barrier()
+            ms8 = torch.tensor([cuda_timed(b8.step, max(5, args.steps // 2), warmup=3)], device="cuda")
+            dist.all_reduce(ms8, op=dist.ReduceOp.MAX)
+            ms8 = float(ms8.item())
+            bad8 = torch.tensor([1 if b8.check_error() else 0], device="cuda")
+            dist.all_reduce(bad8, op=dist.ReduceOp.MAX)
+            peer_logits = b8.logits_view().clone()
+            bytes8 = b8.bytes_per_step()
             b8.graph = None
             del b8
             torch.cuda.empty_cache()
-            line["gemm"] = gemm_case(peak_tf, which)
-            line["gemv_cases"] = gemv_cases(peak)
+            b8 = dc.DecodeGemvChain(shape, fmt, batch=8, rank=rank, world=world, seed=0, mode="launches", exchange="nccl")
+            b8.capture()
+            dist.barrier()
+            ms8n = torch.tensor([cuda_timed(b8.step, max(5, args.steps // 2), warmup=3)], device="cuda")
+            dist.all_reduce(ms8n, op=dist.ReduceOp.MAX)
+            same8 = torch.tensor([1 if bool(torch.equal(peer_logits, b8.logits_view())) else 0], device="cuda")
+            dist.all_reduce(same8, op=dist.ReduceOp.MIN)
+            batch8 = {"ms_per_step": round(ms8, 4), "tokens_per_s": round(8 / (ms8 * 1e-3), 1),
+                      "weight_gbs": round(bytes8 * world / ms8 / 1e6, 1), "exchange": "all-gather kernel over peer memory",
+                      "kernel": "gemv_mma_kernel (8 rows per pass over W)", "nccl_ms_per_step": round(float(ms8n.item()), 4),
+                      "logits_equal_nccl_path": bool(same8.item()), "wait_ran_out": bool(bad8.item())}
+            if not batch8["logits_equal_nccl_path"] or batch8["wait_ran_out"]:
+                batch8["invalid"] = "the two exchange paths disagree or a wait ran out"
+            b8.graph = None
+            del b8
+            torch.cuda.empty_cache()
             if not args.no_decode:
-                line["decode"] = decode_tokens_per_s(args.model)
-                other = "smollm2-135m" if args.model == "qwen3-8b" else "qwen3-8b"
-                line["decode_" + other.split("-")[0]] = decode_tokens_per_s(other)
-    sharded, batch8 = None, None
-    if world > 1 and args.batch == 1 and not args.no_extras:
-        chain.graph = None
-        # eight tokens per step over the same column shards: the 8-row GEMV kernel, then an all-gather kernel that stores
-        # the rank's rows into every peer's gathered vector and unpacks the whole; NCCL all-gathers timed beside it
-        b8 = dc.DecodeGemvChain(shape, fmt, batch=8, rank=rank, world=world, seed=0, mode="launches", exchange="peer")
-        b8.capture()
-        dist.barrier()
-        ms8 = torch.tensor([cuda_timed(b8.step, max(5, args.steps // 2), warmup=3)], device="cuda")
-        dist.all_reduce(ms8, op=dist.ReduceOp.MAX)
-        ms8 = float(ms8.item())
-        bad8 = torch.tensor([1 if b8.check_error() else 0], device="cuda")
-        dist.all_reduce(bad8, op=dist.ReduceOp.MAX)
-        peer_logits = b8.logits_view().clone()
-        bytes8 = b8.bytes_per_step()
-        b8.graph = None
-        del b8
-        torch.cuda.empty_cache()
-        b8 = dc.DecodeGemvChain(shape, fmt, batch=8, rank=rank, world=world, seed=0, mode="launches", exchange="nccl")
-        b8.capture()
-        dist.barrier()
-        ms8n = torch.tensor([cuda_timed(b8.step, max(5, args.steps // 2), warmup=3)], device="cuda")
-        dist.all_reduce(ms8n, op=dist.ReduceOp.MAX)
-        same8 = torch.tensor([1 if bool(torch.equal(peer_logits, b8.logits_view())) else 0], device="cuda")
-        dist.all_reduce(same8, op=dist.ReduceOp.MIN)
-        batch8 = {"ms_per_step": round(ms8, 4), "tokens_per_s": round(8 / (ms8 * 1e-3), 1),
-                  "weight_gbs": round(bytes8 * world / ms8 / 1e6, 1), "exchange": "all-gather kernel over peer memory",
-                  "kernel": "gemv_mma_kernel (8 rows per pass over W)", "nccl_ms_per_step": round(float(ms8n.item()), 4),
-                  "logits_equal_nccl_path": bool(same8.item()), "wait_ran_out": bool(bad8.item())}
-        if not batch8["logits_equal_nccl_path"] or batch8["wait_ran_out"]:
-            batch8["invalid"] = "the two exchange paths disagree or a wait ran out"
-        b8.graph = None
-        del b8
-        torch.cuda.empty_cache()
-        if not args.no_decode:
-            sharded = decode_sharded_tokens_per_s(args.model, rank, world)
+                sharded = decode_sharded_tokens_per_s(args.model, rank, world)
+        except Exception as exc:
+            extras_error = repr(exc)[:300]
+        if extras_timer is not None:
+            extras_timer.cancel()
     if rank == 0:
         if batch8 is not None:
             line["batch8"] = batch8
         if sharded is not None:
             line["decode_sharded"] = sharded
+        if extras_error is not None:
+            line["extras_error"] = extras_error
         print(json.dumps(line))
         if check is not None and not check["ok"]:
             sys.stdout.flush()
@@ -761,12 +784,12 @@ def main():
         # A captured graph that holds NCCL nodes must go before the communicator does (destroying the
         # process group first blocks forever); a watchdog ends the process if teardown still stalls.
         sys.stdout.flush()
-        dist.barrier()
-        torch.cuda.synchronize()
         bad = check is not None and not check["ok"]
-        watchdog = threading.Timer(30.0, lambda: os._exit(1 if bad else 0))
+        watchdog = threading.Timer(60.0, lambda: os._exit(1 if bad else 0))
         watchdog.daemon = True
         watchdog.start()
+        dist.barrier()
+        torch.cuda.synchronize()
         try:
             chain.graph = None
         except NameError:
